@@ -1,0 +1,148 @@
+/* C ABI of libnsa_b200.so: the NSA (native sparse attention) hot path on B200.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*; 0 = the legacy default stream), launches asynchronously on
+ * that stream and returns 0 on success or a negative NSA_ERR_* code.  After a
+ * failure nsa_last_error() returns a description (thread-local).  No entry
+ * point allocates device memory unless its comment says so: scratch space is
+ * passed in by the caller and sized by the matching *_workspace_bytes call.
+ *
+ * Tensor layouts (all contiguous, row-major):
+ *   q, o, do, dq          [B, Hq,  T,  D]
+ *   k, v, dk, dv          [B, Hkv, Lk, D]   Lk = T (window, selection) or n_blk (compression)
+ *   lse                   [B, Hq,  T]       float32, natural log; -1e9 on rows that attend nothing
+ *   block_idx             [B, Hkv, T,  S]   int32, -1 = empty slot
+ *   gate_logits           [B, Hq,  T,  3]
+ * Query head h reads kv head h / (Hq / Hkv).  Scores are scaled by D^-1/2.
+ *
+ * "Reference" below is the msb-msb/openbox-llm checkout; citations are
+ * file:line inside it.
+ */
+#ifndef NSA_B200_H
+#define NSA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NSA_DTYPE_BF16 0
+#define NSA_DTYPE_F32  1
+
+#define NSA_MODE_WINDOW   0   /* nsa_fused_kernel.py:46 */
+#define NSA_MODE_COMPRESS 1   /* nsa_fused_kernel.py:47 */
+
+/* which kernel family serves a call */
+#define NSA_IMPL_AUTO 0   /* tcgen05 kernels when the shape allows, else the SIMT kernels */
+#define NSA_IMPL_SIMT 1   /* CUDA-core kernels: any dtype, D in {16,32,64,128}, any G and block size */
+#define NSA_IMPL_TC   2   /* tcgen05/TMEM kernels only; NSA_ERR_UNSUPPORTED if the shape does not fit */
+
+#define NSA_OK               0
+#define NSA_ERR_BAD_ARG     -1
+#define NSA_ERR_UNSUPPORTED -2
+#define NSA_ERR_CUDA        -3
+#define NSA_ERR_WORKSPACE   -4
+#define NSA_ERR_DEVICE_WAIT -5   /* a bounded wait inside a kernel ran out */
+
+typedef struct NsaDims {
+  int32_t B, Hq, Hkv, T, D;
+  int32_t dtype;            /* NSA_DTYPE_* of q,k,v,o and their gradients */
+} NsaDims;
+
+const char* nsa_last_error(void);
+int nsa_version(void);
+/* 1 if the tcgen05 kernels can serve this shape (bf16, D in {64,128}, Hq/Hkv in {1,2,4,8,16}...) */
+int nsa_tc_supported(const NsaDims* dims, int block_size);
+
+/* ---- range attention: sliding window and compressed-KV branches --------------------------
+ * Replaces _range_attn_forward / _range_attn_backward and the kernels under them
+ * (nsa_fused_kernel.py:442-518, kernels :61-426) behind _RangeAttn (:521-534).
+ * mode WINDOW: query t attends keys [max(0,t-window+1), t]; Lk = T.
+ * mode COMPRESS: query t attends summaries j with (j+1)*block_size-1 <= t; Lk = n_blk.
+ * The forward also writes lse (the reference recomputes it in backward). */
+int nsa_range_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                       const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                       int impl, void* stream);
+size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int impl);
+int nsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                       const void* d_o, void* dq, void* dk, void* dv,
+                       const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                       void* workspace, size_t workspace_bytes, int impl, void* stream);
+
+/* ---- selected-block attention --------------------------------------------------------------
+ * Replaces selection_forward_triton (nsa_selection_kernel.py:175-213, kernels :104-291 and
+ * the LSE combine :336-365) and selection_backward_triton / selection_backward_fsa
+ * (nsa_selection_backward.py:156-189, :278-334) behind SelectionAttnTriton (:337-365).
+ * Query i attends token pos = blk*block_size+n of every listed block with blk >= 0,
+ * pos <= i and pos < T (nsa_selection_kernel.py:144). */
+size_t nsa_selection_fwd_workspace_bytes(const NsaDims* dims, int S, int block_size, int impl);
+int nsa_selection_fwd(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                      void* o, float* lse, const NsaDims* dims, int S, int block_size,
+                      void* workspace, size_t workspace_bytes, int impl, void* stream);
+size_t nsa_selection_bwd_workspace_bytes(const NsaDims* dims, int S, int block_size, int impl);
+int nsa_selection_bwd(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                      const void* o, const float* lse, const void* d_o,
+                      void* dq, void* dk, void* dv, const NsaDims* dims, int S, int block_size,
+                      void* workspace, size_t workspace_bytes, int impl, void* stream);
+
+/* ---- block -> query CSR ---------------------------------------------------------------------
+ * Replaces build_block_to_query_csr (nsa_fsa.py:14-64): pairs (query i, block j) with j >= 0
+ * and j*block_size <= i, grouped by (b, hkv, j), queries ascending.  block_offsets is
+ * [B,Hkv,n_blk+1] global offsets; q_of_block and pair_bh need room for B*Hkv*T*S entries.
+ * The number of pairs is block_offsets[B*Hkv*(n_blk+1)-1]. */
+size_t nsa_csr_workspace_bytes(int B, int Hkv, int T, int S, int block_size);
+int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int Hkv, int T, int S,
+                                 int block_size, int32_t* q_of_block, int32_t* block_offsets,
+                                 int32_t* pair_bh, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+
+/* ---- compression summaries ------------------------------------------------------------------
+ * Mean pooling replaces block_mean_pool (nsa_fused_kernel.py:549-554); the learned pooling
+ * replaces BlockCompressor.forward (nsa_model.py:118-123) as called at nsa_model.py:336-337:
+ * out = proj_w @ sum_pos softmax(pool_logits)[pos] * (x[pos] + intra_pos[pos]).
+ * x [B,Hkv,T,D] -> out [B,Hkv,n_blk,D], n_blk = T / block_size.  Parameters are float32. */
+int nsa_block_mean_pool_fwd(const void* x, void* out, int B, int Hkv, int T, int D, int block_size,
+                            int dtype, void* stream);
+int nsa_block_mean_pool_bwd(const void* d_out, void* dx, int B, int Hkv, int T, int D,
+                            int block_size, int dtype, void* stream);
+int nsa_block_compress_fwd(const void* x, const float* intra_pos, const float* pool_logits,
+                           const float* proj_w, void* out, int B, int Hkv, int T, int D,
+                           int block_size, int dtype, void* stream);
+size_t nsa_block_compress_bwd_workspace_bytes(int B, int Hkv, int T, int D, int block_size);
+int nsa_block_compress_bwd(const void* x, const float* intra_pos, const float* pool_logits,
+                           const float* proj_w, const void* d_out, void* dx, float* d_intra_pos,
+                           float* d_pool_logits, float* d_proj_w, int B, int Hkv, int T, int D,
+                           int block_size, int dtype, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* ---- block scoring and top-n ----------------------------------------------------------------
+ * Replaces the dense scoring pass of nsa_model.py:343-355: importance of block j for
+ * (b, hkv, t) is the sum over the group's query heads of the compression-branch softmax
+ * probability of summary j; the n_sel causally valid blocks ((j+1)*block_size-1 <= t) of
+ * largest importance are written in order (importance descending, index ascending on ties),
+ * -1 in slots with no valid block.  lse_cmp is the lse written by nsa_range_attn_fwd in
+ * COMPRESS mode.  importance_out (optional, may be NULL) receives [B,Hkv,T,n_blk] float32. */
+int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp, int32_t* block_idx,
+                    float* importance_out, const NsaDims* dims, int n_blk, int block_size,
+                    int n_sel, void* stream);
+
+/* ---- gate combine ---------------------------------------------------------------------------
+ * Replaces the sigmoid blend nsa_model.py:366-368 / nsa_fused_kernel.py:572-573 and its
+ * autograd backward: out = sum_i sigmoid(gate[...,i]) * o_i; d_gate is float32-accumulated
+ * and written in the gate dtype. */
+int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const void* o_win,
+                         const void* gate_logits, void* out, const NsaDims* dims, void* stream);
+int nsa_gate_combine_bwd(const void* o_cmp, const void* o_slc, const void* o_win,
+                         const void* gate_logits, const void* d_out, void* do_cmp, void* do_slc,
+                         void* do_win, void* d_gate_logits, const NsaDims* dims, void* stream);
+
+/* error flag raised by a kernel whose bounded wait ran out (0 = none); reading it synchronises
+ * the stream. */
+int nsa_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSA_B200_H */

@@ -1,0 +1,98 @@
+"""ctypes binding of libnsa_b200.so.  There is no fallback: if the library is missing or a
+call fails, an exception is raised."""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libnsa_b200.so")
+
+DTYPE_BF16, DTYPE_F32 = 0, 1
+MODE_WINDOW, MODE_COMPRESS = 0, 1
+IMPL = {"auto": 0, "simt": 1, "tc": 2}
+
+
+class NsaDims(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("B", "Hq", "Hkv", "T", "D", "dtype")]
+
+
+class NsaError(RuntimeError):
+    pass
+
+
+_lib = None
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_dp = ctypes.POINTER(NsaDims)
+
+# every symbol the header declares, with its signature
+SIGNATURES = {
+    "nsa_last_error": (ctypes.c_char_p, []),
+    "nsa_version": (_i, []),
+    "nsa_tc_supported": (_i, [_dp, _i]),
+    "nsa_device_status": (_i, [_vp]),
+    "nsa_range_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _dp, _i, _i, _i, _i, _i, _vp]),
+    "nsa_range_attn_bwd_workspace_bytes": (_sz, [_dp, _i, _i]),
+    "nsa_range_attn_bwd": (_i, [_vp] * 9 + [_dp, _i, _i, _i, _i, _vp, _sz, _i, _vp]),
+    "nsa_selection_fwd_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
+    "nsa_selection_fwd": (_i, [_vp] * 6 + [_dp, _i, _i, _vp, _sz, _i, _vp]),
+    "nsa_selection_bwd_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
+    "nsa_selection_bwd": (_i, [_vp] * 10 + [_dp, _i, _i, _vp, _sz, _i, _vp]),
+    "nsa_csr_workspace_bytes": (_sz, [_i] * 5),
+    "nsa_build_block_to_query_csr": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "nsa_block_mean_pool_fwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "nsa_block_mean_pool_bwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "nsa_block_compress_fwd": (_i, [_vp] * 5 + [_i] * 6 + [_vp]),
+    "nsa_block_compress_bwd_workspace_bytes": (_sz, [_i] * 5),
+    "nsa_block_compress_bwd": (_i, [_vp] * 9 + [_i] * 6 + [_vp, _sz, _vp]),
+    "nsa_topn_blocks": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _vp]),
+    "nsa_gate_combine_fwd": (_i, [_vp] * 5 + [_dp, _vp]),
+    "nsa_gate_combine_bwd": (_i, [_vp] * 9 + [_dp, _vp]),
+}
+
+
+def lib():
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NsaError(f"{LIB_PATH} is missing: build it with `python {_HERE}/build.py`; "
+                           "there is no non-CUDA fallback")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise NsaError(f"libnsa_b200 error {rc}: {lib().nsa_last_error().decode()}")
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return DTYPE_BF16
+    if t.dtype == torch.float32:
+        return DTYPE_F32
+    raise TypeError(f"libnsa_b200 takes bfloat16 or float32 tensors, got {t.dtype}")
+
+
+def ptr(t):
+    if t is None:
+        return None
+    assert t.is_cuda, "libnsa_b200 needs CUDA tensors; there is no CPU path"
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def dims(B, Hq, Hkv, T, D, dtype):
+    return NsaDims(B, Hq, Hkv, T, D, dtype)
+
+
+def workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)

@@ -1,0 +1,255 @@
+// C-ABI entry points of the attention branches: argument checks, kernel-family choice,
+// workspace carving.  The kernels live in simt.cu (CUDA cores) and tc.cu (tcgen05 / TMEM).
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace nsa {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+// One status word per device, raised (atomicOr) by kernels whose bounded waits run out.
+__device__ int g_device_status = 0;
+
+int* device_status_ptr() {
+  int* p = nullptr;
+  if (cudaGetSymbolAddress((void**)&p, g_device_status) != cudaSuccess) return nullptr;
+  return p;
+}
+
+static int check_dims(const NsaDims* d) {
+  NSA_CHECK_ARG(d != nullptr, "dims is null");
+  NSA_CHECK_ARG(d->B >= 0 && d->T >= 0 && d->Hq > 0 && d->Hkv > 0, "bad B/T/Hq/Hkv");
+  NSA_CHECK_ARG(d->Hq % d->Hkv == 0, "Hq=%d is not a multiple of Hkv=%d", d->Hq, d->Hkv);
+  NSA_CHECK_ARG(d->D == 16 || d->D == 32 || d->D == 64 || d->D == 128,
+                "head dim must be a power of two <= 128, got %d", d->D);   // nsa_selection_kernel.py:187
+  NSA_CHECK_ARG(d->dtype == NSA_DTYPE_BF16 || d->dtype == NSA_DTYPE_F32, "bad dtype %d", d->dtype);
+  return NSA_OK;
+}
+
+static size_t elem_size(int dtype) { return dtype == NSA_DTYPE_BF16 ? 2 : 4; }
+
+static AttnArgs base_args(const NsaDims* d, int Lk) {
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.B = d->B; a.Hq = d->Hq; a.Hkv = d->Hkv; a.T = d->T; a.D = d->D; a.Lk = Lk;
+  a.scale = 1.0f / sqrtf((float)d->D);
+  return a;
+}
+
+static bool use_tc(const NsaDims* d, int block_size, int impl, int* err) {
+  *err = NSA_OK;
+  if (impl == NSA_IMPL_SIMT) return false;
+  const bool ok = tc_shape_ok(*d, block_size);
+  if (impl == NSA_IMPL_TC && !ok) {
+    set_error("shape not served by the tcgen05 kernels (bf16, D in {64,128}, group in {1,2,4,8,16})");
+    *err = NSA_ERR_UNSUPPORTED;
+  }
+  return ok;
+}
+
+// backward through the SIMT kernels: dq direct, dk/dv via fp32 accumulators
+static size_t simt_bwd_ws(const NsaDims* d, int Lk) {
+  if (d->dtype == NSA_DTYPE_F32) return 0;   // accumulate straight into dk/dv
+  return 2 * align_up((size_t)d->B * d->Hkv * Lk * d->D * sizeof(float), 256);
+}
+
+static int simt_bwd(AttnArgs& a, const NsaDims* d, void* dk, void* dv, void* ws, size_t ws_bytes,
+                    cudaStream_t st) {
+  const size_t n = (size_t)d->B * d->Hkv * a.Lk * d->D;
+  if (d->dtype == NSA_DTYPE_F32) {
+    a.dk_acc = (float*)dk;
+    a.dv_acc = (float*)dv;
+  } else {
+    if (ws_bytes < simt_bwd_ws(d, a.Lk) || (!ws && n)) {
+      set_error("backward workspace too small: need %zu bytes", simt_bwd_ws(d, a.Lk));
+      return NSA_ERR_WORKSPACE;
+    }
+    a.dk_acc = (float*)ws;
+    a.dv_acc = (float*)((char*)ws + align_up(n * sizeof(float), 256));
+  }
+  if (n) {
+    NSA_CUDA_OK(cudaMemsetAsync(a.dk_acc, 0, n * sizeof(float), st));
+    NSA_CUDA_OK(cudaMemsetAsync(a.dv_acc, 0, n * sizeof(float), st));
+  }
+  int rc = simt_attn_bwd(a, d->dtype, st);
+  if (rc != NSA_OK) return rc;
+  if (d->dtype != NSA_DTYPE_F32) {
+    rc = cast_f32_to(a.dk_acc, dk, n, d->dtype, st);
+    if (rc != NSA_OK) return rc;
+    rc = cast_f32_to(a.dv_acc, dv, n, d->dtype, st);
+  }
+  return rc;
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" const char* nsa_last_error(void) { return g_err; }
+extern "C" int nsa_version(void) { return 100; }
+
+extern "C" int nsa_tc_supported(const NsaDims* dims, int block_size) {
+  if (check_dims(dims) != NSA_OK) return 0;
+  return tc_shape_ok(*dims, block_size) ? 1 : 0;
+}
+
+extern "C" int nsa_device_status(void* stream) {
+  int* p = device_status_ptr();
+  if (!p) { set_error("cudaGetSymbolAddress failed"); return NSA_ERR_CUDA; }
+  int v = 0;
+  NSA_CUDA_OK(cudaMemcpyAsync(&v, p, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  NSA_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  if (v != 0) {
+    set_error("a kernel gave up a bounded wait (status word 0x%x)", v);
+    int zero = 0;
+    cudaMemcpyAsync(p, &zero, sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    cudaStreamSynchronize((cudaStream_t)stream);
+    return NSA_ERR_DEVICE_WAIT;
+  }
+  return NSA_OK;
+}
+
+// ---- range attention -------------------------------------------------------------------------
+extern "C" int nsa_range_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                                  const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                                  int impl, void* stream) {
+  int rc = check_dims(dims);
+  if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(mode == NSA_MODE_WINDOW || mode == NSA_MODE_COMPRESS, "bad mode %d", mode);
+  NSA_CHECK_ARG(Lk >= 0, "bad Lk");
+  if (mode == NSA_MODE_WINDOW) NSA_CHECK_ARG(window >= 1, "window must be >= 1");
+  if (mode == NSA_MODE_COMPRESS) NSA_CHECK_ARG(block_size >= 1, "block_size must be >= 1");
+  const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
+  if (rows == 0) return NSA_OK;
+  NSA_CHECK_ARG(q && o && lse && (Lk == 0 || (k && v)), "null tensor");
+  AttnArgs a = base_args(dims, Lk);
+  a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse;
+  a.kind = mode; a.window = window; a.block_size = block_size;
+  if (use_tc(dims, 64, impl, &rc) && Lk > 0) return tc_attn_fwd(a, (cudaStream_t)stream);
+  if (rc != NSA_OK) return rc;
+  return simt_attn_fwd(a, dims->dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int impl) {
+  if (check_dims(dims) != NSA_OK) return 0;
+  int rc;
+  size_t need = simt_bwd_ws(dims, Lk);
+  if (use_tc(dims, 64, impl, &rc)) {
+    AttnArgs a = base_args(dims, Lk);
+    a.kind = 0;
+    need = need > tc_attn_bwd_workspace(a) ? need : tc_attn_bwd_workspace(a);
+  }
+  return need;
+}
+
+extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o,
+                                  const float* lse, const void* d_o, void* dq, void* dk, void* dv,
+                                  const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                                  void* workspace, size_t workspace_bytes, int impl, void* stream) {
+  int rc = check_dims(dims);
+  if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(mode == NSA_MODE_WINDOW || mode == NSA_MODE_COMPRESS, "bad mode %d", mode);
+  if (mode == NSA_MODE_WINDOW) NSA_CHECK_ARG(window >= 1, "window must be >= 1");
+  if (mode == NSA_MODE_COMPRESS) NSA_CHECK_ARG(block_size >= 1, "block_size must be >= 1");
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
+  const size_t nkv = (size_t)dims->B * dims->Hkv * Lk * dims->D;
+  if (rows == 0 || Lk == 0) {
+    if (rows) NSA_CUDA_OK(cudaMemsetAsync(dq, 0, rows * dims->D * elem_size(dims->dtype), st));
+    if (nkv) {
+      NSA_CUDA_OK(cudaMemsetAsync(dk, 0, nkv * elem_size(dims->dtype), st));
+      NSA_CUDA_OK(cudaMemsetAsync(dv, 0, nkv * elem_size(dims->dtype), st));
+    }
+    return NSA_OK;
+  }
+  NSA_CHECK_ARG(q && k && v && o && lse && d_o && dq && dk && dv, "null tensor");
+  AttnArgs a = base_args(dims, Lk);
+  a.q = q; a.k = k; a.v = v; a.o = (void*)o; a.lse = (float*)lse; a.d_o = d_o; a.dq = dq;
+  a.kind = mode; a.window = window; a.block_size = block_size;
+  if (use_tc(dims, 64, impl, &rc)) {
+    a.dk_acc = (float*)dk;   // tc path writes dk/dv itself; pass the outputs through
+    a.dv_acc = (float*)dv;
+    return tc_attn_bwd(a, workspace, workspace_bytes, st);
+  }
+  if (rc != NSA_OK) return rc;
+  return simt_bwd(a, dims, dk, dv, workspace, workspace_bytes, st);
+}
+
+// ---- selection attention ---------------------------------------------------------------------
+extern "C" size_t nsa_selection_fwd_workspace_bytes(const NsaDims* dims, int S, int block_size,
+                                                    int impl) {
+  (void)dims; (void)S; (void)block_size; (void)impl;
+  return 0;
+}
+
+static int check_sel(const NsaDims* dims, int S, int block_size) {
+  int rc = check_dims(dims);
+  if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(S >= 0, "bad S");
+  NSA_CHECK_ARG(block_size >= 16, "block_size must be >= 16");   // nsa_selection_kernel.py:188
+  return NSA_OK;
+}
+
+extern "C" int nsa_selection_fwd(const void* q, const void* k, const void* v,
+                                 const int32_t* block_idx, void* o, float* lse, const NsaDims* dims,
+                                 int S, int block_size, void* workspace, size_t workspace_bytes,
+                                 int impl, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  int rc = check_sel(dims, S, block_size);
+  if (rc != NSA_OK) return rc;
+  const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
+  if (rows == 0) return NSA_OK;
+  NSA_CHECK_ARG(q && k && v && o && lse && (S == 0 || block_idx), "null tensor");
+  AttnArgs a = base_args(dims, dims->T);
+  a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse; a.block_idx = block_idx;
+  a.kind = 2; a.S = S; a.block_size = block_size;
+  if (use_tc(dims, block_size, impl, &rc) && S > 0) return tc_attn_fwd(a, (cudaStream_t)stream);
+  if (rc != NSA_OK) return rc;
+  return simt_attn_fwd(a, dims->dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t nsa_selection_bwd_workspace_bytes(const NsaDims* dims, int S, int block_size,
+                                                    int impl) {
+  if (check_sel(dims, S, block_size) != NSA_OK) return 0;
+  int rc;
+  size_t need = simt_bwd_ws(dims, dims->T);
+  if (use_tc(dims, block_size, impl, &rc)) {
+    AttnArgs a = base_args(dims, dims->T);
+    a.kind = 2; a.S = S; a.block_size = block_size;
+    need = need > tc_attn_bwd_workspace(a) ? need : tc_attn_bwd_workspace(a);
+  }
+  return need;
+}
+
+extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
+                                 const int32_t* block_idx, const void* o, const float* lse,
+                                 const void* d_o, void* dq, void* dk, void* dv, const NsaDims* dims,
+                                 int S, int block_size, void* workspace, size_t workspace_bytes,
+                                 int impl, void* stream) {
+  int rc = check_sel(dims, S, block_size);
+  if (rc != NSA_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
+  if (rows == 0) return NSA_OK;
+  NSA_CHECK_ARG(q && k && v && o && lse && d_o && dq && dk && dv && (S == 0 || block_idx),
+                "null tensor");
+  AttnArgs a = base_args(dims, dims->T);
+  a.q = q; a.k = k; a.v = v; a.o = (void*)o; a.lse = (float*)lse; a.d_o = d_o; a.dq = dq;
+  a.block_idx = block_idx; a.kind = 2; a.S = S; a.block_size = block_size;
+  if (use_tc(dims, block_size, impl, &rc) && S > 0) {
+    a.dk_acc = (float*)dk;
+    a.dv_acc = (float*)dv;
+    return tc_attn_bwd(a, workspace, workspace_bytes, st);
+  }
+  if (rc != NSA_OK) return rc;
+  return simt_bwd(a, dims, dk, dv, workspace, workspace_bytes, st);
+}

@@ -1,0 +1,611 @@
+// Bandwidth-bound companions of the attention kernels: compression pooling, block scoring +
+// top-n, block->query CSR inversion and the sigmoid gate combine.
+#include "common.cuh"
+
+namespace nsa {
+namespace {
+
+// ------------------------------------------------------------------------------------------
+// mean pooling (nsa_fused_kernel.py:549-554)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void mean_pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ out, int T_, int D,
+                                     int bs, int n_blk, size_t n_out) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_out) return;
+  const int d = (int)(i % D);
+  const int j = (int)((i / D) % n_blk);
+  const size_t bh = i / ((size_t)D * n_blk);
+  const T* p = x + (bh * T_ + (size_t)j * bs) * D + d;
+  float s = 0.f;
+  for (int r = 0; r < bs; ++r) s += to_float(p[(size_t)r * D]);
+  out[i] = from_float<T>(s / (float)bs);
+}
+
+template <typename T>
+__global__ void mean_pool_bwd_kernel(const T* __restrict__ d_out, T* __restrict__ dx, int T_, int D,
+                                     int bs, int n_blk, size_t n_in) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_in) return;
+  const int d = (int)(i % D);
+  const int t = (int)((i / D) % T_);
+  const size_t bh = i / ((size_t)D * T_);
+  const int j = t / bs;
+  float g = 0.f;
+  if (j < n_blk) g = to_float(d_out[(bh * n_blk + j) * D + d]) / (float)bs;
+  dx[i] = from_float<T>(g);
+}
+
+// ------------------------------------------------------------------------------------------
+// learned pooling (nsa_model.py:118-123): one CTA of D threads per (b, hkv, block)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void compress_fwd_kernel(const T* __restrict__ x, const float* __restrict__ intra,
+                                    const float* __restrict__ logits, const float* __restrict__ proj,
+                                    T* __restrict__ out, float* __restrict__ pooled_out, int T_,
+                                    int D, int bs, int n_blk) {
+  extern __shared__ float sm[];
+  float* w = sm;            // [bs]
+  float* pooled = sm + bs;  // [D]
+  const int j = blockIdx.x % n_blk;
+  const size_t bh = blockIdx.x / n_blk;
+  const int d = threadIdx.x;
+  // softmax over the block positions, every thread redundantly (bs is small)
+  float mx = -INFINITY;
+  for (int r = 0; r < bs; ++r) mx = fmaxf(mx, logits[r]);
+  float den = 0.f;
+  for (int r = 0; r < bs; ++r) den += expf(logits[r] - mx);
+  for (int r = d; r < bs; r += blockDim.x) w[r] = expf(logits[r] - mx) / den;
+  __syncthreads();
+  const bool act = d < D;   // the CTA is padded to whole warps
+  const T* p = x + (bh * T_ + (size_t)j * bs) * D + d;
+  float s = 0.f;
+  if (act) {
+    for (int r = 0; r < bs; ++r) s = fmaf(w[r], to_float(p[(size_t)r * D]) + intra[r * D + d], s);
+    pooled[d] = s;
+    if (pooled_out) pooled_out[(bh * n_blk + j) * D + d] = s;
+  }
+  __syncthreads();
+  if (out && act) {
+    float o = 0.f;
+    const float* pr = proj + (size_t)d * D;   // out[o] = sum_i proj[o][i] * pooled[i]
+    for (int i = 0; i < D; ++i) o = fmaf(pr[i], pooled[i], o);
+    out[(bh * n_blk + j) * D + d] = from_float<T>(o);
+  }
+}
+
+// backward stage A: per block.  d_pooled = d_out @ W; dx = w[pos] * d_pooled;
+// sum_dpooled[d] += d_pooled[d]; d_w[pos] += sum_d d_pooled[d] * (x[pos][d] + intra[pos][d]).
+template <typename T>
+__global__ void compress_bwd_block_kernel(const T* __restrict__ x, const float* __restrict__ intra,
+                                          const float* __restrict__ logits,
+                                          const float* __restrict__ proj,
+                                          const T* __restrict__ d_out, T* __restrict__ dx,
+                                          float* __restrict__ d_pooled_out,
+                                          float* __restrict__ sum_dpooled, float* __restrict__ d_w,
+                                          int T_, int D, int bs, int n_blk) {
+  extern __shared__ float sm[];
+  float* w = sm;           // [bs]
+  float* go = sm + bs;     // [D] d_out row
+  float* red = go + D;     // [D] reduction scratch
+  const int j = blockIdx.x % n_blk;
+  const size_t bh = blockIdx.x / n_blk;
+  const int d = threadIdx.x;
+  float mx = -INFINITY;
+  for (int r = 0; r < bs; ++r) mx = fmaxf(mx, logits[r]);
+  float den = 0.f;
+  for (int r = 0; r < bs; ++r) den += expf(logits[r] - mx);
+  for (int r = d; r < bs; r += blockDim.x) w[r] = expf(logits[r] - mx) / den;
+  const bool act = d < D;   // the CTA is padded to whole warps
+  if (act) go[d] = to_float(d_out[(bh * n_blk + j) * D + d]);
+  __syncthreads();
+  float dp = 0.f;   // d_pooled[d] = sum_o d_out[o] * proj[o][d]
+  if (act) {
+    for (int o = 0; o < D; ++o) dp = fmaf(go[o], proj[(size_t)o * D + d], dp);
+    d_pooled_out[(bh * n_blk + j) * D + d] = dp;
+    atomicAdd(sum_dpooled + d, dp);
+  }
+  const size_t xo = (bh * T_ + (size_t)j * bs) * D + d;
+  for (int r = 0; r < bs; ++r) {
+    float xv = 0.f;
+    if (act) {
+      xv = to_float(x[xo + (size_t)r * D]) + intra[r * D + d];
+      dx[xo + (size_t)r * D] = from_float<T>(w[r] * dp);
+    }
+    // reduce dp * xv over d for position r
+    float part = warp_sum(dp * xv);
+    if ((d & 31) == 0) red[d >> 5] = part;
+    __syncthreads();
+    if (d == 0) {
+      float tot = 0.f;
+      for (int k = 0; k < (int)(blockDim.x + 31) / 32; ++k) tot += red[k];
+      atomicAdd(d_w + r, tot);
+    }
+    __syncthreads();
+  }
+}
+
+// tail tokens past the last complete block get zero gradient
+template <typename T>
+__global__ void zero_tail_kernel(T* __restrict__ dx, int T_, int D, int t_first, size_t n_bh) {
+  const size_t per = (size_t)(T_ - t_first) * D;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= per * n_bh) return;
+  const size_t bh = i / per, r = i % per;
+  dx[(bh * T_ + t_first) * D + r] = from_float<T>(0.f);
+}
+
+// stage B: d_proj[o][i] = sum_rows d_out[row][o] * pooled[row][i]; one CTA per o
+template <typename T>
+__global__ void compress_bwd_proj_kernel(const T* __restrict__ d_out, const float* __restrict__ pooled,
+                                         float* __restrict__ d_proj, size_t rows, int D) {
+  const int o = blockIdx.x, i = threadIdx.x;
+  if (i >= D) return;
+  float s = 0.f;
+  for (size_t r = 0; r < rows; ++r) s = fmaf(to_float(d_out[r * D + o]), pooled[r * D + i], s);
+  d_proj[(size_t)o * D + i] = s;
+}
+
+// stage C: d_intra[pos][d] = w[pos] * sum_dpooled[d]; d_logits = w * (d_w - sum(d_w * w))
+__global__ void compress_bwd_final_kernel(const float* __restrict__ logits,
+                                          const float* __restrict__ sum_dpooled,
+                                          const float* __restrict__ d_w, float* __restrict__ d_intra,
+                                          float* __restrict__ d_logits, int D, int bs) {
+  extern __shared__ float w[];
+  float mx = -INFINITY;
+  for (int r = 0; r < bs; ++r) mx = fmaxf(mx, logits[r]);
+  float den = 0.f;
+  for (int r = 0; r < bs; ++r) den += expf(logits[r] - mx);
+  for (int r = threadIdx.x; r < bs; r += blockDim.x) w[r] = expf(logits[r] - mx) / den;
+  __syncthreads();
+  float dot = 0.f;
+  for (int r = 0; r < bs; ++r) dot = fmaf(d_w[r], w[r], dot);
+  for (int r = threadIdx.x; r < bs; r += blockDim.x) d_logits[r] = w[r] * (d_w[r] - dot);
+  for (int i = threadIdx.x; i < bs * D; i += blockDim.x) d_intra[i] = w[i / D] * sum_dpooled[i % D];
+}
+
+// ------------------------------------------------------------------------------------------
+// block scoring + top-n (nsa_model.py:343-355): one warp per (b, hkv, t)
+// ------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(128) topn_kernel(const T* __restrict__ q, const T* __restrict__ kc,
+                                                   const float* __restrict__ lse,
+                                                   int32_t* __restrict__ block_idx,
+                                                   float* __restrict__ imp_out, int B, int Hq, int Hkv,
+                                                   int T_, int n_blk, int bs, int n_sel, float scale) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* qs = sm + (size_t)warp * (D + n_blk);   // [D]
+  float* imp = qs + D;                           // [n_blk]
+  const size_t total = (size_t)B * Hkv * T_;
+  const size_t unit = (size_t)blockIdx.x * 4 + warp;
+  if (unit >= total) return;
+  const int t = (int)(unit % T_);
+  const int hkv = (int)((unit / T_) % Hkv);
+  const int b = (int)(unit / ((size_t)T_ * Hkv));
+  const int G = Hq / Hkv;
+  const int n_valid = min((t + 1) / bs, n_blk);
+  for (int j = lane; j < n_blk; j += 32) imp[j] = 0.f;
+  const T* kbase = kc + (size_t)(b * Hkv + hkv) * n_blk * D;
+  for (int g = 0; g < G; ++g) {
+    const size_t row = ((size_t)(b * Hq + hkv * G + g)) * T_ + t;
+    __syncwarp();
+    for (int d = lane; d < D; d += 32) qs[d] = to_float(q[row * D + d]) * scale;
+    __syncwarp();
+    const float l = lse[row];
+    for (int j = lane; j < n_valid; j += 32) {
+      float s;
+      if constexpr (sizeof(T) == 2) {
+        float acc = 0.f;
+        const uint4* r4 = reinterpret_cast<const uint4*>(kbase + (size_t)j * D);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          uint4 u = __ldg(r4 + i);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float2 f = __bfloat1622float2(h2[c]);
+            acc = fmaf(f.x, qs[i * 8 + 2 * c], acc);
+            acc = fmaf(f.y, qs[i * 8 + 2 * c + 1], acc);
+          }
+        }
+        s = acc;
+      } else {
+        float acc = 0.f;
+        const float* kr = reinterpret_cast<const float*>(kbase) + (size_t)j * D;
+        for (int i = 0; i < D; ++i) acc = fmaf(kr[i], qs[i], acc);
+        s = acc;
+      }
+      imp[j] += expf(s - l);
+    }
+  }
+  __syncwarp();
+  if (imp_out) {
+    float* dst = imp_out + unit * n_blk;
+    for (int j = lane; j < n_blk; j += 32) dst[j] = j < n_valid ? imp[j] : 0.f;
+  }
+  int32_t* out = block_idx + unit * n_sel;
+  for (int s = 0; s < n_sel; ++s) {
+    float best = -1.f;
+    int bj = 0x7fffffff;
+    for (int j = lane; j < n_valid; j += 32) {
+      const float v = imp[j];
+      if (v > best) { best = v; bj = j; }        // ascending j: first maximum wins
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
+      if (ov > best || (ov == best && oj < bj)) { best = ov; bj = oj; }
+    }
+    const bool found = best >= 0.f;
+    if (lane == 0) out[s] = found ? bj : -1;
+    if (found && lane == (bj & 31)) imp[bj] = -2.f;   // taken
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// block -> query CSR (nsa_fsa.py:14-64) through a [B*Hkv, n_blk, T] bitmap
+// ------------------------------------------------------------------------------------------
+__global__ void csr_mark_kernel(const int32_t* __restrict__ idx, uint32_t* __restrict__ bitmap,
+                                int T_, int S, int bs, int n_blk, int words, size_t n_entries) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_entries) return;
+  const int j = idx[i];
+  const int t = (int)((i / S) % T_);
+  const size_t bh = i / ((size_t)S * T_);
+  if (j < 0 || j >= n_blk || (long long)j * bs > t) return;
+  atomicOr(bitmap + (bh * n_blk + j) * words + (t >> 5), 1u << (t & 31));
+}
+
+// one warp per (bh, block) row: population count
+__global__ void csr_count_kernel(const uint32_t* __restrict__ bitmap, int32_t* __restrict__ counts,
+                                 int words, size_t rows) {
+  const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  int c = 0;
+  for (int w = lane; w < words; w += 32) c += __popc(bitmap[row * words + w]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if (lane == 0) counts[row] = c;
+}
+
+// single CTA exclusive scan of counts[rows] into block_offsets laid out [BH][n_blk+1]
+__global__ void csr_scan_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                                int32_t* __restrict__ row_start, int n_blk, size_t rows) {
+  __shared__ int part[1024];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (size_t base = 0; base < rows; base += 1024) {
+    const size_t r = base + threadIdx.x;
+    const int c = r < rows ? counts[r] : 0;
+    part[threadIdx.x] = c;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      int v = threadIdx.x >= o ? part[threadIdx.x - o] : 0;
+      __syncthreads();
+      part[threadIdx.x] += v;
+      __syncthreads();
+    }
+    const int incl = part[threadIdx.x] + carry;
+    if (r < rows) {
+      const size_t bh = r / n_blk, j = r % n_blk;
+      row_start[r] = incl - c;
+      offsets[bh * (n_blk + 1) + j] = incl - c;
+      offsets[bh * (n_blk + 1) + j + 1] = incl;   // last block of a group; else overwritten equal
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = incl;
+    __syncthreads();
+  }
+}
+
+// one warp per row: emit set bits in ascending t
+__global__ void csr_fill_kernel(const uint32_t* __restrict__ bitmap, const int32_t* __restrict__ row_start,
+                                int32_t* __restrict__ q_of_block, int32_t* __restrict__ pair_bh,
+                                int n_blk, int words, size_t rows) {
+  const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  int pos = row_start[row];
+  const int bh = (int)(row / n_blk);
+  for (int w0 = 0; w0 < words; w0 += 32) {
+    const int w = w0 + lane;
+    const uint32_t bits = w < words ? bitmap[row * words + w] : 0u;
+    const int c = __popc(bits);
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int p = pos + incl - c;
+    uint32_t rem = bits;
+    while (rem) {
+      const int bit = __ffs(rem) - 1;
+      rem &= rem - 1;
+      q_of_block[p] = w * 32 + bit;
+      pair_bh[p] = bh;
+      ++p;
+    }
+    pos += __shfl_sync(0xffffffffu, incl, 31);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// gate combine (nsa_model.py:366-368)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+// one warp per (b,h,t) row
+template <typename T>
+__global__ void gate_fwd_kernel(const T* __restrict__ oc, const T* __restrict__ os,
+                                const T* __restrict__ ow, const T* __restrict__ gate,
+                                T* __restrict__ out, size_t rows, int D) {
+  const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float g0 = sigmoidf_(to_float(gate[row * 3 + 0]));
+  const float g1 = sigmoidf_(to_float(gate[row * 3 + 1]));
+  const float g2 = sigmoidf_(to_float(gate[row * 3 + 2]));
+  for (int d = lane; d < D; d += 32) {
+    const size_t i = row * D + d;
+    out[i] = from_float<T>(g0 * to_float(oc[i]) + g1 * to_float(os[i]) + g2 * to_float(ow[i]));
+  }
+}
+
+template <typename T>
+__global__ void gate_bwd_kernel(const T* __restrict__ oc, const T* __restrict__ os,
+                                const T* __restrict__ ow, const T* __restrict__ gate,
+                                const T* __restrict__ d_out, T* __restrict__ dc, T* __restrict__ ds,
+                                T* __restrict__ dw, T* __restrict__ d_gate, size_t rows, int D) {
+  const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float g0 = sigmoidf_(to_float(gate[row * 3 + 0]));
+  const float g1 = sigmoidf_(to_float(gate[row * 3 + 1]));
+  const float g2 = sigmoidf_(to_float(gate[row * 3 + 2]));
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const size_t i = row * D + d;
+    const float g = to_float(d_out[i]);
+    a0 = fmaf(g, to_float(oc[i]), a0);
+    a1 = fmaf(g, to_float(os[i]), a1);
+    a2 = fmaf(g, to_float(ow[i]), a2);
+    dc[i] = from_float<T>(g0 * g);
+    ds[i] = from_float<T>(g1 * g);
+    dw[i] = from_float<T>(g2 * g);
+  }
+  a0 = warp_sum(a0); a1 = warp_sum(a1); a2 = warp_sum(a2);
+  if (lane == 0) {
+    d_gate[row * 3 + 0] = from_float<T>(a0 * g0 * (1.f - g0));
+    d_gate[row * 3 + 1] = from_float<T>(a1 * g1 * (1.f - g1));
+    d_gate[row * 3 + 2] = from_float<T>(a2 * g2 * (1.f - g2));
+  }
+}
+
+inline unsigned blocks_for(size_t n, int per) { return (unsigned)((n + per - 1) / per); }
+
+}  // namespace
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" int nsa_block_mean_pool_fwd(const void* x, void* out, int B, int Hkv, int T, int D,
+                                       int block_size, int dtype, void* stream) {
+  NSA_CHECK_ARG(block_size > 0 && D > 0, "bad block_size/D");
+  const int n_blk = T / block_size;
+  const size_t n = (size_t)B * Hkv * n_blk * D;
+  if (n == 0) return NSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == NSA_DTYPE_BF16)
+    mean_pool_fwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, T, D, block_size, n_blk, n);
+  else
+    mean_pool_fwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const float*)x, (float*)out, T, D, block_size, n_blk, n);
+  NSA_LAUNCH_OK("mean_pool_fwd_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_block_mean_pool_bwd(const void* d_out, void* dx, int B, int Hkv, int T, int D,
+                                       int block_size, int dtype, void* stream) {
+  NSA_CHECK_ARG(block_size > 0 && D > 0, "bad block_size/D");
+  const int n_blk = T / block_size;
+  const size_t n = (size_t)B * Hkv * T * D;
+  if (n == 0) return NSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == NSA_DTYPE_BF16)
+    mean_pool_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, T, D, block_size, n_blk, n);
+  else
+    mean_pool_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const float*)d_out, (float*)dx, T, D, block_size, n_blk, n);
+  NSA_LAUNCH_OK("mean_pool_bwd_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_block_compress_fwd(const void* x, const float* intra_pos, const float* pool_logits,
+                                      const float* proj_w, void* out, int B, int Hkv, int T, int D,
+                                      int block_size, int dtype, void* stream) {
+  NSA_CHECK_ARG(block_size > 0 && D > 0 && D <= 1024, "bad block_size/D");
+  const int n_blk = T / block_size;
+  const size_t ctas = (size_t)B * Hkv * n_blk;
+  if (ctas == 0) return NSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t sm = (size_t)(block_size + D) * sizeof(float);
+  if (dtype == NSA_DTYPE_BF16)
+    compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D, block_size, n_blk);
+  else
+    compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)out, (float*)nullptr, T, D, block_size, n_blk);
+  NSA_LAUNCH_OK("compress_fwd_kernel");
+  return NSA_OK;
+}
+
+extern "C" size_t nsa_block_compress_bwd_workspace_bytes(int B, int Hkv, int T, int D, int block_size) {
+  const size_t rows = (size_t)B * Hkv * (block_size > 0 ? T / block_size : 0);
+  // pooled[rows,D] + d_pooled[rows,D] + sum_dpooled[D] + d_w[block_size]
+  return align_up((2 * rows * D + D + block_size) * sizeof(float), 256);
+}
+
+extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, const float* pool_logits,
+                                      const float* proj_w, const void* d_out, void* dx,
+                                      float* d_intra_pos, float* d_pool_logits, float* d_proj_w,
+                                      int B, int Hkv, int T, int D, int block_size, int dtype,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+  NSA_CHECK_ARG(block_size > 0 && D > 0 && D <= 1024, "bad block_size/D");
+  const int n_blk = T / block_size;
+  const size_t rows = (size_t)B * Hkv * n_blk;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (workspace_bytes < nsa_block_compress_bwd_workspace_bytes(B, Hkv, T, D, block_size) || !workspace) {
+    set_error("compress bwd workspace too small");
+    return NSA_ERR_WORKSPACE;
+  }
+  float* pooled = (float*)workspace;
+  float* d_pooled = pooled + rows * D;
+  float* sum_dp = d_pooled + rows * D;
+  float* d_w = sum_dp + D;
+  NSA_CUDA_OK(cudaMemsetAsync(sum_dp, 0, (size_t)(D + block_size) * sizeof(float), st));
+  const size_t sm_f = (size_t)(block_size + D) * sizeof(float);
+  const size_t sm_b = (size_t)(block_size + D + 32) * sizeof(float);
+  const size_t tail = (size_t)(T - n_blk * block_size) * D * B * Hkv;
+  if (rows > 0) {
+    if (dtype == NSA_DTYPE_BF16) {
+      compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk);
+      compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk);
+      compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D);
+    } else {
+      compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)nullptr, pooled, T, D, block_size, n_blk);
+      compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (const float*)d_out, (float*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk);
+      compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const float*)d_out, pooled, d_proj_w, rows, D);
+    }
+    NSA_LAUNCH_OK("compress_bwd kernels");
+  } else {
+    NSA_CUDA_OK(cudaMemsetAsync(d_proj_w, 0, (size_t)D * D * sizeof(float), st));
+  }
+  if (tail > 0) {
+    if (dtype == NSA_DTYPE_BF16)
+      zero_tail_kernel<<<blocks_for(tail, 256), 256, 0, st>>>((__nv_bfloat16*)dx, T, D, n_blk * block_size, (size_t)B * Hkv);
+    else
+      zero_tail_kernel<<<blocks_for(tail, 256), 256, 0, st>>>((float*)dx, T, D, n_blk * block_size, (size_t)B * Hkv);
+    NSA_LAUNCH_OK("zero_tail_kernel");
+  }
+  compress_bwd_final_kernel<<<1, 256, block_size * sizeof(float), st>>>(pool_logits, sum_dp, d_w, d_intra_pos, d_pool_logits, D, block_size);
+  NSA_LAUNCH_OK("compress_bwd_final_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp,
+                               int32_t* block_idx, float* importance_out, const NsaDims* dims,
+                               int n_blk, int block_size, int n_sel, void* stream) {
+  NSA_CHECK_ARG(dims && q && k_cmp && lse_cmp && block_idx, "null argument");
+  NSA_CHECK_ARG(dims->Hkv > 0 && dims->Hq % dims->Hkv == 0, "Hq must be a multiple of Hkv");
+  NSA_CHECK_ARG(block_size > 0 && n_sel > 0 && n_blk >= 0, "bad block_size/n_sel/n_blk");
+  const int D = dims->D;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t units = (size_t)dims->B * dims->Hkv * dims->T;
+  if (units == 0) return NSA_OK;
+  const size_t sm = (size_t)4 * (D + n_blk) * sizeof(float);
+  NSA_CHECK_ARG(sm <= 200 * 1024, "n_blk %d too large for the scoring kernel", n_blk);
+  const float scale = 1.0f / sqrtf((float)D);
+  const unsigned grid = blocks_for(units, 4);
+#define NSA_TOPN(TT, DD)                                                                        \
+  do {                                                                                          \
+    if (sm > 48 * 1024)                                                                         \
+      NSA_CUDA_OK(cudaFuncSetAttribute(topn_kernel<TT, DD>,                                     \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));  \
+    topn_kernel<TT, DD><<<grid, 128, sm, st>>>((const TT*)q, (const TT*)k_cmp, lse_cmp,         \
+        block_idx, importance_out, dims->B, dims->Hq, dims->Hkv, dims->T, n_blk, block_size,    \
+        n_sel, scale);                                                                          \
+  } while (0)
+  if (dims->dtype == NSA_DTYPE_BF16) {
+    switch (D) {
+      case 16: NSA_TOPN(__nv_bfloat16, 16); break;
+      case 32: NSA_TOPN(__nv_bfloat16, 32); break;
+      case 64: NSA_TOPN(__nv_bfloat16, 64); break;
+      case 128: NSA_TOPN(__nv_bfloat16, 128); break;
+      default: set_error("head dim %d unsupported", D); return NSA_ERR_UNSUPPORTED;
+    }
+  } else {
+    switch (D) {
+      case 16: NSA_TOPN(float, 16); break;
+      case 32: NSA_TOPN(float, 32); break;
+      case 64: NSA_TOPN(float, 64); break;
+      case 128: NSA_TOPN(float, 128); break;
+      default: set_error("head dim %d unsupported", D); return NSA_ERR_UNSUPPORTED;
+    }
+  }
+#undef NSA_TOPN
+  NSA_LAUNCH_OK("topn_kernel");
+  return NSA_OK;
+}
+
+extern "C" size_t nsa_csr_workspace_bytes(int B, int Hkv, int T, int S, int block_size) {
+  (void)S;
+  const size_t n_blk = block_size > 0 ? T / block_size : 0;
+  const size_t rows = (size_t)B * Hkv * n_blk;
+  const size_t words = (T + 31) / 32;
+  return align_up(rows * words * 4, 256) + 2 * align_up(rows * 4, 256);
+}
+
+extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int Hkv, int T, int S,
+                                            int block_size, int32_t* q_of_block,
+                                            int32_t* block_offsets, int32_t* pair_bh, void* workspace,
+                                            size_t workspace_bytes, void* stream) {
+  NSA_CHECK_ARG(block_size > 0 && B >= 0 && Hkv >= 0 && T >= 0 && S >= 0, "bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n_blk = T / block_size;
+  const size_t rows = (size_t)B * Hkv * n_blk;
+  const int words = (T + 31) / 32;
+  if ((size_t)B * Hkv == 0) return NSA_OK;
+  if (rows == 0) {
+    NSA_CUDA_OK(cudaMemsetAsync(block_offsets, 0, (size_t)B * Hkv * sizeof(int32_t), st));
+    return NSA_OK;
+  }
+  if (!workspace || workspace_bytes < nsa_csr_workspace_bytes(B, Hkv, T, S, block_size)) {
+    set_error("csr workspace too small");
+    return NSA_ERR_WORKSPACE;
+  }
+  uint32_t* bitmap = (uint32_t*)workspace;
+  int32_t* counts = (int32_t*)((char*)workspace + align_up(rows * words * 4, 256));
+  int32_t* row_start = (int32_t*)((char*)counts + align_up(rows * 4, 256));
+  NSA_CUDA_OK(cudaMemsetAsync(bitmap, 0, rows * words * 4, st));
+  const size_t n_entries = (size_t)B * Hkv * T * S;
+  if (n_entries)
+    csr_mark_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(block_idx, bitmap, T, S, block_size, n_blk, words, n_entries);
+  csr_count_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, counts, words, rows);
+  csr_scan_kernel<<<1, 1024, 0, st>>>(counts, block_offsets, row_start, n_blk, rows);
+  csr_fill_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, row_start, q_of_block, pair_bh, n_blk, words, rows);
+  NSA_LAUNCH_OK("csr kernels");
+  return NSA_OK;
+}
+
+extern "C" int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const void* o_win,
+                                    const void* gate_logits, void* out, const NsaDims* dims,
+                                    void* stream) {
+  NSA_CHECK_ARG(dims, "null dims");
+  const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
+  if (rows == 0) return NSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dims->dtype == NSA_DTYPE_BF16)
+    gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (__nv_bfloat16*)out, rows, dims->D);
+  else
+    gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (float*)out, rows, dims->D);
+  NSA_LAUNCH_OK("gate_fwd_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_gate_combine_bwd(const void* o_cmp, const void* o_slc, const void* o_win,
+                                    const void* gate_logits, const void* d_out, void* do_cmp,
+                                    void* do_slc, void* do_win, void* d_gate_logits,
+                                    const NsaDims* dims, void* stream) {
+  NSA_CHECK_ARG(dims, "null dims");
+  const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
+  if (rows == 0) return NSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dims->dtype == NSA_DTYPE_BF16)
+    gate_bwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)do_cmp, (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, (__nv_bfloat16*)d_gate_logits, rows, dims->D);
+  else
+    gate_bwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (const float*)d_out, (float*)do_cmp, (float*)do_slc, (float*)do_win, (float*)d_gate_logits, rows, dims->D);
+  NSA_LAUNCH_OK("gate_bwd_kernel");
+  return NSA_OK;
+}

@@ -1,0 +1,90 @@
+// Shared host/device helpers of libnsa_b200: error reporting, dtype loads, launch checks.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/nsa_b200.h"
+
+namespace nsa {
+
+void set_error(const char* fmt, ...);
+
+#define NSA_CHECK_ARG(cond, ...)            \
+  do {                                      \
+    if (!(cond)) {                          \
+      nsa::set_error(__VA_ARGS__);          \
+      return NSA_ERR_BAD_ARG;               \
+    }                                       \
+  } while (0)
+
+#define NSA_CUDA_OK(expr)                                                        \
+  do {                                                                           \
+    cudaError_t _e = (expr);                                                     \
+    if (_e != cudaSuccess) {                                                     \
+      nsa::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),     \
+                     __FILE__, __LINE__);                                        \
+      return NSA_ERR_CUDA;                                                       \
+    }                                                                            \
+  } while (0)
+
+#define NSA_LAUNCH_OK(name)                                                      \
+  do {                                                                           \
+    cudaError_t _e = cudaGetLastError();                                         \
+    if (_e != cudaSuccess) {                                                     \
+      nsa::set_error("launch of %s failed: %s", name, cudaGetErrorString(_e));   \
+      return NSA_ERR_CUDA;                                                       \
+    }                                                                            \
+  } while (0)
+
+constexpr float kLseEmpty = -1.0e9f;  // nsa_selection_kernel.py:134,171
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+  return __float2bfloat16_rn(x);
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+
+// error word raised by kernels whose bounded waits run out; defined in api.cu
+int* device_status_ptr();
+
+// ---- SIMT kernel family (simt.cu) ---------------------------------------------------------
+struct AttnArgs {
+  const void* q; const void* k; const void* v; const int32_t* block_idx;
+  void* o; float* lse;
+  const void* d_o; void* dq; float* dk_acc; float* dv_acc;   // backward
+  int B, Hq, Hkv, T, Lk, D, S;
+  int kind;          // 0 window, 1 compress, 2 selection
+  int window, block_size;
+  float scale;
+};
+int simt_attn_fwd(const AttnArgs& a, int dtype, cudaStream_t st);
+int simt_attn_bwd(const AttnArgs& a, int dtype, cudaStream_t st);
+int cast_f32_to(const float* src, void* dst, size_t n, int dtype, cudaStream_t st);
+
+// ---- tcgen05 kernel family (tc.cu) ----------------------------------------------------------
+bool tc_shape_ok(const NsaDims& d, int block_size);
+int tc_attn_fwd(const AttnArgs& a, cudaStream_t st);
+size_t tc_attn_bwd_workspace(const AttnArgs& a);
+int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
+
+}  // namespace nsa

@@ -1,0 +1,415 @@
+"""Host side of the NSA attention path: the reference's operator interface on top of the
+C-ABI library.
+
+Names, argument meaning and error behaviour follow the reference modules they replace:
+  selection_forward_triton, selection_forward_reference   nsa_selection_kernel.py:55-213
+  selection_backward_triton, SelectionAttnTriton,
+  selection_attn_triton                                    nsa_selection_backward.py:156-369
+  build_block_to_query_csr                                 nsa_fsa.py:14-64
+  _RangeAttn, window_attn_triton, compression_attn_triton,
+  block_mean_pool, nsa_fused_forward                       nsa_fused_kernel.py:521-573
+`nsa_attention` is the one addition: the whole op (pooling, compression attention, block
+scoring + top-n, selection, window, gate) behind one autograd.Function.
+"""
+import torch
+
+from . import _lib as L
+
+MODE_WINDOW = L.MODE_WINDOW
+MODE_COMPRESS = L.MODE_COMPRESS
+
+_impl = "auto"
+
+
+def set_impl(name: str):
+    """Choose the kernel family: 'auto' (tcgen05 where the shape fits), 'simt' or 'tc'."""
+    global _impl
+    assert name in L.IMPL
+    _impl = name
+
+
+def get_impl() -> str:
+    return _impl
+
+
+def tc_supported(B, Hq, Hkv, T, D, dtype, block_size=64) -> bool:
+    code = L.DTYPE_BF16 if dtype == torch.bfloat16 else L.DTYPE_F32
+    return bool(L.lib().nsa_tc_supported(L.dims(B, Hq, Hkv, T, D, code), block_size))
+
+
+def _check_qkv(q, k, v):
+    B, Hq, T, D = q.shape
+    assert k.shape == v.shape and k.shape[0] == B and k.shape[3] == D
+    assert Hq % k.shape[1] == 0, "GQA needs Hq divisible by Hkv"
+    assert D in (16, 32, 64, 128), "head dim must be a power of two <= 128"
+    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert q.dtype == k.dtype == v.dtype
+    return B, Hq, k.shape[1], T, D
+
+
+# ---------------------------------------------------------------------------------------
+# raw launch wrappers
+# ---------------------------------------------------------------------------------------
+def range_attn_forward(q, k, v, mode, window, block_size):
+    """o, lse of the window (mode 0) or compression (mode 1) branch."""
+    B, Hq, Hkv, T, D = _check_qkv(q, k, v)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, T, device=q.device, dtype=torch.float32)
+    d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
+    L.check(L.lib().nsa_range_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse), d,
+                                       k.shape[2], mode, int(window), int(block_size),
+                                       L.IMPL[_impl], L.stream()))
+    return o, lse
+
+
+def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size):
+    B, Hq, Hkv, T, D = _check_qkv(q, k, v)
+    q, k, v, o, do = (t.contiguous() for t in (q, k, v, o, do))
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
+    nws = L.lib().nsa_range_attn_bwd_workspace_bytes(d, k.shape[2], L.IMPL[_impl])
+    ws = L.workspace(nws, q.device)
+    L.check(L.lib().nsa_range_attn_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse),
+                                       L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, k.shape[2],
+                                       mode, int(window), int(block_size), L.ptr(ws), nws,
+                                       L.IMPL[_impl], L.stream()))
+    return dq, dk, dv
+
+
+def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False):
+    """nsa_selection_kernel.py:175-213.  q [B,Hq,T,D], k/v [B,Hkv,T,D], block_idx [B,Hkv,T,S]."""
+    B, Hq, Hkv, T, D = _check_qkv(q, k, v)
+    S = block_idx.shape[-1]
+    assert block_idx.shape[:3] == (B, Hkv, T)
+    assert block_size >= 16, "block_size must be >= 16 (tl.dot inner dim)"
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    idx = block_idx.to(torch.int32).contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, T, device=q.device, dtype=torch.float32)
+    d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
+    nws = L.lib().nsa_selection_fwd_workspace_bytes(d, S, block_size, L.IMPL[_impl])
+    ws = L.workspace(nws, q.device)
+    L.check(L.lib().nsa_selection_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
+                                      L.ptr(lse), d, S, int(block_size), L.ptr(ws), nws,
+                                      L.IMPL[_impl], L.stream()))
+    return (o, lse) if return_lse else o
+
+
+def _selection_backward(q, k, v, block_idx, block_size, do, o, lse):
+    B, Hq, Hkv, T, D = _check_qkv(q, k, v)
+    S = block_idx.shape[-1]
+    assert block_size >= 16
+    q, k, v, o, do = (t.contiguous() for t in (q, k, v, o, do))
+    idx = block_idx.to(torch.int32).contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
+    nws = L.lib().nsa_selection_bwd_workspace_bytes(d, S, block_size, L.IMPL[_impl])
+    ws = L.workspace(nws, q.device)
+    L.check(L.lib().nsa_selection_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
+                                      L.ptr(lse), L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, S,
+                                      int(block_size), L.ptr(ws), nws, L.IMPL[_impl], L.stream()))
+    return dq, dk, dv
+
+
+def selection_backward_triton(q, k, v, block_idx, block_size, do, o):
+    """nsa_selection_backward.py:156-189: dq, dk, dv from (q,k,v,block_idx,dO,O); the softmax
+    statistics are recomputed by a forward pass because this signature carries no LSE."""
+    _, lse = selection_forward_triton(q, k, v, block_idx, block_size, return_lse=True)
+    return _selection_backward(q, k, v, block_idx, block_size, do, o, lse)
+
+
+@torch.no_grad()
+def build_block_to_query_csr(block_idx, block_size):
+    """nsa_fsa.py:14-64: (q_of_block [P], block_offsets [B,Hkv,n_blk+1], pair_bh [P]), int32."""
+    B, Hkv, T, S = block_idx.shape
+    idx = block_idx.to(torch.int32).contiguous()
+    n_blk = T // block_size
+    dev = idx.device
+    cap = max(B * Hkv * T * S, 1)
+    q_of_block = torch.empty(cap, dtype=torch.int32, device=dev)
+    pair_bh = torch.empty(cap, dtype=torch.int32, device=dev)
+    offsets = torch.zeros(B, Hkv, n_blk + 1, dtype=torch.int32, device=dev)
+    nws = L.lib().nsa_csr_workspace_bytes(B, Hkv, T, S, block_size)
+    ws = L.workspace(nws, dev)
+    L.check(L.lib().nsa_build_block_to_query_csr(L.ptr(idx), B, Hkv, T, S, int(block_size),
+                                                 L.ptr(q_of_block), L.ptr(offsets), L.ptr(pair_bh),
+                                                 L.ptr(ws), nws, L.stream()))
+    P = int(offsets.view(-1)[-1].item()) if offsets.numel() else 0
+    return q_of_block[:P], offsets, pair_bh[:P]
+
+
+def _pool_dims(x, block_size):
+    B, H, T, D = x.shape
+    return B, H, T, D, T // block_size
+
+
+def _mean_pool_fwd(x, block_size):
+    B, H, T, D, n_blk = _pool_dims(x, block_size)
+    x = x.contiguous()
+    out = torch.empty(B, H, n_blk, D, device=x.device, dtype=x.dtype)
+    L.check(L.lib().nsa_block_mean_pool_fwd(L.ptr(x), L.ptr(out), B, H, T, D, int(block_size),
+                                            L.dtype_code(x), L.stream()))
+    return out
+
+
+def _mean_pool_bwd(d_out, T, block_size):
+    B, H, n_blk, D = d_out.shape
+    d_out = d_out.contiguous()
+    dx = torch.empty(B, H, T, D, device=d_out.device, dtype=d_out.dtype)
+    L.check(L.lib().nsa_block_mean_pool_bwd(L.ptr(d_out), L.ptr(dx), B, H, T, D, int(block_size),
+                                            L.dtype_code(d_out), L.stream()))
+    return dx
+
+
+def _compress_fwd(x, intra, logits, proj, block_size):
+    B, H, T, D, n_blk = _pool_dims(x, block_size)
+    x = x.contiguous()
+    out = torch.empty(B, H, n_blk, D, device=x.device, dtype=x.dtype)
+    L.check(L.lib().nsa_block_compress_fwd(L.ptr(x), L.ptr(intra), L.ptr(logits), L.ptr(proj),
+                                           L.ptr(out), B, H, T, D, int(block_size),
+                                           L.dtype_code(x), L.stream()))
+    return out
+
+
+def _compress_bwd(x, intra, logits, proj, d_out, block_size):
+    B, H, T, D, n_blk = _pool_dims(x, block_size)
+    x, d_out = x.contiguous(), d_out.contiguous()
+    dx = torch.empty_like(x)
+    d_intra, d_logits, d_proj = (torch.empty_like(t) for t in (intra, logits, proj))
+    nws = L.lib().nsa_block_compress_bwd_workspace_bytes(B, H, T, D, int(block_size))
+    ws = L.workspace(nws, x.device)
+    L.check(L.lib().nsa_block_compress_bwd(L.ptr(x), L.ptr(intra), L.ptr(logits), L.ptr(proj),
+                                           L.ptr(d_out), L.ptr(dx), L.ptr(d_intra), L.ptr(d_logits),
+                                           L.ptr(d_proj), B, H, T, D, int(block_size),
+                                           L.dtype_code(x), L.ptr(ws), nws, L.stream()))
+    return dx, d_intra, d_logits, d_proj
+
+
+@torch.no_grad()
+def topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, return_importance=False):
+    """Block scoring + top-n (nsa_model.py:343-355): block_idx [B,Hkv,T,n_sel] int32, ordered by
+    (importance descending, index ascending), -1 where fewer than n_sel blocks are causally
+    valid.  lse_cmp is the LSE of the compression branch for the same q, k_cmp."""
+    B, Hq, T, D = q.shape
+    Hkv, n_blk = k_cmp.shape[1], k_cmp.shape[2]
+    q, k_cmp, lse_cmp = q.contiguous(), k_cmp.contiguous(), lse_cmp.contiguous()
+    idx = torch.empty(B, Hkv, T, n_sel, device=q.device, dtype=torch.int32)
+    imp = torch.empty(B, Hkv, T, n_blk, device=q.device, dtype=torch.float32) if return_importance else None
+    d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
+    L.check(L.lib().nsa_topn_blocks(L.ptr(q), L.ptr(k_cmp), L.ptr(lse_cmp), L.ptr(idx), L.ptr(imp),
+                                    d, n_blk, int(block_size), int(n_sel), L.stream()))
+    return (idx, imp) if return_importance else idx
+
+
+def _gate_fwd(o_cmp, o_slc, o_win, gate):
+    B, Hq, T, D = o_cmp.shape
+    out = torch.empty_like(o_cmp)
+    d = L.dims(B, Hq, 1, T, D, L.dtype_code(o_cmp))
+    L.check(L.lib().nsa_gate_combine_fwd(L.ptr(o_cmp), L.ptr(o_slc), L.ptr(o_win), L.ptr(gate),
+                                         L.ptr(out), d, L.stream()))
+    return out
+
+
+def _gate_bwd(o_cmp, o_slc, o_win, gate, d_out):
+    B, Hq, T, D = o_cmp.shape
+    d_out = d_out.contiguous()
+    dc, ds, dw = (torch.empty_like(o_cmp) for _ in range(3))
+    dg = torch.empty_like(gate)
+    d = L.dims(B, Hq, 1, T, D, L.dtype_code(o_cmp))
+    L.check(L.lib().nsa_gate_combine_bwd(L.ptr(o_cmp), L.ptr(o_slc), L.ptr(o_win), L.ptr(gate),
+                                         L.ptr(d_out), L.ptr(dc), L.ptr(ds), L.ptr(dw), L.ptr(dg),
+                                         d, L.stream()))
+    return dc, ds, dw, dg
+
+
+# ---------------------------------------------------------------------------------------
+# autograd boundary (same classes and callables as the reference)
+# ---------------------------------------------------------------------------------------
+class _RangeAttn(torch.autograd.Function):
+    """nsa_fused_kernel.py:521-534; additionally keeps the LSE so backward is one pass."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, mode, window, block_size):
+        o, lse = range_attn_forward(q, k, v, mode, window, block_size)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.mode, ctx.window, ctx.block_size = mode, window, block_size
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = range_attn_backward(q, k, v, o, lse, do, ctx.mode, ctx.window, ctx.block_size)
+        return dq, dk, dv, None, None, None
+
+
+def window_attn_triton(q, k, v, window):
+    return _RangeAttn.apply(q, k, v, MODE_WINDOW, window, 0)
+
+
+def compression_attn_triton(q, k_cmp, v_cmp, block_size):
+    return _RangeAttn.apply(q, k_cmp, v_cmp, MODE_COMPRESS, 0, block_size)
+
+
+class SelectionAttnTriton(torch.autograd.Function):
+    """nsa_selection_backward.py:337-365: block_idx and block_size get no gradient."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, block_idx, block_size):
+        o, lse = selection_forward_triton(q, k, v, block_idx, block_size, return_lse=True)
+        ctx.save_for_backward(q, k, v, block_idx, o, lse)
+        ctx.block_size = block_size
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, block_idx, o, lse = ctx.saved_tensors
+        dq, dk, dv = _selection_backward(q, k, v, block_idx, ctx.block_size, do, o, lse)
+        return dq, dk, dv, None, None
+
+
+def selection_attn_triton(q, k, v, block_idx, block_size):
+    return SelectionAttnTriton.apply(q, k, v, block_idx, block_size)
+
+
+class _MeanPool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, block_size):
+        ctx.T, ctx.block_size = x.shape[2], block_size
+        return _mean_pool_fwd(x, block_size)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        return _mean_pool_bwd(d_out, ctx.T, ctx.block_size), None
+
+
+def block_mean_pool(x, block_size):
+    """nsa_fused_kernel.py:549-554: [B,Hkv,T,D] -> [B,Hkv,n_blk,D]."""
+    return _MeanPool.apply(x, block_size)
+
+
+class _BlockCompress(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, intra_pos, pool_logits, proj_weight, block_size):
+        intra, logits, proj = (t.detach().float().contiguous() for t in (intra_pos, pool_logits, proj_weight))
+        ctx.save_for_backward(x, intra, logits, proj)
+        ctx.block_size = block_size
+        ctx.param_dtypes = (intra_pos.dtype, pool_logits.dtype, proj_weight.dtype)
+        return _compress_fwd(x, intra, logits, proj, block_size)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        x, intra, logits, proj = ctx.saved_tensors
+        dx, di, dl, dp = _compress_bwd(x, intra, logits, proj, d_out, ctx.block_size)
+        a, b, c = ctx.param_dtypes
+        return dx, di.to(a), dl.to(b), dp.to(c), None
+
+
+def block_compress(x, intra_pos, pool_logits, proj_weight, block_size):
+    """BlockCompressor.forward (nsa_model.py:118-123) on the block view of x [B,Hkv,T,D]."""
+    return _BlockCompress.apply(x, intra_pos, pool_logits, proj_weight, block_size)
+
+
+class _GateCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o_cmp, o_slc, o_win, gate_logits):
+        o_cmp, o_slc, o_win = (t.contiguous() for t in (o_cmp, o_slc, o_win))
+        gate = gate_logits.to(o_cmp.dtype).contiguous()
+        ctx.save_for_backward(o_cmp, o_slc, o_win, gate)
+        ctx.gate_dtype = gate_logits.dtype
+        return _gate_fwd(o_cmp, o_slc, o_win, gate)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        o_cmp, o_slc, o_win, gate = ctx.saved_tensors
+        dc, ds, dw, dg = _gate_bwd(o_cmp, o_slc, o_win, gate, d_out)
+        return dc, ds, dw, dg.to(ctx.gate_dtype)
+
+
+def gate_combine(o_cmp, o_slc, o_win, gate_logits):
+    """sigmoid(gate)[...,0]*o_cmp + [...,1]*o_slc + [...,2]*o_win (nsa_model.py:366-368)."""
+    return _GateCombine.apply(o_cmp, o_slc, o_win, gate_logits)
+
+
+def nsa_fused_forward(q, kc, vc, ks, vs, kw, vw, gate_logits, block_idx, block_size, window):
+    """nsa_fused_kernel.py:560-573: the three branches with a given block_idx, mean pooling."""
+    k_cmp = block_mean_pool(kc, block_size)
+    v_cmp = block_mean_pool(vc, block_size)
+    o_cmp = compression_attn_triton(q, k_cmp, v_cmp, block_size)
+    o_slc = selection_attn_triton(q, ks, vs, block_idx, block_size)
+    o_win = window_attn_triton(q, kw, vw, window)
+    return gate_combine(o_cmp, o_slc, o_win, gate_logits)
+
+
+class _NSAAttention(torch.autograd.Function):
+    """The whole op in one node: pooling -> compression attention (+LSE) -> block scoring and
+    top-n -> selection attention -> window attention -> gate combine.  Saves q once."""
+
+    @staticmethod
+    def forward(ctx, q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
+                block_idx, k_intra, k_logits, k_proj, v_intra, v_logits, v_proj):
+        learned = k_intra is not None
+        if learned:
+            cp = [t.detach().float().contiguous() for t in
+                  (k_intra, k_logits, k_proj, v_intra, v_logits, v_proj)]
+            k_cmp = _compress_fwd(kc, cp[0], cp[1], cp[2], block_size)
+            v_cmp = _compress_fwd(vc, cp[3], cp[4], cp[5], block_size)
+        else:
+            cp = []
+            k_cmp = _mean_pool_fwd(kc, block_size)
+            v_cmp = _mean_pool_fwd(vc, block_size)
+        o_cmp, lse_cmp = range_attn_forward(q, k_cmp, v_cmp, MODE_COMPRESS, 0, block_size)
+        if block_idx is None:
+            block_idx = topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel)
+        else:
+            block_idx = block_idx.to(torch.int32).contiguous()
+        o_slc, lse_slc = selection_forward_triton(q, ks, vs, block_idx, block_size, return_lse=True)
+        o_win, lse_win = range_attn_forward(q, kw, vw, MODE_WINDOW, window, 0)
+        gate = gate_logits.to(q.dtype).contiguous()
+        out = _gate_fwd(o_cmp, o_slc, o_win, gate)
+        ctx.save_for_backward(q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o_cmp, o_slc, o_win,
+                              lse_cmp, lse_slc, lse_win, block_idx, *cp)
+        ctx.cfg = (block_size, window, learned, gate_logits.dtype,
+                   tuple(t.dtype for t in (k_intra, k_logits, k_proj, v_intra, v_logits, v_proj))
+                   if learned else None)
+        ctx.mark_non_differentiable(block_idx)
+        return out, block_idx
+
+    @staticmethod
+    def backward(ctx, d_out, _d_idx):
+        (q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o_cmp, o_slc, o_win,
+         lse_cmp, lse_slc, lse_win, block_idx, *cp) = ctx.saved_tensors
+        block_size, window, learned, gate_dtype, pdt = ctx.cfg
+        T = q.shape[2]
+        do_cmp, do_slc, do_win, d_gate = _gate_bwd(o_cmp, o_slc, o_win, gate, d_out)
+        dq, dk_cmp, dv_cmp = range_attn_backward(q, k_cmp, v_cmp, o_cmp, lse_cmp, do_cmp,
+                                                 MODE_COMPRESS, 0, block_size)
+        dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, do_slc, o_slc, lse_slc)
+        dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, do_win, MODE_WINDOW, window, 0)
+        dq = dq.float().add_(dq2).add_(dq3).to(q.dtype) if q.dtype != torch.float32 else dq.add_(dq2).add_(dq3)
+        pgrads = [None] * 6
+        if learned:
+            dkc, a, b, c = _compress_bwd(kc, cp[0], cp[1], cp[2], dk_cmp, block_size)
+            dvc, d, e, f = _compress_bwd(vc, cp[3], cp[4], cp[5], dv_cmp, block_size)
+            pgrads = [g.to(t) for g, t in zip((a, b, c, d, e, f), pdt)]
+        else:
+            dkc = _mean_pool_bwd(dk_cmp, T, block_size)
+            dvc = _mean_pool_bwd(dv_cmp, T, block_size)
+        return (dq, dkc, dvc, dks, dvs, dkw, dvw, d_gate.to(gate_dtype), None, None, None, None,
+                *pgrads)
+
+
+def nsa_attention(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
+                  block_idx=None, compressor=None, return_block_idx=False):
+    """Full NSA attention (pre out_proj) as one differentiable op.
+
+    q [B,Hq,T,D]; kc..vw [B,Hkv,T,D]; gate_logits [B,Hq,T,3].  `compressor` is None for mean
+    pooling or a dict k_intra,k_logits,k_proj,v_intra,v_logits,v_proj holding the parameters
+    of the two BlockCompressor modules (nsa_model.py:180-181).  With block_idx=None the blocks
+    are picked by the scorer (nsa_model.py:343-355 semantics, deterministic tie order)."""
+    cp = [None] * 6
+    if compressor is not None:
+        cp = [compressor[n] for n in ("k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj")]
+    out, idx = _NSAAttention.apply(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel,
+                                   window, block_idx, *cp)
+    return (out, idx) if return_block_idx else out

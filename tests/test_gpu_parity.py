@@ -1,0 +1,340 @@
+"""CUDA kernels (through the C-ABI) against the oracle on the same seeded inputs."""
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from tests.util import (REF_CONFIGS, TC_CONFIGS, cfg_id, check, dev, err, load_golden,
+                        make_inputs, pkg, window_for)
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _impls_for(c, dtype):
+    nsa = pkg()
+    impls = ["simt"]
+    if dtype == torch.bfloat16 and nsa.tc_supported(c["B"], c["Hq"], c["Hkv"], c["T"], c["D"],
+                                                    dtype, c["block_size"]):
+        impls.append("tc")
+    return impls
+
+
+@pytest.fixture(autouse=True)
+def _reset_impl():
+    yield
+    pkg().set_impl("auto")
+
+
+ALL = [(c, dt) for c in REF_CONFIGS for dt in DTYPES] + [(c, torch.bfloat16) for c in TC_CONFIGS]
+IDS = [cfg_id(c) + "-" + str(dt).split(".")[-1] for c, dt in ALL]
+
+
+@pytest.mark.parametrize("c,dtype", ALL, ids=IDS)
+def test_branches_forward_backward(c, dtype):
+    """Each branch alone: o, lse, dq, dk, dv (test_kernel.py, test_kernel_backward.py and the
+    range half of test_kernel_fused.py)."""
+    nsa = pkg()
+    t = make_inputs(c, dtype)
+    bs, W, T = c["block_size"], window_for(c), c["T"]
+    k_pool = O.ref_block_mean_pool(t["kc"], bs).to(dtype).float()
+    v_pool = O.ref_block_mean_pool(t["vc"], bs).to(dtype).float()
+    n_blk = T // bs
+    branches = {
+        "sel": (t["ks"], t["vs"], O.selection_keep_fn(t["block_idx"], T, bs)),
+        "win": (t["kw"], t["vw"], O.window_keep_fn(T, W)),
+        "cmp": (k_pool, v_pool, O.compress_keep_fn(n_blk, bs)),
+    }
+    for impl in _impls_for(c, dtype):
+        nsa.set_impl(impl)
+        for name, (k, v, keep_fn) in branches.items():
+            o_ref, lse_ref = O.stream_attn_forward(t["q"], k, v, keep_fn)
+            q_d, k_d, v_d, do_d = (dev(x, dtype) for x in (t["q"], k, v, t["do"]))
+            idx_d = t["block_idx"].cuda()
+            if name == "sel":
+                o, lse = nsa.selection_forward_triton(q_d, k_d, v_d, idx_d, bs, return_lse=True)
+            else:
+                mode = nsa.MODE_WINDOW if name == "win" else nsa.MODE_COMPRESS
+                o, lse = nsa.range_attn_forward(q_d, k_d, v_d, mode, W, bs)
+            tag = f"{impl}/{name}"
+            check(o, o_ref, dtype, tag + " o")
+            empty = lse_ref == O.LSE_EMPTY
+            assert (lse.cpu()[empty] == O.LSE_EMPTY).all(), tag + " lse sentinel"
+            assert (o.float().cpu()[empty] == 0).all(), tag + " empty rows must be exactly 0"
+            lse_abs = (lse.cpu()[~empty] - lse_ref[~empty]).abs().max().item() if (~empty).any() else 0
+            assert lse_abs <= (1e-4 if dtype == torch.float32 else 2e-2), tag + f" lse {lse_abs}"
+            # backward consumes the kernel's own o and lse, as the autograd Functions do
+            dq_ref, dk_ref, dv_ref = O.stream_attn_backward(t["q"], k, v, o_ref, lse_ref, t["do"], keep_fn)
+            if name == "sel":
+                dq, dk, dv = nsa.ops._selection_backward(q_d, k_d, v_d, idx_d, bs, do_d, o, lse)
+            else:
+                dq, dk, dv = nsa.range_attn_backward(q_d, k_d, v_d, o, lse, do_d, mode, W, bs)
+            # reference bf16 gate for gradients is 1.2e-1 abs (test_kernel_backward.py:28,74)
+            check(dq, dq_ref, dtype, tag + " dq", abs32=4e-3)
+            check(dk, dk_ref, dtype, tag + " dk", abs32=4e-3)
+            check(dv, dv_ref, dtype, tag + " dv", abs32=4e-3)
+
+
+@pytest.mark.parametrize("c,dtype", ALL, ids=IDS)
+def test_fused_three_branch(c, dtype):
+    """nsa_fused_forward and all its input gradients (test_kernel_fused.py)."""
+    nsa = pkg()
+    t = make_inputs(c, dtype)
+    bs, W = c["block_size"], window_for(c)
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+    fwd = O.stream_nsa_forward(*(t[n] for n in names), bs, c["S"], W, block_idx=t["block_idx"])
+    g_ref = O.stream_nsa_backward(*(t[n] for n in names), bs, W, fwd, t["do"])
+    for impl in _impls_for(c, dtype):
+        nsa.set_impl(impl)
+        ins = [dev(t[n], dtype).requires_grad_(True) for n in names]
+        out = nsa.nsa_fused_forward(*ins, t["block_idx"].cuda(), bs, W)
+        out.backward(dev(t["do"], dtype))
+        check(out, fwd["out"], dtype, impl + " fused out", abs16=3e-2)   # test_kernel_fused.py:25
+        for n, x in zip(names, ins):
+            check(x.grad, g_ref[n], dtype, impl + " fused d" + n, abs32=3e-3, abs16=3e-2)
+
+
+@pytest.mark.parametrize("c,dtype", ALL, ids=IDS)
+def test_whole_op_with_scorer(c, dtype):
+    """nsa_attention: learned pooling + scoring/top-n inside the op.  The block choice is
+    compared on its own; the rest is compared with the oracle fed the kernel's choice."""
+    nsa = pkg()
+    t = make_inputs(c, dtype, seed=1, scale_qkv=True)
+    bs, W, S, D = c["block_size"], window_for(c), c["S"], c["D"]
+    g = torch.Generator().manual_seed(5)
+    comp = {}
+    for p in ("k", "v"):
+        comp[p + "_intra"] = 0.02 * torch.randn(bs, D, generator=g)
+        comp[p + "_logits"] = 0.5 * torch.randn(bs, generator=g)
+        comp[p + "_proj"] = torch.randn(D, D, generator=g) * D ** -0.5
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+    for impl in _impls_for(c, dtype):
+        nsa.set_impl(impl)
+        ins = [dev(t[n], dtype).requires_grad_(True) for n in names]
+        comp_d = {k: v.cuda().requires_grad_(True) for k, v in comp.items()}
+        out, idx = nsa.nsa_attention(*ins, bs, S, W, compressor=comp_d, return_block_idx=True)
+        out.backward(dev(t["do"], dtype))
+        # oracle uses summaries rounded to the op dtype, as the kernels see them
+        fwd = O.stream_nsa_forward(*(t[n] for n in names), bs, S, W, block_idx=idx.cpu(),
+                                   compressor=comp)
+        g_ref = O.stream_nsa_backward(*(t[n] for n in names), bs, W, fwd, t["do"], compressor=comp)
+        check(out, fwd["out"], dtype, impl + " op out", abs16=3e-2)
+        for n, x in zip(names, ins):
+            check(x.grad, g_ref[n], dtype, impl + " op d" + n, abs32=3e-3, abs16=3e-2)
+        for k in comp:
+            ma, rl = err(comp_d[k].grad, g_ref[k])
+            lim = 5e-3 if dtype == torch.float32 else 5e-2
+            assert rl <= lim or ma <= lim, f"{impl} d{k}: abs {ma:.3e} rel {rl:.3e}"
+
+
+@pytest.mark.parametrize("c", REF_CONFIGS + TC_CONFIGS[:3], ids=cfg_id)
+def test_topn_blocks(c):
+    """Scoring + top-n: exact against the kernel's own importance (value descending, index
+    ascending, -1 padding); set-equal to the oracle wherever the oracle's margin between the
+    last kept and first dropped block exceeds the accumulation noise."""
+    nsa = pkg()
+    for dtype in DTYPES:
+        t = make_inputs(c, dtype, seed=2, scale_qkv=False)
+        bs, S, T = c["block_size"], c["S"], c["T"]
+        n_blk = T // bs
+        k_cmp = O.ref_block_mean_pool(t["kc"], bs).to(dtype).float()
+        q_d, k_d = dev(t["q"], dtype), dev(k_cmp, dtype)
+        _, lse = nsa.range_attn_forward(q_d, k_d, k_d, nsa.MODE_COMPRESS, 0, bs)
+        idx, imp = nsa.topn_blocks(q_d, k_d, lse, bs, S, return_importance=True)
+        idx, imp = idx.cpu(), imp.cpu()
+        valid = O.compress_keep(0, T, n_blk, bs)
+        assert (idx == O.canonical_topn(imp, valid, S)).all(), "not the canonical order of own scores"
+        imp_ref, _ = O.stream_importance(t["q"], k_cmp, bs)
+        assert (imp - imp_ref).abs().max().item() <= (1e-5 if dtype == torch.float32 else 1e-3)
+        ref = O.canonical_topn(imp_ref, valid, S)
+        k_top = min(S, n_blk)
+        srt = torch.sort(imp_ref.masked_fill(~valid[None, None], -1.0), dim=-1, descending=True).values
+        margin = (srt[..., k_top - 1] - srt[..., k_top]) if n_blk > k_top else torch.ones(srt.shape[:-1])
+        n_valid = valid.sum(-1)[None, None].expand_as(margin)
+        clear = (margin > (1e-5 if dtype == torch.float32 else 1e-4)) | (n_valid <= k_top)
+        same = (idx.sort(-1).values == ref.sort(-1).values).all(-1)
+        assert same[clear].all(), "block set differs from the oracle on clear-margin rows"
+        assert clear.float().mean() > 0.3
+
+
+@pytest.mark.parametrize("c", REF_CONFIGS, ids=cfg_id)
+def test_csr_bit_exact(c):
+    nsa = pkg()
+    idx = O.make_block_idx(c["B"], c["Hkv"], c["T"], c["block_size"], c["S"], seed=4)
+    idx[0, 0, c["T"] // 2, 0] = (c["T"] // 2) // c["block_size"]     # a partially-future block
+    qob, off, pbh = nsa.build_block_to_query_csr(idx.cuda(), c["block_size"])
+    r_qob, r_off, r_pbh = O.build_block_to_query_csr(idx, c["block_size"])
+    assert (off.cpu().numpy() == r_off).all()
+    assert (qob.cpu().numpy() == r_qob).all()
+    assert (pbh.cpu().numpy() == r_pbh).all()
+
+
+@pytest.mark.parametrize("name", ["nsa_g2_d16.npz", "nsa_g3_d32.npz", "nsa_g4_d32.npz"])
+def test_golden_vectors_on_gpu(name):
+    """The reference's own outputs (fp32) straight against the kernels."""
+    nsa = pkg()
+    d = load_golden(name)
+    B, Hq, Hkv, D, T, bs, S, W = (int(x) for x in d["meta"])
+    f32 = torch.float32
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+    ins = [d[n].cuda().requires_grad_(True) for n in names]
+    out = nsa.nsa_fused_forward(*ins, d["block_idx"].cuda(), bs, W)
+    out.backward(d["do"].cuda())
+    check(out, d["fused_o"], f32, "golden fused out")
+    for n, x in zip(names, ins):
+        check(x.grad, d["fused_d" + n], f32, "golden fused d" + n, abs32=3e-3)
+    o = nsa.selection_forward_triton(d["q"].cuda(), d["ks"].cuda(), d["vs"].cuda(), d["block_idx"].cuda(), bs)
+    check(o, d["sel_o"], f32, "golden selection o")
+    dq, dk, dv = nsa.selection_backward_triton(d["q"].cuda(), d["ks"].cuda(), d["vs"].cuda(),
+                                               d["block_idx"].cuda(), bs, d["do"].cuda(), o)
+    check(dq, d["sel_dq"], f32, "golden sel dq", abs32=4e-3)
+    check(dk, d["sel_dk"], f32, "golden sel dk", abs32=4e-3)
+    check(dv, d["sel_dv"], f32, "golden sel dv", abs32=4e-3)
+    # learned compressor
+    x = d["kc"].cuda().requires_grad_(True)
+    ps = [d[k].cuda().requires_grad_(True) for k in ("comp_intra", "comp_logits", "comp_proj")]
+    y = nsa.block_compress(x, *ps, bs)
+    y.backward(d["comp_dy"].cuda())
+    check(y, d["comp_y"], f32, "golden compressor y", abs32=1e-4)
+    check(x.grad, d["comp_dx"], f32, "golden compressor dx", abs32=1e-4)
+    for p, k in zip(ps, ("comp_dintra", "comp_dlogits", "comp_dproj")):
+        check(p.grad, d[k], f32, "golden " + k, abs32=1e-3)
+    qob, off, pbh = nsa.build_block_to_query_csr(d["block_idx"].cuda(), bs)
+    assert (qob.cpu() == d["csr_q"]).all() and (off.cpu() == d["csr_off"]).all() and (pbh.cpu() == d["csr_bh"]).all()
+
+
+def test_module_against_reference_module():
+    """NSAAttentionB200 with the reference module's parameters reproduces its output and every
+    gradient (nsa_model.py:196-304), given the same block choice."""
+    nsa = pkg()
+    mod_cls = __import__("importlib").import_module("openbox-llm_b200.module").NSAAttentionB200
+    d = load_golden("nsa_module.npz")
+    m = mod_cls(d_model=64, n_q_heads=4, n_kv_heads=2, block_size=16, n_selected_blocks=3, window=24).cuda()
+    sd = {k[2:]: v for k, v in d.items() if k.startswith("p.")}
+    m.load_state_dict(sd)                                        # same keys as the reference
+    x = d["x"].cuda().requires_grad_(True)
+    # the reference's torch.topk call on CPU fixes the arbitrary picks of short rows
+    B, T, _ = d["x"].shape
+    split = lambda y, h: y.view(B, T, h, 16).transpose(1, 2)
+    q = split(d["x"] @ sd["q_proj.weight"].t(), 4)
+    kc = split(d["x"] @ sd["k_cmp.weight"].t(), 2)
+    k_cmp = O.ref_block_compressor(kc, sd["comp_k.intra_pos"], sd["comp_k.pool_logits"],
+                                   sd["comp_k.proj.weight"], 16)
+    idx = O.ref_topk_blocks(q, k_cmp, 16, 3)
+    y = m(x, block_idx=idx.cuda())
+    y.backward(d["dy"].cuda())
+    check(y, d["y"], torch.float32, "module y", abs32=5e-4)      # test_integration.py:29
+    check(x.grad, d["dx"], torch.float32, "module dx")
+    for n, p in m.named_parameters():
+        check(p.grad, d["g." + n], torch.float32, "module grad " + n)   # test_integration.py:30
+    # own scorer: rows with >= n_sel valid blocks pick the same set as the reference
+    _, own = nsa.nsa_attention(q.cuda(), *(split(d["x"] @ sd[k + ".weight"].t(), 2).cuda().contiguous()
+                                           for k in ("k_cmp", "v_cmp", "k_slc", "v_slc", "k_win", "v_win")),
+                               torch.zeros(B, 4, T, 3).cuda(), 16, 3, 24,
+                               compressor=dict(k_intra=sd["comp_k.intra_pos"].cuda(), k_logits=sd["comp_k.pool_logits"].cuda(),
+                                               k_proj=sd["comp_k.proj.weight"].cuda(), v_intra=sd["comp_v.intra_pos"].cuda(),
+                                               v_logits=sd["comp_v.pool_logits"].cuda(), v_proj=sd["comp_v.proj.weight"].cuda()),
+                               return_block_idx=True)
+    rows = torch.arange(T) >= 3 * 16 - 1
+    assert (own.cpu()[:, :, rows].sort(-1).values == idx[:, :, rows].sort(-1).values).all()
+    assert (own.cpu()[:, :, :15] == -1).all()
+
+
+def test_edge_cases():
+    """Empty and ragged inputs: T below one block, T not a multiple of the block, S = 0 slots
+    used, window larger than T, all-padding block lists, zero batch."""
+    nsa = pkg()
+    f32 = torch.float32
+    g = torch.Generator().manual_seed(0)
+    for (B, Hq, Hkv, D, T, bs, W) in [(1, 4, 2, 32, 10, 16, 64), (2, 4, 1, 64, 100, 32, 7), (1, 2, 2, 16, 70, 16, 500)]:
+        q = torch.randn(B, Hq, T, D, generator=g)
+        k = torch.randn(B, Hkv, T, D, generator=g)
+        v = torch.randn(B, Hkv, T, D, generator=g)
+        do = torch.randn(B, Hq, T, D, generator=g)
+        n_blk = T // bs
+        o, lse = nsa.range_attn_forward(q.cuda(), k.cuda(), v.cuda(), nsa.MODE_WINDOW, W, 0)
+        o_ref, lse_ref = O.stream_attn_forward(q, k, v, O.window_keep_fn(T, W))
+        check(o, o_ref, f32, "ragged window")
+        dq, dk, dv = nsa.range_attn_backward(q.cuda(), k.cuda(), v.cuda(), o, lse, do.cuda(), nsa.MODE_WINDOW, W, 0)
+        r = O.stream_attn_backward(q, k, v, o_ref, lse_ref, do, O.window_keep_fn(T, W))
+        for a, b, n in zip((dq, dk, dv), r, "qkv"):
+            check(a, b, f32, "ragged window d" + n, abs32=4e-3)
+        kp = nsa.block_mean_pool(k.cuda(), bs)
+        assert kp.shape == (B, Hkv, n_blk, D)
+        if n_blk:
+            check(kp, O.ref_block_mean_pool(k, bs), f32, "ragged pool", abs32=1e-5)
+        o, lse = nsa.range_attn_forward(q.cuda(), kp, kp, nsa.MODE_COMPRESS, 0, bs)
+        if n_blk:
+            o_ref, _ = O.stream_attn_forward(q, kp.cpu(), kp.cpu(), O.compress_keep_fn(n_blk, bs))
+            check(o, o_ref, f32, "ragged compress")
+        else:
+            assert (o == 0).all() and (lse == O.LSE_EMPTY).all()
+        idx = torch.full((B, Hkv, T, 3), -1, dtype=torch.int32)
+        o, lse = nsa.selection_forward_triton(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), max(bs, 16), return_lse=True)
+        assert (o == 0).all() and (lse == O.LSE_EMPTY).all()
+        dq, dk, dv = nsa.ops._selection_backward(q.cuda(), k.cuda(), v.cuda(), idx.cuda(), max(bs, 16), do.cuda(), o, lse)
+        assert (dq == 0).all() and (dk == 0).all() and (dv == 0).all()
+        # whole op on the ragged shape (n_blk may be 0: compression and selection contribute 0)
+        gate = torch.randn(B, Hq, T, 3, generator=g)
+        out = nsa.nsa_attention(q.cuda(), k.cuda(), v.cuda(), k.cuda(), v.cuda(), k.cuda(), v.cuda(),
+                                gate.cuda(), max(bs, 16), 2, W)
+        ref = O.stream_nsa_forward(q, k, v, k, v, k, v, gate, max(bs, 16), 2, W)
+        check(out, ref["out"], f32, "ragged whole op")
+    # zero batch
+    e = torch.empty(0, 4, 32, 32).cuda()
+    o, _ = nsa.range_attn_forward(e, e[:, :2], e[:, :2], nsa.MODE_WINDOW, 8, 0)
+    assert o.shape == e.shape
+    # bad arguments raise like the reference's asserts (nsa_selection_kernel.py:186-189)
+    with pytest.raises(AssertionError):
+        nsa.selection_forward_triton(torch.zeros(1, 2, 32, 48).cuda(), torch.zeros(1, 2, 32, 48).cuda(),
+                                     torch.zeros(1, 2, 32, 48).cuda(), torch.zeros(1, 2, 32, 1, dtype=torch.int32).cuda(), 16)
+    with pytest.raises(AssertionError):
+        nsa.selection_forward_triton(torch.zeros(1, 2, 32, 32).cuda(), torch.zeros(1, 2, 32, 32).cuda(),
+                                     torch.zeros(1, 2, 32, 32).cuda(), torch.zeros(1, 2, 32, 1, dtype=torch.int32).cuda(), 8)
+
+
+def test_headline_shape_properties():
+    """BASELINE config 2 at full size (B=4, T=8192, 16 q heads / 1 kv head, D=128, bf16):
+    size-independent checks plus the oracle on sampled query rows."""
+    nsa = pkg()
+    c = dict(B=4, Hq=16, Hkv=1, D=128, T=8192, block_size=64, S=16)
+    dtype = torch.bfloat16
+    t = make_inputs(c, dtype, seed=0, scale_qkv=True)
+    t["block_idx"] = O.make_block_idx_recent(c["B"], c["Hkv"], c["T"], 64, 16)
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+    ins = [dev(t[n], dtype).requires_grad_(True) for n in names]
+    out, idx = nsa.nsa_attention(*ins, 64, 16, 512, return_block_idx=True)
+    out.backward(dev(t["do"], dtype))
+    idx = idx.cpu()
+    T = c["T"]
+    # index sanity: valid, causal, distinct, -1 only when fewer than 16 blocks are complete
+    tt = torch.arange(T).view(1, 1, T, 1)
+    assert ((idx == -1) | ((idx >= 0) & ((idx + 1) * 64 - 1 <= tt))).all()
+    assert ((idx >= 0).sum(-1) == torch.clamp((tt.squeeze(-1) + 1) // 64, max=16)).all()
+    srt = idx.sort(-1).values
+    assert ((srt[..., 1:] != srt[..., :-1]) | (srt[..., 1:] == -1)).all()
+    # oracle on a batch slice and sampled row windows, with the kernel's block choice
+    b = 1
+    sl = lambda x: x[b:b + 1]
+    rows = [(0, 192), (4032, 4160), (8064, 8192)]
+    k_cmp = O.ref_block_mean_pool(sl(t["kc"]), 64).to(dtype).float()
+    v_cmp = O.ref_block_mean_pool(sl(t["vc"]), 64).to(dtype).float()
+    for t0, t1 in rows:
+        qs = sl(t["q"])[:, :, t0:t1]
+        parts = []
+        for k, v, keep in ((k_cmp, v_cmp, O.compress_keep(t0, t1, T // 64, 64)),
+                           (sl(t["ks"]), sl(t["vs"]), O.selection_keep(sl(idx), t0, t1, T, 64)),
+                           (sl(t["kw"]), sl(t["vw"]), O.window_keep(t0, t1, T, 512))):
+            o_b, _ = O.stream_attn_forward(qs, k, v, lambda a, bb, keep=keep: keep[..., a:bb, :])
+            parts.append(o_b)
+        ref = O.ref_gate_combine(*parts, sl(t["gate"])[:, :, t0:t1])
+        check(out[b:b + 1, :, t0:t1], ref, dtype, f"headline rows {t0}:{t1}", scale_abs=False)
+    # checksum identities of attention gradients, per branch pair (k, v):
+    #   sum_j dk_j . k_j == sum_i dq_i . q_i  holds for the sum over the three branches
+    g = {n: x.grad.float() for n, x in zip(names, ins)}
+    lhs = sum((g[n] * t[n].cuda()).sum().item() for n in ("ks", "kw")) + \
+        (g["kc"] * t["kc"].cuda()).sum().item()
+    rhs = (g["q"] * t["q"].cuda()).sum().item()
+    assert abs(lhs - rhs) <= 2e-2 * max(1.0, abs(rhs)), (lhs, rhs)
+    for n in names:
+        assert torch.isfinite(g[n]).all()
