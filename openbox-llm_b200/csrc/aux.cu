@@ -497,7 +497,7 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
 extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp,
                                int32_t* block_idx, float* importance_out, const NsaDims* dims,
                                int n_blk, int block_size, int n_sel, void* stream) {
-  NSA_CHECK_ARG(dims && q && k_cmp && lse_cmp && block_idx, "null argument");
+  NSA_CHECK_ARG(dims && q && lse_cmp && block_idx && (k_cmp || n_blk == 0), "null argument");
   NSA_CHECK_ARG(dims->Hkv > 0 && dims->Hq % dims->Hkv == 0, "Hq must be a multiple of Hkv");
   NSA_CHECK_ARG(block_size > 0 && n_sel > 0 && n_blk >= 0, "bad block_size/n_sel/n_blk");
   const int D = dims->D;

@@ -71,15 +71,22 @@ def compress_keep(t0: int, t1: int, Lk: int, block_size: int) -> torch.Tensor:
 
 
 def selection_keep(block_idx: torch.Tensor, t0: int, t1: int, T: int,
-                   block_size: int) -> torch.Tensor:
+                   block_size: int, clamp_tail: bool = False) -> torch.Tensor:
     """[B,Hkv,t1-t0,T] bool keep mask of the selection branch for query rows
     t0..t1 (nsa_selection_kernel.py:73-84): token j is kept for query i iff
-    block(j) is listed for i (slots < 0 are padding) and j <= i.  Tokens past the
-    last complete block belong to block n_blk-1 (the reference clamps)."""
+    block(j) is listed for i (slots < 0 are padding) and j <= i.
+
+    When T is not a multiple of block_size the reference's dense function and its
+    kernels disagree about the tail tokens: the dense one assigns them to block
+    n_blk-1 (the clamp at nsa_selection_kernel.py:78), the kernels attend exactly
+    pos = blk*block_size+n < T (nsa_selection_kernel.py:142-144).  clamp_tail=True
+    gives the former, the default gives the kernels' rule, which is the one the
+    drop-in must keep.  The reference's gates only use T % block_size == 0, where
+    the two coincide."""
     B, Hkv, _, S = block_idx.shape
-    n_blk = T // block_size
+    n_blk = T // block_size if clamp_tail else -(-T // block_size)
     idx = block_idx[:, :, t0:t1].long()
-    valid = idx >= 0
+    valid = (idx >= 0) & (idx < max(n_blk, 1))
     oh = torch.zeros(B, Hkv, t1 - t0, S, max(n_blk, 1), dtype=torch.bool)
     oh.scatter_(-1, idx.clamp(min=0).unsqueeze(-1), valid.unsqueeze(-1))
     chosen = oh.any(dim=3)                                   # [B,Hkv,rows,n_blk]
@@ -87,6 +94,7 @@ def selection_keep(block_idx: torch.Tensor, t0: int, t1: int, T: int,
     keep = chosen[..., blk_of_tok]                           # [B,Hkv,rows,T]
     causal = torch.arange(T)[None, :] <= torch.arange(t0, t1)[:, None]
     return keep & causal[None, None]
+
 
 
 # ---------------------------------------------------------------------------
@@ -101,7 +109,7 @@ def ref_selection_forward(q, k, v, block_idx, block_size):
     kexp = _expand_kv(k.float(), G)
     vexp = _expand_kv(v.float(), G)
     s = torch.matmul(q.float(), kexp.transpose(-1, -2)) * scale
-    keep = selection_keep(block_idx, 0, T, T, block_size).repeat_interleave(G, dim=1)
+    keep = selection_keep(block_idx, 0, T, T, block_size, clamp_tail=True).repeat_interleave(G, dim=1)
     s = s.masked_fill(~keep, torch.finfo(s.dtype).min)
     row_has = keep.any(dim=-1, keepdim=True)
     p = torch.softmax(s, dim=-1) * row_has
@@ -198,6 +206,8 @@ def canonical_topn(imp: torch.Tensor, valid: torch.Tensor, n_sel: int) -> torch.
     set torch.topk returns."""
     B, Hkv, T, n_blk = imp.shape
     k_top = min(n_sel, n_blk)
+    if n_blk == 0:
+        return torch.full((B, Hkv, T, n_sel), -1, dtype=torch.int32)
     key = imp.masked_fill(~valid[None, None], -1.0)      # probabilities are >= 0
     # stable sort of -key keeps the lower index first among equal values
     order = torch.sort(-key, dim=-1, stable=True).indices[..., :k_top]
@@ -259,7 +269,7 @@ def stream_attn_forward(q, k, v, keep_fn: KeepFn, chunk: int = 512):
     kf, vf = k.float(), v.float()
     o = torch.zeros(B, Hkv, G, T, D)
     lse = torch.full((B, Hkv, G, T), LSE_EMPTY)
-    for t0 in range(0, T, chunk):
+    for t0 in range(0, T if Lk > 0 else 0, chunk):
         t1 = min(T, t0 + chunk)
         keep = _keep_for(keep_fn, t0, t1, B, Hkv, G, Lk)
         s = torch.einsum("bhgtd,bhjd->bhgtj", qf[:, :, :, t0:t1], kf) * scale
@@ -292,7 +302,7 @@ def stream_attn_backward(q, k, v, o, lse, do, keep_fn: KeepFn, chunk: int = 512)
     dq = torch.zeros(B, Hkv, G, T, D)
     dk = torch.zeros(B, Hkv, Lk, D)
     dv = torch.zeros(B, Hkv, Lk, D)
-    for t0 in range(0, T, chunk):
+    for t0 in range(0, T if Lk > 0 else 0, chunk):
         t1 = min(T, t0 + chunk)
         keep = _keep_for(keep_fn, t0, t1, B, Hkv, G, Lk)
         s = torch.einsum("bhgtd,bhjd->bhgtj", qf[:, :, :, t0:t1], kf) * scale
@@ -328,7 +338,7 @@ def stream_importance(q, k_cmp, block_size, chunk: int = 512):
     qf = q.float().view(B, Hkv, G, T, D)
     kf = k_cmp.float()
     imp = torch.zeros(B, Hkv, T, n_blk)
-    for t0 in range(0, T, chunk):
+    for t0 in range(0, T if n_blk > 0 else 0, chunk):
         t1 = min(T, t0 + chunk)
         keep = compress_keep(t0, t1, n_blk, block_size)[None, None, None].expand(
             B, Hkv, G, t1 - t0, n_blk)

@@ -27,7 +27,7 @@ TC_CONFIGS = [
     dict(B=1, Hq=8, Hkv=2, D=64, T=768, block_size=64, S=5, window=133),
     dict(B=1, Hq=4, Hkv=1, D=128, T=448, block_size=64, S=3, window=64),
     dict(B=1, Hq=16, Hkv=4, D=64, T=1000, block_size=64, S=16, window=77),   # ragged T
-    dict(B=1, Hq=2, Hkv=1, D=128, T=320, block_size=64, S=2, window=1),
+    dict(B=1, Hq=2, Hkv=1, D=128, T=320, block_size=64, S=2, window=3),
     dict(B=1, Hq=1, Hkv=1, D=64, T=256, block_size=64, S=4, window=300),
 ]
 
