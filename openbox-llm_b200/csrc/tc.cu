@@ -1,8 +1,461 @@
-// placeholder until the tcgen05 kernels land
-#include "common.cuh"
+// tcgen05 / TMEM attention kernels for sm_100a.
+//
+// One CTA owns a tile of 128 rows = nq consecutive query tokens x the Gp query heads of one
+// (batch, kv head) group (row r -> head r / nq, token r % nq), so the heads of a GQA group
+// share every K/V tile.  The CTA walks a list of 64-key tiles:
+//   window      the tiles covering [t_first - W + 1, t_last]
+//   compression the tiles covering summaries [0, (t_last + 1) / Bsz - 1]
+//   selection   the union of the 64-token blocks listed for the tile's nq queries, built in
+//               shared memory, with a per-(query, block) membership bit
+// Per tile: TMA brings K and V (128B-swizzled boxes) into a 2-stage ring; one thread issues
+// S = Q K^T (tcgen05.mma, accumulator in TMEM); each of the 128 threads owns one row of S
+// (tcgen05.ld, lane = row), masks it, runs the online softmax in the log2 domain without any
+// cross-thread traffic, writes P as packed bf16 back to TMEM (tcgen05.st) and the same
+// thread issues O += P V with P as the TMEM A operand and V as an MN-major shared-memory B
+// operand.  The running maximum is only raised when it grows by more than 8 (log2 units), so
+// the O accumulator in TMEM is rescaled rarely.
+#include "tc_common.cuh"
+
 namespace nsa {
-bool tc_shape_ok(const NsaDims&, int) { return false; }
-int tc_attn_fwd(const AttnArgs&, cudaStream_t) { set_error("tc path not built"); return NSA_ERR_UNSUPPORTED; }
-size_t tc_attn_bwd_workspace(const AttnArgs&) { return 0; }
-int tc_attn_bwd(const AttnArgs&, void*, size_t, cudaStream_t) { set_error("tc path not built"); return NSA_ERR_UNSUPPORTED; }
+namespace tc {
+
+struct FwdArgs {
+  const int32_t* block_idx;
+  __nv_bfloat16* o;
+  float* lse;
+  int* status;
+  int B, Hq, Hkv, T, Lk, S, G, Gp, nq;
+  int kind, window, block_size;
+  int n_qtiles, nb_sel;      // nb_sel = ceil(T / 64) blocks a selection list may name
+  int nw;                    // 32-bit membership words per block = max(1, nq / 32)
+  float scale_log2;
+};
+
+template <int D> struct FwdSmem {
+  static constexpr int kSlabs = D / 64;
+  static constexpr int kQBytes = kRows * 128 * kSlabs;
+  static constexpr int kKVBytes = kKeys * 128 * kSlabs;
+  static constexpr int kFixed = kQBytes + 4 * kKVBytes;   // Q + 2 K stages + 2 V stages
+};
+
+__host__ __device__ inline size_t fwd_smem_bytes(int D, int nb_sel, int nw, int kind) {
+  size_t fixed = (size_t)(kRows * 128 + 4 * kKeys * 128) * (D / 64);
+  size_t extra = 256 /*barriers etc*/ + 132 * 4 /*scan*/;
+  if (kind == 2) extra += (size_t)nb_sel * nw * 4 + (size_t)nb_sel * 2 + 16;
+  return fixed + extra + 1024 /*alignment slack*/;
 }
+
+template <int D>
+__global__ void __launch_bounds__(128, 2)
+tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const FwdArgs p) {
+  using L = FwdSmem<D>;
+  constexpr int kSlabs = L::kSlabs;
+  constexpr uint32_t kTmemCols = 256;
+  constexpr uint32_t kColO = 0, kColS = 128, kColP = 192;
+  constexpr uint32_t kIdescQK = idesc_bf16(128, kKeys, 0, 0);
+  constexpr uint32_t kIdescPV = idesc_bf16(128, D, 0, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + L::kQBytes;
+  uint8_t* sV = sK + 2 * L::kKVBytes;
+  uint64_t* bars = (uint64_t*)(sV + 2 * L::kKVBytes);
+  uint64_t* bar_q = bars + 0;
+  uint64_t* bar_k = bars + 1;   // [2]
+  uint64_t* bar_v = bars + 3;   // [2]
+  uint64_t* bar_s = bars + 5;
+  uint64_t* bar_o = bars + 6;
+  uint32_t* s_tmem = (uint32_t*)(bars + 8);
+  volatile int* s_abort = (volatile int*)(s_tmem + 1);
+  int* s_ntiles = (int*)(s_tmem + 2);
+  int* s_scan = (int*)(s_tmem + 4);                 // [129]
+  uint32_t* s_member = (uint32_t*)(s_scan + 132);   // [nb_sel * nw]   (selection only)
+  uint16_t* s_tiles = (uint16_t*)(s_member + (p.kind == 2 ? p.nb_sel * p.nw : 0));
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int qtile = p.n_qtiles - 1 - (int)blockIdx.x;   // long rows first
+  const int bh = blockIdx.y;
+  const int b = bh / p.Hkv, hkv = bh % p.Hkv;
+  const int t0 = qtile * p.nq;
+  const int t_last = min(p.T - 1, t0 + p.nq - 1);
+  const int g = tid / p.nq, ql = tid % p.nq;
+  const int t = t0 + ql;
+  const bool row_ok = (g < p.G) && (t < p.T);
+  const int head = hkv * p.G + g;
+
+  if (tid == 0) {
+    *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k + 0, 1); mbar_init(bar_k + 1, 1);
+    mbar_init(bar_v + 0, 1); mbar_init(bar_v + 1, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+  }
+  __syncthreads();
+  if (*s_abort) return;
+
+  // ---- tile list ------------------------------------------------------------------------
+  int n_tiles = 0, first_key = 0;
+  if (p.kind == 0) {
+    first_key = max(0, t0 - p.window + 1) & ~(kKeys - 1);
+    n_tiles = (min(t_last, p.Lk - 1) - first_key) / kKeys + 1;
+  } else if (p.kind == 1) {
+    const int hi_last = min(p.Lk, (t_last + 1) / p.block_size) - 1;
+    n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
+  } else {
+    const int nmem = p.nb_sel * p.nw;
+    for (int i = tid; i < nmem; i += 128) s_member[i] = 0u;
+    __syncthreads();
+    const int32_t* idx = p.block_idx + ((size_t)bh * p.T + t0) * p.S;
+    const int n_entries = (t_last - t0 + 1) * p.S;
+    for (int e = tid; e < n_entries; e += 128) {
+      const int q_local = e / p.S;
+      const int blk = __ldg(idx + e);
+      if (blk >= 0 && blk < p.nb_sel && blk * kKeys <= t0 + q_local)
+        atomicOr(&s_member[blk * p.nw + (q_local >> 5)], 1u << (q_local & 31));
+    }
+    __syncthreads();
+    const int per = (p.nb_sel + 127) / 128;
+    const int j0 = tid * per, j1 = min(p.nb_sel, j0 + per);
+    int cnt = 0;
+    for (int j = j0; j < j1; ++j) {
+      uint32_t any = 0;
+      for (int w = 0; w < p.nw; ++w) any |= s_member[j * p.nw + w];
+      cnt += any != 0;
+    }
+    s_scan[tid + 1] = cnt;
+    __syncthreads();
+    if (tid == 0) {
+      s_scan[0] = 0;
+      for (int i = 1; i <= 128; ++i) s_scan[i] += s_scan[i - 1];
+      *s_ntiles = s_scan[128];
+    }
+    __syncthreads();
+    int pos = s_scan[tid];
+    for (int j = j0; j < j1; ++j) {
+      uint32_t any = 0;
+      for (int w = 0; w < p.nw; ++w) any |= s_member[j * p.nw + w];
+      if (any) s_tiles[pos++] = (uint16_t)j;
+    }
+    __syncthreads();
+    n_tiles = *s_ntiles;
+  }
+
+  float m_used = -INFINITY, l_sum = 0.f;
+  uint32_t tmem = 0;
+
+  if (n_tiles > 0) {
+    // ---- TMEM ---------------------------------------------------------------------------
+    if (warp == 0) {
+      tmem_alloc(s_tmem, kTmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    tmem = *s_tmem;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+
+    auto key0_of = [&](int i) -> int {
+      if (p.kind == 2) return (int)s_tiles[i] * kKeys;
+      return first_key + i * kKeys;
+    };
+    auto load_k = [&](int i) {
+      uint64_t* bar = bar_k + (i & 1);
+      mbar_expect_tx(bar, L::kKVBytes);
+#pragma unroll
+      for (int s = 0; s < kSlabs; ++s)
+        tma_load_3d(sK + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_k, bar, s * 64, key0_of(i), bh);
+    };
+    auto load_v = [&](int i) {
+      uint64_t* bar = bar_v + (i & 1);
+      mbar_expect_tx(bar, L::kKVBytes);
+#pragma unroll
+      for (int s = 0; s < kSlabs; ++s)
+        tma_load_3d(sV + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_v, bar, s * 64, key0_of(i), bh);
+    };
+    auto issue_s = [&](int i) {   // S = Q K^T for tile i
+      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (i & 1) * L::kKVBytes);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+        mma_ss(tmem + kColS, desc_kmajor(qa + slab * (kRows * 128) + in),
+               desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescQK, kk > 0);
+      }
+      tc_commit(bar_s);
+    };
+    auto issue_pv = [&](int i) {  // O (+)= P V for tile i
+      const uint32_t va = smem_u32(sV + (i & 1) * L::kKVBytes);
+#pragma unroll
+      for (int kk = 0; kk < kKeys / 16; ++kk)
+        mma_ts(tmem + kColO, tmem + kColP + kk * 8, desc_mnmajor(va + kk * 2048, kKeys * 128),
+               kIdescPV, (i > 0) || (kk > 0));
+      tc_commit(bar_o);
+    };
+
+    if (tid == 0) {
+      mbar_expect_tx(bar_q, L::kQBytes);
+#pragma unroll
+      for (int s = 0; s < kSlabs; ++s)
+        tma_load_3d(sQ + s * (kRows * 128), &tm_q, bar_q, s * 64, t0, b * p.Hq + hkv * p.G);
+      load_k(0);
+      load_v(0);
+      if (n_tiles > 1) { load_k(1); load_v(1); }
+      mbar_wait(bar_q, 0, p.status, s_abort, 1);
+      mbar_wait(bar_k, 0, p.status, s_abort, 2);
+      tc_fence_after();
+      issue_s(0);
+    }
+
+    for (int i = 0; i < n_tiles; ++i) {
+      const int key0 = key0_of(i);
+      mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
+      tc_fence_after();
+      if (tid == 0 && i + 2 < n_tiles) load_k(i + 2);   // the K stage of tile i is free again
+      __syncwarp();
+
+      uint32_t r[64];
+      tmem_ld32(lane_base + kColS, r);
+      tmem_ld32(lane_base + kColS + 32, r + 32);
+      tmem_wait_ld();
+
+      // valid columns of this row in this tile form one range [lo, hi]
+      int lo = 0, hi = -1;
+      if (row_ok) {
+        if (p.kind == 0) {
+          lo = max(0, t - p.window + 1 - key0);
+          hi = min(kKeys - 1, t - key0);
+        } else if (p.kind == 1) {
+          hi = min(kKeys - 1, min(p.Lk, (t + 1) / p.block_size) - 1 - key0);
+        } else {
+          const uint32_t w = s_member[(key0 / kKeys) * p.nw + (ql >> 5)];
+          if ((w >> (ql & 31)) & 1u) hi = min(kKeys - 1, t - key0);
+        }
+      }
+      float x[64];
+      float tmax = -INFINITY;
+      if (lo <= 0 && hi >= kKeys - 1) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          x[c] = __uint_as_float(r[c]) * p.scale_log2;
+          tmax = fmaxf(tmax, x[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          x[c] = (c >= lo && c <= hi) ? __uint_as_float(r[c]) * p.scale_log2 : -INFINITY;
+          tmax = fmaxf(tmax, x[c]);
+        }
+      }
+      float alpha = 1.f;
+      bool rescale = false;
+      if (tmax > m_used + 8.f) {              // also the first finite maximum (m_used = -inf)
+        if (m_used != -INFINITY) {
+          alpha = ex2(m_used - tmax);
+          rescale = true;
+          l_sum *= alpha;
+        }
+        m_used = tmax;
+      }
+      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+      float psum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float p0 = ex2(x[2 * c] - msub), p1 = ex2(x[2 * c + 1] - msub);
+        psum += p0 + p1;
+        pk[c] = pack_bf16(p0, p1);
+      }
+      l_sum += psum;
+
+      if (i > 0) {                            // P and O are free once PV of tile i-1 is done
+        mbar_wait(bar_o, (i - 1) & 1, p.status, s_abort, 8);
+        tc_fence_after();
+        if (tid == 0 && i + 1 < n_tiles && i + 1 >= 2) load_v(i + 1);
+        __syncwarp();
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t o32[32];
+            tmem_ld32(lane_base + kColO + cc * 32, o32);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o32[c] = __float_as_uint(__uint_as_float(o32[c]) * alpha);
+            tmem_st32(lane_base + kColO + cc * 32, o32);
+          }
+        }
+      }
+      __syncwarp();
+      tmem_st32(lane_base + kColP, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        mbar_wait(bar_v + (i & 1), (i >> 1) & 1, p.status, s_abort, 16);
+        issue_pv(i);
+        if (i + 1 < n_tiles) {
+          mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
+          issue_s(i + 1);
+        }
+      }
+    }
+    mbar_wait(bar_o, (n_tiles - 1) & 1, p.status, s_abort, 8);
+    tc_fence_after();
+    __syncwarp();
+  }
+
+  // ---- epilogue ---------------------------------------------------------------------------
+  const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+  __nv_bfloat16* orow = p.o + ((size_t)(b * p.Hq + head) * p.T + t) * D;
+  if (n_tiles > 0) {
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+    for (int cc = 0; cc < D / 32; ++cc) {
+      uint32_t o32[32];
+      tmem_ld32(lane_base + kColO + cc * 32, o32);
+      tmem_wait_ld();
+      if (row_ok) {
+        uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 u;
+          u.x = pack_bf16(__uint_as_float(o32[v4 * 8 + 0]) * inv, __uint_as_float(o32[v4 * 8 + 1]) * inv);
+          u.y = pack_bf16(__uint_as_float(o32[v4 * 8 + 2]) * inv, __uint_as_float(o32[v4 * 8 + 3]) * inv);
+          u.z = pack_bf16(__uint_as_float(o32[v4 * 8 + 4]) * inv, __uint_as_float(o32[v4 * 8 + 5]) * inv);
+          u.w = pack_bf16(__uint_as_float(o32[v4 * 8 + 6]) * inv, __uint_as_float(o32[v4 * 8 + 7]) * inv);
+          if (l_sum > 0.f) dst[v4] = u; else dst[v4] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+  } else if (row_ok) {
+    uint4* dst = reinterpret_cast<uint4*>(orow);
+#pragma unroll
+    for (int v4 = 0; v4 < D / 8; ++v4) dst[v4] = make_uint4(0, 0, 0, 0);
+  }
+  if (row_ok)
+    p.lse[(size_t)(b * p.Hq + head) * p.T + t] =
+        l_sum > 0.f ? (m_used + log2f(l_sum)) * kLn2 : kLseEmpty;
+}
+
+// ---- host side -------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// 3-D map over a [heads, rows, D] bf16 tensor: box = 64 elements x box_rows x box_heads
+static int make_map(CUtensorMap* m, const void* base, int D, int rows, int heads, int box_rows,
+                    int box_heads) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available"); return NSA_ERR_CUDA; }
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows * D * 2};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)box_heads};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d", (int)r); return NSA_ERR_CUDA; }
+  return NSA_OK;
+}
+
+static int group_pad(int G) {
+  int gp = 1;
+  while (gp < G) gp <<= 1;
+  return gp;
+}
+
+}  // namespace tc
+
+bool tc_shape_ok(const NsaDims& d, int block_size) {
+  if (d.dtype != NSA_DTYPE_BF16) return false;
+  if (d.D != 64 && d.D != 128) return false;
+  if (block_size != tc::kKeys) return false;
+  const int G = d.Hq / d.Hkv;
+  if (G > 128) return false;
+  if (d.T < 1) return false;
+  const int nq = tc::kRows / tc::group_pad(G);
+  const int nb = (d.T + tc::kKeys - 1) / tc::kKeys;
+  if (nb > 65535) return false;
+  if (tc::fwd_smem_bytes(d.D, nb, nq >= 32 ? nq / 32 : 1, 2) > 112 * 1024) return false;
+  return true;
+}
+
+int tc_attn_fwd(const AttnArgs& a, cudaStream_t st) {
+  using namespace tc;
+  FwdArgs p;
+  p.block_idx = a.block_idx;
+  p.o = (__nv_bfloat16*)a.o;
+  p.lse = a.lse;
+  p.status = device_status_ptr();
+  if (!p.status) { set_error("device status word unavailable"); return NSA_ERR_CUDA; }
+  p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.T = a.T; p.Lk = a.Lk; p.S = a.S;
+  p.G = a.Hq / a.Hkv;
+  p.Gp = group_pad(p.G);
+  p.nq = kRows / p.Gp;
+  p.kind = a.kind; p.window = a.window; p.block_size = a.block_size;
+  p.n_qtiles = (a.T + p.nq - 1) / p.nq;
+  p.nb_sel = (a.T + kKeys - 1) / kKeys;
+  p.nw = p.nq >= 32 ? p.nq / 32 : 1;
+  p.scale_log2 = a.scale * kLog2e;
+  CUtensorMap tm_q, tm_k, tm_v;
+  int rc = make_map(&tm_q, a.q, a.D, a.T, a.B * a.Hq, p.nq, p.Gp);
+  if (rc == NSA_OK) rc = make_map(&tm_k, a.k, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
+  if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
+  if (rc != NSA_OK) return rc;
+  const size_t smem = fwd_smem_bytes(a.D, p.nb_sel, p.nw, a.kind);
+  dim3 grid(p.n_qtiles, a.B * a.Hkv);
+  if (a.D == 128) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tc_fwd_kernel<128><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p);
+  } else {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tc_fwd_kernel<64><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p);
+  }
+  NSA_LAUNCH_OK("tc_fwd_kernel");
+  return NSA_OK;
+}
+
+size_t tc_attn_bwd_workspace(const AttnArgs& a) {
+  return 2 * align_up((size_t)a.B * a.Hkv * a.Lk * a.D * sizeof(float), 256);
+}
+
+int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
+  // backward still runs on the CUDA-core kernels
+  AttnArgs b = a;
+  const size_t n = (size_t)a.B * a.Hkv * a.Lk * a.D;
+  if (ws_bytes < tc_attn_bwd_workspace(a) || !ws) { set_error("backward workspace too small"); return NSA_ERR_WORKSPACE; }
+  void* dk = (void*)a.dk_acc;
+  void* dv = (void*)a.dv_acc;
+  b.dk_acc = (float*)ws;
+  b.dv_acc = (float*)((char*)ws + align_up(n * sizeof(float), 256));
+  NSA_CUDA_OK(cudaMemsetAsync(b.dk_acc, 0, n * sizeof(float), st));
+  NSA_CUDA_OK(cudaMemsetAsync(b.dv_acc, 0, n * sizeof(float), st));
+  int rc = simt_attn_bwd(b, NSA_DTYPE_BF16, st);
+  if (rc != NSA_OK) return rc;
+  rc = cast_f32_to(b.dk_acc, dk, n, NSA_DTYPE_BF16, st);
+  if (rc != NSA_OK) return rc;
+  return cast_f32_to(b.dv_acc, dv, n, NSA_DTYPE_BF16, st);
+}
+
+}  // namespace nsa
