@@ -1,0 +1,358 @@
+"""Benchmark of the NSA attention op, forward + backward, on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One step = one forward + backward pass of the whole op (learned block pooling, compression
+attention, block scoring + top-n, selected-block attention, sliding-window attention, gate
+combine and every input/parameter gradient) over one batch of synthetic input.  Workload
+"c4_t32k" is the configuration the headline metric is quoted on (B=8, T=32768, 16 query heads /
+2 kv heads, D=128, 64-token blocks, top-16, window 512, bf16).  Under torchrun every rank runs
+that workload on its own (batch x kv-head units are independent: no data-path collective) and
+the reported value is the sum over ranks divided by the slowest rank's time ("weak" scaling).
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
+reference's pure-torch algorithm on the host cores instead.
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE config 4: the T=32K training shape of the headline metric
+    "c4_t32k": dict(B=8, T=32768, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
+    # BASELINE config 2
+    "c2_t8k": dict(B=4, T=8192, Hq=16, Hkv=1, D=128, block_size=64, n_sel=16, window=512),
+    "tiny": dict(B=1, T=2048, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
+}
+METRIC = "NSA fwd+bwd tokens/s per B200 at T=32K bf16; % of tensor-pipe peak"
+NAMES = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+COMP = ["k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj"]
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(tflops=float(p["bf16_tflops_sustained"]), tflops_burst=float(p["bf16_tflops"]),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1400.0, tflops_burst=1590.0, hbm=6650.0, source="fallback")
+
+
+def device_inputs(w, seed, device):
+    """Synthetic inputs of the workload's shapes: q, six K/V tensors, gate logits, upstream
+    gradient ~ N(0,1) (bf16); compressor parameters as the reference initialises them
+    (nsa_model.py:113-116) with 0.02-std noise on the two zero-initialised ones."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    B, T, Hq, Hkv, D, bs = w["B"], w["T"], w["Hq"], w["Hkv"], w["D"], w["block_size"]
+    mk = lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    t = {"q": mk(B, Hq, T, D)}
+    for n in NAMES[1:7]:
+        t[n] = mk(B, Hkv, T, D)
+    t["gate"] = mk(B, Hq, T, 3)
+    t["do"] = mk(B, Hq, T, D)
+    comp = {}
+    for p in ("k", "v"):
+        comp[p + "_intra"] = 0.02 * torch.randn(bs, D, generator=g, device=device)
+        comp[p + "_logits"] = 0.02 * torch.randn(bs, generator=g, device=device)
+        bound = D ** -0.5                                   # nn.Linear default init range
+        comp[p + "_proj"] = (torch.rand(D, D, generator=g, device=device) * 2 - 1) * bound
+    return t, comp
+
+
+def run_step(nsa, t, comp, w):
+    ins = [t[n].requires_grad_(True) for n in NAMES]
+    cps = {k: v.requires_grad_(True) for k, v in comp.items()}
+    out, idx = nsa.nsa_attention(*ins, w["block_size"], w["n_sel"], w["window"], compressor=cps,
+                                 return_block_idx=True)
+    grads = torch.autograd.grad(out, ins + [cps[k] for k in COMP], t["do"])
+    return out, idx, grads
+
+
+def attended(idx, w):
+    """Exact (query, key) pairs attended per branch, summed over batch and kv heads; every one
+    of them is visited by each of the G query heads of its group."""
+    T, bs, W = w["T"], w["block_size"], w["window"]
+    tt = torch.arange(T, device=idx.device)
+    units = idx.shape[0] * idx.shape[1]
+    n_cmp = int(torch.clamp((tt + 1) // bs, max=T // bs).sum().item()) * units
+    n_win = int(torch.clamp(tt + 1, max=W).sum().item()) * units
+    i64 = idx.long()
+    start = i64 * bs
+    end = torch.minimum(start + bs - 1, tt.view(1, 1, T, 1))
+    cnt = torch.where((i64 >= 0) & (start <= tt.view(1, 1, T, 1)), end - start + 1, torch.zeros_like(i64))
+    return {"cmp": n_cmp, "slc": int(cnt.sum().item()), "win": n_win}
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [x for x in sm if x > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference_pass(w, rows, threads, seed=0):
+    """One forward+backward of the reference's pure-torch algorithm (dense masked scores over
+    all T keys per query row, as nsa_model.py:196-304 computes them) restated by the oracle,
+    on `rows` query rows of ONE (batch, kv-head) unit.  Returns seconds."""
+    from oracle import nsa_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(seed)
+    T, D, bs, G = w["T"], w["D"], w["block_size"], w["Hq"] // w["Hkv"]
+    r0 = T - rows
+    q = torch.randn(1, G, rows, D, generator=g)
+    kv = [torch.randn(1, 1, T, D, generator=g) for _ in range(6)]
+    gate = torch.randn(1, G, rows, 3, generator=g)
+    do = torch.randn(1, G, rows, D, generator=g)
+    idx = O.make_block_idx_recent(1, 1, T, bs, w["n_sel"])
+    t0 = time.perf_counter()
+    k_cmp = O.ref_block_mean_pool(kv[0], bs)
+    v_cmp = O.ref_block_mean_pool(kv[1], bs)
+    n_blk = T // bs
+    fns = [(k_cmp, v_cmp, lambda a, b: O.compress_keep(r0 + a, r0 + b, n_blk, bs)),
+           (kv[2], kv[3], lambda a, b: O.selection_keep(idx, r0 + a, r0 + b, T, bs)),
+           (kv[4], kv[5], lambda a, b: O.window_keep(r0 + a, r0 + b, T, w["window"]))]
+    outs = [O.stream_attn_forward(q, k, v, fn, chunk=256) for k, v, fn in fns]
+    out = O.ref_gate_combine(outs[0][0], outs[1][0], outs[2][0], gate)
+    dos = O.gate_combine_backward(outs[0][0], outs[1][0], outs[2][0], gate, do)
+    for (k, v, fn), (o, lse), d in zip(fns, outs, dos[:3]):
+        O.stream_attn_backward(q, k, v, o, lse, d, fn, chunk=256)
+    return time.perf_counter() - t0, float(out.abs().mean())
+
+
+def cpu_baseline(w, threads, budget_s=20.0):
+    rows = 64
+    dt, _ = cpu_reference_pass(w, rows, threads)           # warm-up and calibration
+    rows = int(max(64, min(w["T"], rows * budget_s / max(dt, 1e-3) // 64 * 64)))
+    dt, _ = cpu_reference_pass(w, rows, threads)
+    # a token is one (batch, position) over all Hq heads = Hkv units' rows
+    tok_s = rows / (dt * w["Hkv"])
+    return {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{rows} query rows (the last ones) of one (batch, kv-head) unit against all "
+                      f"T={w['T']} keys, fp32 fwd+bwd of the three branches + gate, "
+                      f"{dt:.1f} s; scaled by the {w['Hkv']} units a token spans"}
+
+
+def reference_arm(args, w, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    times, rows = [], 64
+    dt, _ = cpu_reference_pass(w, rows, threads)
+    rows = int(max(64, min(w["T"], rows * 6.0 / max(dt, 1e-3) // 64 * 64)))   # about 6 s a step
+    for i in range(args.warmup + args.steps):
+        dt, _ = cpu_reference_pass(w, rows, threads, seed=i)
+        if i >= args.warmup:
+            times.append(dt)
+    tok_s = rows * len(times) / (sum(times) * w["Hkv"])
+    sample = (f"each step: {rows} query rows of one (batch, kv-head) unit against all T={w['T']} "
+              f"keys, fp32, oracle restatement of the reference's pure-torch path")
+    line = {"impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(workload=args.workload, **w),
+            "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c4_t32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, w, rank)
+        return
+
+    assert args.warmup >= 3, "timing rules: at least 3 warm-up steps"
+    nsa = importlib.import_module("openbox-llm_b200")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    L = importlib.import_module("openbox-llm_b200._lib")
+
+    t, comp = device_inputs(w, seed=1234 + rank, device=dev)
+    for _ in range(args.warmup):
+        out, idx, grads = run_step(nsa, t, comp, w)
+    torch.cuda.synchronize()
+    counts = attended(idx, w)
+    G = w["Hq"] // w["Hkv"]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------------------
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ
+                           else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    L.lib().nsa_profile_enable(1)
+    launches0 = L.lib().nsa_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        out, idx, grads = run_step(nsa, t, comp, w)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = L.lib().nsa_launch_count() - launches0
+    prof = L.profile_summary()
+    L.lib().nsa_profile_enable(0)
+    clocks = sampler.stop()
+    assert L.lib().nsa_device_status(None) == 0, L.lib().nsa_last_error()
+
+    # ---- end to end: pinned host buffers in, results out, every step ---------------------------
+    host_in = {n: torch.empty(t[n].shape, dtype=t[n].dtype, pin_memory=True).copy_(t[n]) for n in NAMES + ["do"]}
+    host_out = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in [out] + list(grads)]
+    h2d = sum(x.numel() * x.element_size() for x in host_in.values())
+    d2h = sum(x.numel() * x.element_size() for x in host_out)
+    dbuf = {n: torch.empty_like(t[n]) for n in host_in}
+
+    def e2e_step():
+        for n in host_in:
+            dbuf[n].copy_(host_in[n], non_blocking=True)
+        o, _, g = run_step(nsa, dbuf, comp, w)
+        for dst, src in zip(host_out, [o] + list(g)):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_step()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+
+    if dist is not None:
+        tt = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    tokens = world * w["B"] * w["T"] * args.steps
+    pk = peaks()
+    # ---- roofline of the dominant kernel ---------------------------------------------------
+    # algorithmic FLOPs: 4*D per attended (query head, key) pair forward (QK^T and PV),
+    # backward 2.5x that (recomputed S, dP, dV, dK, dQ); masked or padded MMA work not counted.
+    pairs = {k: v * G for k, v in counts.items()}
+    D = w["D"]
+    flop_tab = {}
+    for br in ("cmp", "slc", "win"):
+        flop_tab["tc_fwd_" + br] = 4 * D * pairs[br]
+        flop_tab["tc_bwd_dq_" + br] = 6 * D * pairs[br]      # S, dP, dQ
+        flop_tab["tc_bwd_dkdv_" + br] = 8 * D * pairs[br]    # S, dP, dV, dK
+        flop_tab["simt_fwd_" + br] = 4 * D * pairs[br]
+        flop_tab["simt_bwd_" + br] = 10 * D * pairs[br]
+    total_ms = sum(v[1] for v in prof.values()) or 1.0
+    top = max(prof.items(), key=lambda kv: kv[1][1]) if prof else (None, (0, 0.0))
+    roof = None
+    if top[0] is not None:
+        name, (cnt, tms) = top
+        per_launch_ms = tms / max(cnt, 1)
+        if name in flop_tab:
+            achieved = flop_tab[name] / (per_launch_ms * 1e-3) / 1e12
+            roof = {"kernel": name, "bound": "tensor", "achieved": achieved, "peak": pk["tflops"],
+                    "unit": "TFLOP/s", "frac": achieved / pk["tflops"], "traffic": None,
+                    "peak_source": pk["source"] + " (sustained bf16 GEMM)",
+                    "launch_ms": per_launch_ms, "share_of_kernel_time": tms / total_ms}
+        else:
+            roof = {"kernel": name, "bound": "hbm", "achieved": None, "peak": pk["hbm"], "unit": "GB/s",
+                    "frac": None, "traffic": None, "launch_ms": per_launch_ms,
+                    "share_of_kernel_time": tms / total_ms}
+    total_flops = 14 * D * sum(pairs.values())
+    line = {
+        "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": dict(workload=args.workload, **w, compression="learned block pooling, stride = block",
+                       kv_tensors="six independent (kc,vc,ks,vs,kw,vw)",
+                       l2="inputs (2.9 GB per step) exceed the 126 MB L2"),
+        "tflops_algorithmic": total_flops * world / (ms / args.steps * 1e-3) / 1e12,
+        "frac_of_tensor_peak": total_flops / (ms / args.steps * 1e-3) / 1e12 / pk["tflops"],
+        "clocks": clocks,
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(launches),
+        "roofline": roof,
+        "kernels": {k: {"launches": v[0], "ms": round(v[1], 3), "share": round(v[1] / total_ms, 4)}
+                    for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+        "impl": nsa.get_impl(),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(w, os.cpu_count() or 1)
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

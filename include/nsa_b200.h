@@ -138,6 +138,16 @@ int nsa_gate_combine_bwd(const void* o_cmp, const void* o_slc, const void* o_win
                          const void* gate_logits, const void* d_out, void* do_cmp, void* do_slc,
                          void* do_win, void* d_gate_logits, const NsaDims* dims, void* stream);
 
+/* ---- accounting ------------------------------------------------------------------------------
+ * nsa_launch_count: kernels launched by this library in this process so far.
+ * nsa_profile_enable(1) makes every later kernel launch be bracketed by CUDA events on its own
+ * stream (and drops earlier records); nsa_profile_summary waits for those events and writes one
+ * line "kernel_name launches total_ms" per kernel into buf, returning the number of lines.
+ * No counterpart in the reference (it times whole calls with perf_counter, bench_kernel.py:56-69). */
+long long nsa_launch_count(void);
+void nsa_profile_enable(int on);
+int nsa_profile_summary(char* buf, size_t cap);
+
 /* error flag raised by a kernel whose bounded wait ran out (0 = none); reading it synchronises
  * the stream. */
 int nsa_device_status(void* stream);

@@ -31,6 +31,9 @@ SIGNATURES = {
     "nsa_version": (_i, []),
     "nsa_tc_supported": (_i, [_dp, _i]),
     "nsa_device_status": (_i, [_vp]),
+    "nsa_launch_count": (ctypes.c_longlong, []),
+    "nsa_profile_enable": (None, [_i]),
+    "nsa_profile_summary": (_i, [ctypes.c_char_p, _sz]),
     "nsa_range_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _dp, _i, _i, _i, _i, _i, _vp]),
     "nsa_range_attn_bwd_workspace_bytes": (_sz, [_dp, _i, _i]),
     "nsa_range_attn_bwd": (_i, [_vp] * 9 + [_dp, _i, _i, _i, _i, _vp, _sz, _i, _vp]),
@@ -96,3 +99,14 @@ def dims(B, Hq, Hkv, T, D, dtype):
 
 def workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)
+
+
+def profile_summary():
+    """{kernel name: (launches, total_ms)} since nsa_profile_enable(1)."""
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib().nsa_profile_summary(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.split()
+        out[name] = (int(cnt), float(ms))
+    return out

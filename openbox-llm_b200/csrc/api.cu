@@ -3,6 +3,11 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
+#include <string>
+#include <vector>
+
 #include "common.cuh"
 
 namespace nsa {
@@ -23,6 +28,32 @@ int* device_status_ptr() {
   int* p = nullptr;
   if (cudaGetSymbolAddress((void**)&p, g_device_status) != cudaSuccess) return nullptr;
   return p;
+}
+
+// ---- kernel accounting ---------------------------------------------------------------------
+static std::atomic<long long> g_launches{0};
+static std::atomic<int> g_profile{0};
+struct ProfRec { std::string name; cudaEvent_t e0, e1; };
+static std::mutex g_prof_mu;
+static std::vector<ProfRec> g_prof;
+static thread_local cudaEvent_t t_open_e1 = nullptr;
+
+void kernel_begin(const char* name, cudaStream_t st) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  t_open_e1 = nullptr;
+  if (!g_profile.load(std::memory_order_relaxed)) return;
+  ProfRec r;
+  r.name = name;
+  if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) return;
+  cudaEventRecord(r.e0, st);
+  t_open_e1 = r.e1;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof.push_back(r);
+}
+
+void kernel_end(cudaStream_t st) {
+  if (t_open_e1) cudaEventRecord(t_open_e1, st);
+  t_open_e1 = nullptr;
 }
 
 static int check_dims(const NsaDims* d) {
@@ -100,6 +131,39 @@ extern "C" int nsa_version(void) { return 100; }
 extern "C" int nsa_tc_supported(const NsaDims* dims, int block_size) {
   if (check_dims(dims) != NSA_OK) return 0;
   return tc_shape_ok(*dims, block_size) ? 1 : 0;
+}
+
+extern "C" long long nsa_launch_count(void) { return g_launches.load(); }
+
+extern "C" void nsa_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+  g_prof.clear();
+  g_profile.store(on ? 1 : 0);
+}
+
+extern "C" int nsa_profile_summary(char* buf, size_t cap) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  std::vector<std::string> names;
+  std::vector<double> ms;
+  std::vector<long long> cnt;
+  for (auto& r : g_prof) {
+    if (cudaEventSynchronize(r.e1) != cudaSuccess) continue;
+    float t = 0.f;
+    if (cudaEventElapsedTime(&t, r.e0, r.e1) != cudaSuccess) continue;
+    size_t i = 0;
+    for (; i < names.size(); ++i) if (names[i] == r.name) break;
+    if (i == names.size()) { names.push_back(r.name); ms.push_back(0); cnt.push_back(0); }
+    ms[i] += t; cnt[i] += 1;
+  }
+  size_t off = 0;
+  if (cap) buf[0] = 0;
+  for (size_t i = 0; i < names.size(); ++i) {
+    int n = snprintf(buf + off, off < cap ? cap - off : 0, "%s %lld %.6f\n", names[i].c_str(), cnt[i], ms[i]);
+    if (n < 0 || off + (size_t)n >= cap) break;
+    off += (size_t)n;
+  }
+  return (int)names.size();
 }
 
 extern "C" int nsa_device_status(void* stream) {

@@ -402,9 +402,9 @@ extern "C" int nsa_block_mean_pool_fwd(const void* x, void* out, int B, int Hkv,
   if (n == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == NSA_DTYPE_BF16)
-    mean_pool_fwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, T, D, block_size, n_blk, n);
+    { KernelScope ks("mean_pool_fwd_kernel", st); mean_pool_fwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, T, D, block_size, n_blk, n); }
   else
-    mean_pool_fwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const float*)x, (float*)out, T, D, block_size, n_blk, n);
+    { KernelScope ks("mean_pool_fwd_kernel", st); mean_pool_fwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const float*)x, (float*)out, T, D, block_size, n_blk, n); }
   NSA_LAUNCH_OK("mean_pool_fwd_kernel");
   return NSA_OK;
 }
@@ -417,9 +417,9 @@ extern "C" int nsa_block_mean_pool_bwd(const void* d_out, void* dx, int B, int H
   if (n == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == NSA_DTYPE_BF16)
-    mean_pool_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, T, D, block_size, n_blk, n);
+    { KernelScope ks("mean_pool_bwd_kernel", st); mean_pool_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, T, D, block_size, n_blk, n); }
   else
-    mean_pool_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const float*)d_out, (float*)dx, T, D, block_size, n_blk, n);
+    { KernelScope ks("mean_pool_bwd_kernel", st); mean_pool_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const float*)d_out, (float*)dx, T, D, block_size, n_blk, n); }
   NSA_LAUNCH_OK("mean_pool_bwd_kernel");
   return NSA_OK;
 }
@@ -434,9 +434,9 @@ extern "C" int nsa_block_compress_fwd(const void* x, const float* intra_pos, con
   cudaStream_t st = (cudaStream_t)stream;
   const size_t sm = (size_t)(block_size + D) * sizeof(float);
   if (dtype == NSA_DTYPE_BF16)
-    compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D, block_size, n_blk);
+    { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D, block_size, n_blk); }
   else
-    compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)out, (float*)nullptr, T, D, block_size, n_blk);
+    { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)out, (float*)nullptr, T, D, block_size, n_blk); }
   NSA_LAUNCH_OK("compress_fwd_kernel");
   return NSA_OK;
 }
@@ -470,13 +470,13 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
   const size_t tail = (size_t)(T - n_blk * block_size) * D * B * Hkv;
   if (rows > 0) {
     if (dtype == NSA_DTYPE_BF16) {
-      compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk);
-      compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk);
-      compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D);
+      { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk); }
+      { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk); }
+      { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D); }
     } else {
-      compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)nullptr, pooled, T, D, block_size, n_blk);
-      compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (const float*)d_out, (float*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk);
-      compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const float*)d_out, pooled, d_proj_w, rows, D);
+      { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)nullptr, pooled, T, D, block_size, n_blk); }
+      { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (const float*)d_out, (float*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk); }
+      { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const float*)d_out, pooled, d_proj_w, rows, D); }
     }
     NSA_LAUNCH_OK("compress_bwd kernels");
   } else {
@@ -484,12 +484,12 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
   }
   if (tail > 0) {
     if (dtype == NSA_DTYPE_BF16)
-      zero_tail_kernel<<<blocks_for(tail, 256), 256, 0, st>>>((__nv_bfloat16*)dx, T, D, n_blk * block_size, (size_t)B * Hkv);
+      { KernelScope ks("zero_tail_kernel", st); zero_tail_kernel<<<blocks_for(tail, 256), 256, 0, st>>>((__nv_bfloat16*)dx, T, D, n_blk * block_size, (size_t)B * Hkv); }
     else
-      zero_tail_kernel<<<blocks_for(tail, 256), 256, 0, st>>>((float*)dx, T, D, n_blk * block_size, (size_t)B * Hkv);
+      { KernelScope ks("zero_tail_kernel", st); zero_tail_kernel<<<blocks_for(tail, 256), 256, 0, st>>>((float*)dx, T, D, n_blk * block_size, (size_t)B * Hkv); }
     NSA_LAUNCH_OK("zero_tail_kernel");
   }
-  compress_bwd_final_kernel<<<1, 256, block_size * sizeof(float), st>>>(pool_logits, sum_dp, d_w, d_intra_pos, d_pool_logits, D, block_size);
+  { KernelScope ks("compress_bwd_final_kernel", st); compress_bwd_final_kernel<<<1, 256, block_size * sizeof(float), st>>>(pool_logits, sum_dp, d_w, d_intra_pos, d_pool_logits, D, block_size); }
   NSA_LAUNCH_OK("compress_bwd_final_kernel");
   return NSA_OK;
 }
@@ -513,6 +513,7 @@ extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* ls
     if (sm > 48 * 1024)                                                                         \
       NSA_CUDA_OK(cudaFuncSetAttribute(topn_kernel<TT, DD>,                                     \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));  \
+    KernelScope ks("topn_kernel", st);                                                          \
     topn_kernel<TT, DD><<<grid, 128, sm, st>>>((const TT*)q, (const TT*)k_cmp, lse_cmp,         \
         block_idx, importance_out, dims->B, dims->Hq, dims->Hkv, dims->T, n_blk, block_size,    \
         n_sel, scale);                                                                          \
@@ -571,10 +572,10 @@ extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int
   NSA_CUDA_OK(cudaMemsetAsync(bitmap, 0, rows * words * 4, st));
   const size_t n_entries = (size_t)B * Hkv * T * S;
   if (n_entries)
-    csr_mark_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(block_idx, bitmap, T, S, block_size, n_blk, words, n_entries);
-  csr_count_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, counts, words, rows);
-  csr_scan_kernel<<<1, 1024, 0, st>>>(counts, block_offsets, row_start, n_blk, rows);
-  csr_fill_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, row_start, q_of_block, pair_bh, n_blk, words, rows);
+    { KernelScope ks("csr_mark_kernel", st); csr_mark_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(block_idx, bitmap, T, S, block_size, n_blk, words, n_entries); }
+  { KernelScope ks("csr_count_kernel", st); csr_count_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, counts, words, rows); }
+  { KernelScope ks("csr_scan_kernel", st); csr_scan_kernel<<<1, 1024, 0, st>>>(counts, block_offsets, row_start, n_blk, rows); }
+  { KernelScope ks("csr_fill_kernel", st); csr_fill_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, row_start, q_of_block, pair_bh, n_blk, words, rows); }
   NSA_LAUNCH_OK("csr kernels");
   return NSA_OK;
 }
@@ -587,9 +588,9 @@ extern "C" int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const 
   if (rows == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (dims->dtype == NSA_DTYPE_BF16)
-    gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (__nv_bfloat16*)out, rows, dims->D);
+    { KernelScope ks("gate_fwd_kernel", st); gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (__nv_bfloat16*)out, rows, dims->D); }
   else
-    gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (float*)out, rows, dims->D);
+    { KernelScope ks("gate_fwd_kernel", st); gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (float*)out, rows, dims->D); }
   NSA_LAUNCH_OK("gate_fwd_kernel");
   return NSA_OK;
 }
@@ -603,9 +604,9 @@ extern "C" int nsa_gate_combine_bwd(const void* o_cmp, const void* o_slc, const 
   if (rows == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (dims->dtype == NSA_DTYPE_BF16)
-    gate_bwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)do_cmp, (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, (__nv_bfloat16*)d_gate_logits, rows, dims->D);
+    { KernelScope ks("gate_bwd_kernel", st); gate_bwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)do_cmp, (__nv_bfloat16*)do_slc, (__nv_bfloat16*)do_win, (__nv_bfloat16*)d_gate_logits, rows, dims->D); }
   else
-    gate_bwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (const float*)d_out, (float*)do_cmp, (float*)do_slc, (float*)do_win, (float*)d_gate_logits, rows, dims->D);
+    { KernelScope ks("gate_bwd_kernel", st); gate_bwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (const float*)d_out, (float*)do_cmp, (float*)do_slc, (float*)do_win, (float*)d_gate_logits, rows, dims->D); }
   NSA_LAUNCH_OK("gate_bwd_kernel");
   return NSA_OK;
 }

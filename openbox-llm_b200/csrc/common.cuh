@@ -67,6 +67,19 @@ __device__ __forceinline__ float warp_max(float x) {
 // error word raised by kernels whose bounded waits run out; defined in api.cu
 int* device_status_ptr();
 
+// Per-kernel accounting (api.cu): every kernel launch of the library sits inside a KernelScope,
+// which counts it and, when profiling is on, brackets it with CUDA events on its stream.
+void kernel_begin(const char* name, cudaStream_t st);
+void kernel_end(cudaStream_t st);
+struct KernelScope {
+  cudaStream_t st;
+  KernelScope(const char* name, cudaStream_t s) : st(s) { kernel_begin(name, s); }
+  ~KernelScope() { kernel_end(st); }
+};
+
+// kernel names carry the branch they serve: <prefix>_win / _cmp / _slc
+inline const char* branch_name(const char* const names[3], int kind) { return names[kind == 0 ? 0 : (kind == 1 ? 1 : 2)]; }
+
 // ---- SIMT kernel family (simt.cu) ---------------------------------------------------------
 struct AttnArgs {
   const void* q; const void* k; const void* v; const int32_t* block_idx;

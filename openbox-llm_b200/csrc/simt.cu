@@ -14,6 +14,8 @@ namespace nsa {
 namespace {
 
 constexpr int kWarps = 4;
+const char* const kFwdNames[3] = {"simt_fwd_win", "simt_fwd_cmp", "simt_fwd_slc"};
+const char* const kBwdNames[3] = {"simt_bwd_win", "simt_bwd_cmp", "simt_bwd_slc"};
 
 template <typename T, int D>
 __device__ __forceinline__ float dot_row(const T* __restrict__ row, const float* __restrict__ qs);
@@ -227,10 +229,10 @@ int launch_fwd(const AttnArgs& a, cudaStream_t st) {
   const size_t rows = (size_t)a.B * a.Hq * a.T;
   const unsigned grid = (unsigned)((rows + kWarps - 1) / kWarps);
   switch (a.D) {
-    case 16:  simt_fwd_kernel<T, 16><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 32:  simt_fwd_kernel<T, 32><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 64:  simt_fwd_kernel<T, 64><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 128: simt_fwd_kernel<T, 128><<<grid, kWarps * 32, 0, st>>>(a); break;
+    case 16: { KernelScope ks(branch_name(kFwdNames, a.kind), st); simt_fwd_kernel<T, 16><<<grid, kWarps * 32, 0, st>>>(a); } break;
+    case 32: { KernelScope ks(branch_name(kFwdNames, a.kind), st); simt_fwd_kernel<T, 32><<<grid, kWarps * 32, 0, st>>>(a); } break;
+    case 64: { KernelScope ks(branch_name(kFwdNames, a.kind), st); simt_fwd_kernel<T, 64><<<grid, kWarps * 32, 0, st>>>(a); } break;
+    case 128: { KernelScope ks(branch_name(kFwdNames, a.kind), st); simt_fwd_kernel<T, 128><<<grid, kWarps * 32, 0, st>>>(a); } break;
     default: set_error("head dim %d not in {16,32,64,128}", a.D); return NSA_ERR_UNSUPPORTED;
   }
   NSA_LAUNCH_OK("simt_fwd_kernel");
@@ -241,10 +243,10 @@ int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   const size_t rows = (size_t)a.B * a.Hq * a.T;
   const unsigned grid = (unsigned)((rows + kWarps - 1) / kWarps);
   switch (a.D) {
-    case 16:  simt_bwd_kernel<T, 16><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 32:  simt_bwd_kernel<T, 32><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 64:  simt_bwd_kernel<T, 64><<<grid, kWarps * 32, 0, st>>>(a); break;
-    case 128: simt_bwd_kernel<T, 128><<<grid, kWarps * 32, 0, st>>>(a); break;
+    case 16: { KernelScope ks(branch_name(kBwdNames, a.kind), st); simt_bwd_kernel<T, 16><<<grid, kWarps * 32, 0, st>>>(a); } break;
+    case 32: { KernelScope ks(branch_name(kBwdNames, a.kind), st); simt_bwd_kernel<T, 32><<<grid, kWarps * 32, 0, st>>>(a); } break;
+    case 64: { KernelScope ks(branch_name(kBwdNames, a.kind), st); simt_bwd_kernel<T, 64><<<grid, kWarps * 32, 0, st>>>(a); } break;
+    case 128: { KernelScope ks(branch_name(kBwdNames, a.kind), st); simt_bwd_kernel<T, 128><<<grid, kWarps * 32, 0, st>>>(a); } break;
     default: set_error("head dim %d not in {16,32,64,128}", a.D); return NSA_ERR_UNSUPPORTED;
   }
   NSA_LAUNCH_OK("simt_bwd_kernel");
@@ -267,9 +269,9 @@ int cast_f32_to(const float* src, void* dst, size_t n, int dtype, cudaStream_t s
   if (n == 0) return NSA_OK;
   const unsigned grid = (unsigned)min((size_t)148 * 16, (n + 255) / 256);
   if (dtype == NSA_DTYPE_BF16) {
-    cast_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), n);
+    { KernelScope ks("cast_kernel", st); cast_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), n); }
   } else {
-    cast_kernel<float><<<grid, 256, 0, st>>>(src, reinterpret_cast<float*>(dst), n);
+    { KernelScope ks("cast_kernel", st); cast_kernel<float><<<grid, 256, 0, st>>>(src, reinterpret_cast<float*>(dst), n); }
   }
   NSA_LAUNCH_OK("cast_kernel");
   return NSA_OK;

@@ -379,6 +379,8 @@ static int make_map(CUtensorMap* m, const void* base, int D, int rows, int heads
   return NSA_OK;
 }
 
+static const char* const kFwdNames[3] = {"tc_fwd_win", "tc_fwd_cmp", "tc_fwd_slc"};
+
 static int group_pad(int G) {
   int gp = 1;
   while (gp < G) gp <<= 1;
@@ -427,10 +429,10 @@ int tc_attn_fwd(const AttnArgs& a, cudaStream_t st) {
   dim3 grid(p.n_qtiles, a.B * a.Hkv);
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tc_fwd_kernel<128><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p);
+    { KernelScope ks(branch_name(kFwdNames, a.kind), st); tc_fwd_kernel<128><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p); }
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tc_fwd_kernel<64><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p);
+    { KernelScope ks(branch_name(kFwdNames, a.kind), st); tc_fwd_kernel<64><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p); }
   }
   NSA_LAUNCH_OK("tc_fwd_kernel");
   return NSA_OK;
