@@ -65,7 +65,7 @@ int nsa_tc_supported(const NsaDims* dims, int block_size);
 int nsa_range_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                        const NsaDims* dims, int Lk, int mode, int window, int block_size,
                        int impl, void* stream);
-size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int impl);
+size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int mode, int window, int impl);
 int nsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
                        const void* d_o, void* dq, void* dk, void* dv,
                        const NsaDims* dims, int Lk, int mode, int window, int block_size,

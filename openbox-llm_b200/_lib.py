@@ -35,7 +35,7 @@ SIGNATURES = {
     "nsa_profile_enable": (None, [_i]),
     "nsa_profile_summary": (_i, [ctypes.c_char_p, _sz]),
     "nsa_range_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _dp, _i, _i, _i, _i, _i, _vp]),
-    "nsa_range_attn_bwd_workspace_bytes": (_sz, [_dp, _i, _i]),
+    "nsa_range_attn_bwd_workspace_bytes": (_sz, [_dp, _i, _i, _i, _i]),
     "nsa_range_attn_bwd": (_i, [_vp] * 9 + [_dp, _i, _i, _i, _i, _vp, _sz, _i, _vp]),
     "nsa_selection_fwd_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
     "nsa_selection_fwd": (_i, [_vp] * 6 + [_dp, _i, _i, _vp, _sz, _i, _vp]),

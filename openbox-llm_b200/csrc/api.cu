@@ -203,13 +203,14 @@ extern "C" int nsa_range_attn_fwd(const void* q, const void* k, const void* v, v
   return simt_attn_fwd(a, dims->dtype, (cudaStream_t)stream);
 }
 
-extern "C" size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int impl) {
+extern "C" size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int mode,
+                                                     int window, int impl) {
   if (check_dims(dims) != NSA_OK) return 0;
   int rc;
   size_t need = simt_bwd_ws(dims, Lk);
   if (use_tc(dims, 64, impl, &rc)) {
     AttnArgs a = base_args(dims, Lk);
-    a.kind = 0;
+    a.kind = mode; a.window = window > 0 ? window : 1;
     need = need > tc_attn_bwd_workspace(a) ? need : tc_attn_bwd_workspace(a);
   }
   return need;

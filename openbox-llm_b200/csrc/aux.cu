@@ -306,7 +306,8 @@ __global__ void csr_scan_kernel(const int32_t* __restrict__ counts, int32_t* __r
 // one warp per row: emit set bits in ascending t
 __global__ void csr_fill_kernel(const uint32_t* __restrict__ bitmap, const int32_t* __restrict__ row_start,
                                 int32_t* __restrict__ q_of_block, int32_t* __restrict__ pair_bh,
-                                int n_blk, int words, size_t rows) {
+                                int n_blk, int words, size_t rows, const int32_t* __restrict__ idx,
+                                int32_t* __restrict__ pair_of_slot, int T_, int S) {
   const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -327,8 +328,15 @@ __global__ void csr_fill_kernel(const uint32_t* __restrict__ bitmap, const int32
     while (rem) {
       const int bit = __ffs(rem) - 1;
       rem &= rem - 1;
-      q_of_block[p] = w * 32 + bit;
+      const int tq = w * 32 + bit;
+      q_of_block[p] = tq;
       pair_bh[p] = bh;
+      if (pair_of_slot) {   // which slot of query tq names this block
+        const int jb = (int)(row % n_blk);
+        const size_t e0 = ((size_t)bh * T_ + tq) * S;
+        for (int sl = 0; sl < S; ++sl)
+          if (idx[e0 + sl] == jb) { pair_of_slot[e0 + sl] = p; break; }
+      }
       ++p;
     }
     pos += __shfl_sync(0xffffffffu, incl, 31);
@@ -542,19 +550,19 @@ extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* ls
 
 extern "C" size_t nsa_csr_workspace_bytes(int B, int Hkv, int T, int S, int block_size) {
   (void)S;
-  const size_t n_blk = block_size > 0 ? T / block_size : 0;
+  const size_t n_blk = block_size > 0 ? (T + block_size - 1) / block_size : 0;
   const size_t rows = (size_t)B * Hkv * n_blk;
   const size_t words = (T + 31) / 32;
   return align_up(rows * words * 4, 256) + 2 * align_up(rows * 4, 256);
 }
 
-extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int Hkv, int T, int S,
-                                            int block_size, int32_t* q_of_block,
-                                            int32_t* block_offsets, int32_t* pair_bh, void* workspace,
-                                            size_t workspace_bytes, void* stream) {
-  NSA_CHECK_ARG(block_size > 0 && B >= 0 && Hkv >= 0 && T >= 0 && S >= 0, "bad sizes");
-  cudaStream_t st = (cudaStream_t)stream;
-  const int n_blk = T / block_size;
+namespace nsa {
+// CSR over n_blk blocks (the public entry point uses T / block_size, as the reference does;
+// the tcgen05 backward also counts a ragged tail block).  pair_of_slot, when given, receives
+// for every (b, hkv, t, slot) the pair index of that selection or -1.
+int build_csr_internal(const int32_t* block_idx, int B, int Hkv, int T, int S, int block_size,
+                       int n_blk, int32_t* q_of_block, int32_t* block_offsets, int32_t* pair_bh,
+                       int32_t* pair_of_slot, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   const size_t rows = (size_t)B * Hkv * n_blk;
   const int words = (T + 31) / 32;
   if ((size_t)B * Hkv == 0) return NSA_OK;
@@ -562,7 +570,8 @@ extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int
     NSA_CUDA_OK(cudaMemsetAsync(block_offsets, 0, (size_t)B * Hkv * sizeof(int32_t), st));
     return NSA_OK;
   }
-  if (!workspace || workspace_bytes < nsa_csr_workspace_bytes(B, Hkv, T, S, block_size)) {
+  const size_t need = align_up(rows * words * 4, 256) + 2 * align_up(rows * 4, 256);
+  if (!workspace || workspace_bytes < need) {
     set_error("csr workspace too small");
     return NSA_ERR_WORKSPACE;
   }
@@ -571,13 +580,28 @@ extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int
   int32_t* row_start = (int32_t*)((char*)counts + align_up(rows * 4, 256));
   NSA_CUDA_OK(cudaMemsetAsync(bitmap, 0, rows * words * 4, st));
   const size_t n_entries = (size_t)B * Hkv * T * S;
-  if (n_entries)
-    { KernelScope ks("csr_mark_kernel", st); csr_mark_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(block_idx, bitmap, T, S, block_size, n_blk, words, n_entries); }
+  if (pair_of_slot && n_entries)
+    NSA_CUDA_OK(cudaMemsetAsync(pair_of_slot, 0xff, n_entries * sizeof(int32_t), st));
+  if (n_entries) {
+    KernelScope ks("csr_mark_kernel", st);
+    csr_mark_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(block_idx, bitmap, T, S, block_size, n_blk, words, n_entries);
+  }
   { KernelScope ks("csr_count_kernel", st); csr_count_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, counts, words, rows); }
   { KernelScope ks("csr_scan_kernel", st); csr_scan_kernel<<<1, 1024, 0, st>>>(counts, block_offsets, row_start, n_blk, rows); }
-  { KernelScope ks("csr_fill_kernel", st); csr_fill_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, row_start, q_of_block, pair_bh, n_blk, words, rows); }
+  { KernelScope ks("csr_fill_kernel", st); csr_fill_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, row_start, q_of_block, pair_bh, n_blk, words, rows, block_idx, pair_of_slot, T, S); }
   NSA_LAUNCH_OK("csr kernels");
   return NSA_OK;
+}
+}  // namespace nsa
+
+extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int Hkv, int T, int S,
+                                            int block_size, int32_t* q_of_block,
+                                            int32_t* block_offsets, int32_t* pair_bh, void* workspace,
+                                            size_t workspace_bytes, void* stream) {
+  NSA_CHECK_ARG(block_size > 0 && B >= 0 && Hkv >= 0 && T >= 0 && S >= 0, "bad sizes");
+  return build_csr_internal(block_idx, B, Hkv, T, S, block_size, T / block_size, q_of_block,
+                            block_offsets, pair_bh, nullptr, workspace, workspace_bytes,
+                            (cudaStream_t)stream);
 }
 
 extern "C" int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const void* o_win,

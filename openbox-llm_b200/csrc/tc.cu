@@ -15,6 +15,7 @@
 // operand.  The running maximum is only raised when it grows by more than 8 (log2 units), so
 // the O accumulator in TMEM is rescaled rarely.
 #include "tc_common.cuh"
+#include "tc_host.cuh"
 
 namespace nsa {
 namespace tc {
@@ -345,47 +346,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         l_sum > 0.f ? (m_used + log2f(l_sum)) * kLn2 : kLseEmpty;
 }
 
-// ---- host side -------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
-            cudaSuccess && qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-
-// 3-D map over a [heads, rows, D] bf16 tensor: box = 64 elements x box_rows x box_heads
-static int make_map(CUtensorMap* m, const void* base, int D, int rows, int heads, int box_rows,
-                    int box_heads) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) { set_error("cuTensorMapEncodeTiled is not available"); return NSA_ERR_CUDA; }
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows * D * 2};
-  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)box_heads};
-  cuuint32_t estr[3] = {1u, 1u, 1u};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d", (int)r); return NSA_ERR_CUDA; }
-  return NSA_OK;
-}
-
 static const char* const kFwdNames[3] = {"tc_fwd_win", "tc_fwd_cmp", "tc_fwd_slc"};
-
-static int group_pad(int G) {
-  int gp = 1;
-  while (gp < G) gp <<= 1;
-  return gp;
-}
 
 }  // namespace tc
 
@@ -436,28 +397,6 @@ int tc_attn_fwd(const AttnArgs& a, cudaStream_t st) {
   }
   NSA_LAUNCH_OK("tc_fwd_kernel");
   return NSA_OK;
-}
-
-size_t tc_attn_bwd_workspace(const AttnArgs& a) {
-  return 2 * align_up((size_t)a.B * a.Hkv * a.Lk * a.D * sizeof(float), 256);
-}
-
-int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
-  // backward still runs on the CUDA-core kernels
-  AttnArgs b = a;
-  const size_t n = (size_t)a.B * a.Hkv * a.Lk * a.D;
-  if (ws_bytes < tc_attn_bwd_workspace(a) || !ws) { set_error("backward workspace too small"); return NSA_ERR_WORKSPACE; }
-  void* dk = (void*)a.dk_acc;
-  void* dv = (void*)a.dv_acc;
-  b.dk_acc = (float*)ws;
-  b.dv_acc = (float*)((char*)ws + align_up(n * sizeof(float), 256));
-  NSA_CUDA_OK(cudaMemsetAsync(b.dk_acc, 0, n * sizeof(float), st));
-  NSA_CUDA_OK(cudaMemsetAsync(b.dv_acc, 0, n * sizeof(float), st));
-  int rc = simt_attn_bwd(b, NSA_DTYPE_BF16, st);
-  if (rc != NSA_OK) return rc;
-  rc = cast_f32_to(b.dk_acc, dk, n, NSA_DTYPE_BF16, st);
-  if (rc != NSA_OK) return rc;
-  return cast_f32_to(b.dv_acc, dv, n, NSA_DTYPE_BF16, st);
 }
 
 }  // namespace nsa

@@ -1,0 +1,560 @@
+// tcgen05 / TMEM backward of the three attention branches, key-tile outer.
+//
+// One CTA owns a tile of 64 keys of one (batch, kv head): K and V of the tile are loaded
+// once (TMA), dK^T and dV^T of the tile stay in TMEM for the whole CTA and are written once,
+// with no atomics.  The CTA walks the (query, head) rows that attend the tile, 128 rows at a
+// time (nq queries x the G heads of the group):
+//   window      queries [64 j, 64 j + 63 + W - 1]
+//   compression queries t >= (64 j + 1) * Bsz - 1
+//   selection   the queries that list block j, from the block -> query CSR
+// Q and dO rows are gathered with 16-byte cp.async into 128B-swizzled tiles (double buffered).
+// Per row tile, five MMAs:
+//   S    = Q K^T          (A: Q  K-major,   B: K  K-major)
+//   dP   = dO V^T         (A: dO K-major,   B: V  K-major)
+//   dV^T += dO^T P        (A: dO MN-major,  B: P  MN-major)      P, dS: bf16 tiles the threads
+//   dK^T += Q^T dS        (A: Q  MN-major,  B: dS MN-major)      write to shared memory
+//   dQ   = dS K           (A: dS K-major,   B: K  MN-major)
+// with p = exp2(s*scale*log2e - lse*log2e) and dS = scale * p * (dP - delta) computed by the
+// thread that owns the row (TMEM lane = row).  dQ of a row is the sum over the key tiles it
+// attends; every (row tile, key tile) result is written as a bf16 partial and a second kernel
+// adds the partials of each query in fp32.
+#include "tc_common.cuh"
+#include "tc_host.cuh"
+
+namespace nsa {
+namespace tc {
+
+struct BwdArgs {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* d_o;
+  const float* lse;
+  const float* delta;
+  const int32_t* q_of_block;
+  const int32_t* offsets;      // [B*Hkv, n_ktiles + 1] global pair offsets (selection)
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  __nv_bfloat16* dq_part;
+  int* status;
+  int B, Hq, Hkv, T, Lk, G, nq;
+  int kind, window, block_size;
+  int n_ktiles, n_slots;
+  float scale, scale_log2;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+constexpr int kRowTileBytes = kRows * 128 * 2;   // Q or dO row tile: always two 64-element slabs
+constexpr int kPBytes = kRows * 128;             // P or dS: 128 rows x 64 keys bf16
+
+__host__ __device__ inline size_t bwd_smem_bytes(int D) {
+  return (size_t)2 * kKeys * 128 * (D / 64)      // K, V
+         + 4 * (size_t)kRowTileBytes             // Q, dO x 2 stages
+         + 2 * (size_t)kPBytes                   // P, dS
+         + 256 + 2 * 128 * 4                     // barriers, row tables
+         + 1024;
+}
+
+template <int D>
+__global__ void __launch_bounds__(128, 1)
+tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const BwdArgs p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kKVBytes = kKeys * 128 * kSlabs;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 128, kColDV = 256, kColDK = 320;
+  constexpr uint32_t kIdescS = idesc_bf16(128, kKeys, 0, 0);     // rows x keys
+  constexpr uint32_t kIdescT = idesc_bf16(128, kKeys, 1, 1);     // d x keys, both MN-major
+  constexpr uint32_t kIdescDQ = idesc_bf16(128, D, 0, 1);        // rows x d
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + kKVBytes;
+  uint8_t* sQ = sV + kKVBytes;                  // [2] stages
+  uint8_t* sDO = sQ + 2 * kRowTileBytes;        // [2]
+  uint8_t* sP = sDO + 2 * kRowTileBytes;
+  uint8_t* sDS = sP + kPBytes;
+  uint64_t* bars = (uint64_t*)(sDS + kPBytes);
+  uint64_t* bar_kv = bars + 0;
+  uint64_t* bar_sp = bars + 1;
+  uint64_t* bar_acc = bars + 2;
+  uint32_t* s_tmem = (uint32_t*)(bars + 4);
+  volatile int* s_abort = (volatile int*)(s_tmem + 1);
+  int* s_rowt = (int*)(s_tmem + 4);             // [2][128] query position of each row, -1 = none
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int j = blockIdx.x;                      // key tile
+  const int bh = blockIdx.y;
+  const int b = bh / p.Hkv, hkv = bh % p.Hkv;
+  const int key0 = j * kKeys;
+  const int ql = tid / p.G, g = tid % p.G;
+  const int head = hkv * p.G + g;
+  const bool row_slot_ok = ql < p.nq;
+
+  // ---- the queries that attend this key tile ---------------------------------------------
+  int t_lo = 0, n_q = 0, pair_base = 0;
+  if (p.kind == 0) {
+    t_lo = key0;
+    n_q = min(p.T - 1, key0 + kKeys - 1 + p.window - 1) - t_lo + 1;
+  } else if (p.kind == 1) {
+    t_lo = (key0 + 1) * p.block_size - 1;
+    n_q = p.T - t_lo;
+  } else {
+    pair_base = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j);
+    n_q = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j + 1) - pair_base;
+  }
+  n_q = max(n_q, 0);
+  const int n_rt = (n_q + p.nq - 1) / p.nq;
+
+  if (n_rt == 0) {   // nobody attends these keys: their gradients are zero
+    for (int i = tid; i < kKeys * D / 8; i += 128) {
+      const int key = key0 + i / (D / 8);
+      if (key < p.Lk) {
+        const size_t off = ((size_t)bh * p.Lk + key) * D + (i % (D / 8)) * 8;
+        *reinterpret_cast<uint4*>(p.dk + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(p.dv + off) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_sp, 1);
+    mbar_init(bar_acc, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+  }
+  if (D == 64) {   // the second slab of the row tiles is never gathered: keep it zero
+    for (int i = tid; i < 4 * (kRows * 128) / 16; i += 128) {
+      const int buf = i / ((kRows * 128) / 16), o16 = i % ((kRows * 128) / 16);
+      uint8_t* base = (buf < 2 ? sQ + buf * kRowTileBytes : sDO + (buf - 2) * kRowTileBytes) + kRows * 128;
+      *reinterpret_cast<uint4*>(base + o16 * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  __syncthreads();
+  if (*s_abort) return;
+
+  if (warp == 0) {
+    tmem_alloc(s_tmem, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+
+  if (tid == 0) {
+    mbar_expect_tx(bar_kv, 2 * kKVBytes);
+#pragma unroll
+    for (int s = 0; s < kSlabs; ++s) {
+      tma_load_3d(sK + s * (kKeys * 128), &tm_k, bar_kv, s * 64, key0, bh);
+      tma_load_3d(sV + s * (kKeys * 128), &tm_v, bar_kv, s * 64, key0, bh);
+    }
+  }
+
+  // row metadata of tile i for this thread's row
+  auto row_query = [&](int i) -> int {
+    const int qi = i * p.nq + ql;
+    if (!row_slot_ok || qi >= n_q) return -1;
+    if (p.kind == 2) return __ldg(p.q_of_block + pair_base + qi);
+    return t_lo + qi;
+  };
+  // gather the Q and dO rows of tile i into stage st (16-byte chunks, 128B swizzle)
+  auto gather = [&](int st, const int* rowt) {
+    constexpr int kChunks = D / 8;                 // 16-byte chunks per row
+    constexpr int kRowsPerPass = 128 / kChunks;
+    const int c = tid % kChunks;
+    const uint32_t q_base = smem_u32(sQ + st * kRowTileBytes), do_base = smem_u32(sDO + st * kRowTileBytes);
+#pragma unroll 4
+    for (int r = tid / kChunks; r < kRows; r += kRowsPerPass) {
+      const int tq = rowt[r];
+      const int rg = r % p.G;
+      const size_t src = tq >= 0 ? ((size_t)(b * p.Hq + hkv * p.G + rg) * p.T + tq) * D + c * 8 : 0;
+      const uint32_t dst = (uint32_t)((c >> 3) * (kRows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+      const uint32_t nbytes = tq >= 0 ? 16u : 0u;   // 0 -> the chunk is zero-filled
+      cp_async16(q_base + dst, p.q + src, nbytes);
+      cp_async16(do_base + dst, p.d_o + src, nbytes);
+    }
+    cp_async_commit();
+  };
+
+  int t_cur = row_query(0);
+  s_rowt[tid] = t_cur;
+  __syncthreads();
+  gather(0, s_rowt);
+  float lse2_cur = 0.f, delta_cur = 0.f;
+  if (t_cur >= 0) {
+    const size_t ri = (size_t)(b * p.Hq + head) * p.T + t_cur;
+    lse2_cur = __ldg(p.lse + ri) * kLog2e;
+    delta_cur = __ldg(p.delta + ri);
+  }
+
+  for (int i = 0; i < n_rt; ++i) {
+    const int st = i & 1;
+    // metadata of the next tile (global loads overlap the waits below)
+    int t_next = -1;
+    float lse2_next = 0.f, delta_next = 0.f;
+    if (i + 1 < n_rt) {
+      t_next = row_query(i + 1);
+      s_rowt[(st ^ 1) * 128 + tid] = t_next;
+      if (t_next >= 0) {
+        const size_t ri = (size_t)(b * p.Hq + head) * p.T + t_next;
+        lse2_next = __ldg(p.lse + ri) * kLog2e;
+        delta_next = __ldg(p.delta + ri);
+      }
+    }
+    cp_async_wait_all();        // gather(i) has landed
+    fence_proxy_async();        // ... and is visible to the tensor core
+    __syncthreads();
+    if (tid == 0) {
+      if (i == 0) mbar_wait(bar_kv, 0, p.status, s_abort, 32);
+      tc_fence_after();
+      const uint32_t qa = smem_u32(sQ + st * kRowTileBytes), da = smem_u32(sDO + st * kRowTileBytes);
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+        mma_ss(tmem + kColS, desc_kmajor(qa + slab * (kRows * 128) + in),
+               desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescS, kk > 0);
+      }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+        mma_ss(tmem + kColDP, desc_kmajor(da + slab * (kRows * 128) + in),
+               desc_kmajor(va + slab * (kKeys * 128) + in), kIdescS, kk > 0);
+      }
+      tc_commit(bar_sp);
+    }
+    if (i + 1 < n_rt) gather(st ^ 1, s_rowt + (st ^ 1) * 128);
+
+    // valid key columns of this row: one range [lo, hi]
+    int lo = 0, hi = -1;
+    if (t_cur >= 0) {
+      if (p.kind == 0) {
+        lo = max(0, t_cur - p.window + 1 - key0);
+        hi = min(kKeys - 1, t_cur - key0);
+      } else if (p.kind == 1) {
+        hi = min(kKeys - 1, min(p.Lk, (t_cur + 1) / p.block_size) - 1 - key0);
+      } else {
+        hi = min(kKeys - 1, min(t_cur, p.T - 1) - key0);
+      }
+    }
+    mbar_wait(bar_sp, i & 1, p.status, s_abort, 64);
+    tc_fence_after();
+    __syncwarp();
+    const uint32_t p_row = smem_u32(sP) + tid * 128, ds_row = smem_u32(sDS) + tid * 128;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t rs[32], rp[32];
+      tmem_ld32(lane_base + kColS + half * 32, rs);
+      tmem_ld32(lane_base + kColDP + half * 32, rp);
+      tmem_wait_ld();
+      uint32_t pp[16], pd[16];
+#pragma unroll
+      for (int c2 = 0; c2 < 16; ++c2) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int c = half * 32 + c2 * 2 + e;
+          const bool ok = (c >= lo) && (c <= hi);
+          const float pr = ok ? ex2(__uint_as_float(rs[c2 * 2 + e]) * p.scale_log2 - lse2_cur) : 0.f;
+          pv[e] = pr;
+          dv[e] = pr * (__uint_as_float(rp[c2 * 2 + e]) - delta_cur) * p.scale;
+        }
+        pp[c2] = pack_bf16(pv[0], pv[1]);
+        pd[c2] = pack_bf16(dv[0], dv[1]);
+      }
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        const uint32_t chunk = (uint32_t)((half * 4 + k4) ^ (tid & 7)) << 4;
+        st_shared_v4(p_row + chunk, pp[k4 * 4], pp[k4 * 4 + 1], pp[k4 * 4 + 2], pp[k4 * 4 + 3]);
+        st_shared_v4(ds_row + chunk, pd[k4 * 4], pd[k4 * 4 + 1], pd[k4 * 4 + 2], pd[k4 * 4 + 3]);
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t qa = smem_u32(sQ + st * kRowTileBytes), da = smem_u32(sDO + st * kRowTileBytes);
+      const uint32_t pa = smem_u32(sP), dsa = smem_u32(sDS), ka = smem_u32(sK);
+#pragma unroll
+      for (int kk = 0; kk < kRows / 16; ++kk) {      // contraction over the 128 rows
+        mma_ss(tmem + kColDV, desc_mnmajor(da + kk * 2048, kRows * 128), desc_mnmajor(pa + kk * 2048, 0),
+               kIdescT, (i > 0) || (kk > 0));
+      }
+#pragma unroll
+      for (int kk = 0; kk < kRows / 16; ++kk) {
+        mma_ss(tmem + kColDK, desc_mnmajor(qa + kk * 2048, kRows * 128), desc_mnmajor(dsa + kk * 2048, 0),
+               kIdescT, (i > 0) || (kk > 0));
+      }
+#pragma unroll
+      for (int kk = 0; kk < kKeys / 16; ++kk) {      // contraction over the 64 keys
+        mma_ss(tmem + kColDQ, desc_kmajor(dsa + kk * 32), desc_mnmajor(ka + kk * 2048, kKeys * 128),
+               kIdescDQ, kk > 0);
+      }
+      tc_commit(bar_acc);
+    }
+    mbar_wait(bar_acc, i & 1, p.status, s_abort, 128);
+    tc_fence_after();
+    __syncwarp();
+    // dQ partial of this (row tile, key tile)
+    size_t pidx = 0;
+    if (t_cur >= 0) {
+      if (p.kind == 2) {
+        pidx = ((size_t)(pair_base + i * p.nq + ql) * p.G + g) * D;
+      } else {
+        const int slot = p.kind == 0 ? j - (max(0, t_cur - p.window + 1) >> 6) : j;
+        pidx = ((((size_t)bh * p.T + t_cur) * p.n_slots + slot) * p.G + g) * D;
+      }
+    }
+#pragma unroll
+    for (int cc = 0; cc < D / 32; ++cc) {
+      uint32_t r32[32];
+      tmem_ld32(lane_base + kColDQ + cc * 32, r32);
+      tmem_wait_ld();
+      if (t_cur >= 0) {
+        uint4* dst = reinterpret_cast<uint4*>(p.dq_part + pidx + cc * 32);
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 u;
+          u.x = pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1]));
+          u.y = pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3]));
+          u.z = pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5]));
+          u.w = pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7]));
+          dst[v4] = u;
+        }
+      }
+    }
+    tc_fence_before();
+    t_cur = t_next; lse2_cur = lse2_next; delta_cur = delta_next;
+  }
+
+  // ---- dK^T, dV^T: lane = d, column = key ---------------------------------------------------
+  __syncwarp();
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    __nv_bfloat16* dst = which == 0 ? p.dv : p.dk;
+    const uint32_t col = which == 0 ? kColDV : kColDK;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t r32[32];
+      tmem_ld32(lane_base + col + half * 32, r32);
+      tmem_wait_ld();
+      if (tid < D) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int key = key0 + half * 32 + c;
+          if (key < p.Lk)
+            dst[((size_t)bh * p.Lk + key) * D + tid] = __float2bfloat16_rn(__uint_as_float(r32[c]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+// delta[b,h,t] = sum_d dO * O (fp32), one warp per row
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o,
+                             float* __restrict__ delta, size_t rows, int D) {
+  const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d_o + row * D + d));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + row * D + d));
+    s = fmaf(a.x, c.x, fmaf(a.y, c.y, s));
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[row] = s;
+}
+
+// dq[b, hkv*G+g, t, :] = sum over the partial slots of query (bh, t); one thread per 8 elements
+template <int D>
+__global__ void dq_reduce_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ pair_of_slot,
+                                 __nv_bfloat16* __restrict__ dq, int B, int Hq, int Hkv, int T, int G,
+                                 int kind, int window, int block_size, int Lk, int n_slots, int S) {
+  constexpr int kVec = D / 8;
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)B * Hkv * T * G * kVec;
+  if (gid >= total) return;
+  const int v = (int)(gid % kVec);
+  const int g = (int)((gid / kVec) % G);
+  const int t = (int)((gid / ((size_t)kVec * G)) % T);
+  const size_t bh = gid / ((size_t)kVec * G * T);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  auto add = [&](size_t row_index) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(part + (row_index * G + g) * D + v * 8));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      acc[2 * e] += f.x;
+      acc[2 * e + 1] += f.y;
+    }
+  };
+  if (kind == 2) {
+    const int32_t* ps = pair_of_slot + (bh * T + t) * S;
+    for (int s = 0; s < S; ++s) {
+      const int pr = __ldg(ps + s);
+      if (pr >= 0) add((size_t)pr);
+    }
+  } else {
+    int first, last;   // key tiles this query attends
+    if (kind == 0) { first = max(0, t - window + 1) >> 6; last = t >> 6; }
+    else { first = 0; last = (min(Lk, (t + 1) / block_size) - 1); last = last < 0 ? -1 : last >> 6; }
+    for (int jt = first; jt <= last; ++jt) {
+      const int slot = kind == 0 ? jt - first : jt;
+      add((bh * T + t) * n_slots + slot);
+    }
+  }
+  const int b = (int)(bh / Hkv), hkv = (int)(bh % Hkv);
+  uint4 u;
+  u.x = pack_bf16(acc[0], acc[1]); u.y = pack_bf16(acc[2], acc[3]);
+  u.z = pack_bf16(acc[4], acc[5]); u.w = pack_bf16(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(dq + (((size_t)b * Hq + hkv * G + g) * T + t) * D + v * 8) = u;
+}
+
+static const char* const kBwdNames[3] = {"tc_bwd_win", "tc_bwd_cmp", "tc_bwd_slc"};
+static const char* const kRedNames[3] = {"dq_reduce_win", "dq_reduce_cmp", "dq_reduce_slc"};
+
+struct BwdPlan {
+  int n_ktiles, n_slots, nq;
+  size_t cap_pairs;          // selection: pairs the CSR may hold
+  size_t off_delta, off_part, off_csr_ws, off_qob, off_off, off_pbh, off_pos, total;
+};
+
+static BwdPlan plan_bwd(const AttnArgs& a) {
+  BwdPlan pl;
+  const int G = a.Hq / a.Hkv;
+  pl.nq = kRows / G;
+  pl.n_ktiles = (a.Lk + kKeys - 1) / kKeys;
+  const size_t units = (size_t)a.B * a.Hkv;
+  size_t part_rows;
+  if (a.kind == 2) {
+    pl.n_slots = a.S;
+    pl.cap_pairs = units * a.T * a.S;
+    part_rows = pl.cap_pairs;
+  } else {
+    pl.n_slots = a.kind == 0 ? (a.window + kKeys - 2) / kKeys + 1 : pl.n_ktiles;
+    pl.cap_pairs = 0;
+    part_rows = units * a.T * pl.n_slots;
+  }
+  size_t off = 0;
+  pl.off_delta = off; off += align_up((size_t)a.B * a.Hq * a.T * sizeof(float), 256);
+  pl.off_part = off; off += align_up(part_rows * G * a.D * 2, 256);
+  pl.off_csr_ws = pl.off_qob = pl.off_off = pl.off_pbh = pl.off_pos = off;
+  if (a.kind == 2) {
+    pl.off_csr_ws = off; off += align_up(nsa_csr_workspace_bytes(a.B, a.Hkv, pl.n_ktiles * kKeys, a.S, kKeys), 256);
+    pl.off_qob = off; off += align_up(pl.cap_pairs * 4, 256);
+    pl.off_pbh = off; off += align_up(pl.cap_pairs * 4, 256);
+    pl.off_off = off; off += align_up(units * (pl.n_ktiles + 1) * 4, 256);
+    pl.off_pos = off; off += align_up(pl.cap_pairs * 4, 256);
+  }
+  pl.total = off;
+  return pl;
+}
+
+}  // namespace tc
+
+// defined in aux.cu: CSR with an explicit block count and the (query, slot) -> pair map
+int build_csr_internal(const int32_t* block_idx, int B, int Hkv, int T, int S, int block_size,
+                       int n_blk, int32_t* q_of_block, int32_t* block_offsets, int32_t* pair_bh,
+                       int32_t* pair_of_slot, void* workspace, size_t workspace_bytes, cudaStream_t st);
+
+size_t tc_attn_bwd_workspace(const AttnArgs& a) { return tc::plan_bwd(a).total; }
+
+int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
+  using namespace tc;
+  const BwdPlan pl = plan_bwd(a);
+  if (!ws || ws_bytes < pl.total) {
+    set_error("backward workspace too small: need %zu bytes", pl.total);
+    return NSA_ERR_WORKSPACE;
+  }
+  char* base = (char*)ws;
+  const int G = a.Hq / a.Hkv;
+  BwdArgs p;
+  p.q = (const __nv_bfloat16*)a.q;
+  p.d_o = (const __nv_bfloat16*)a.d_o;
+  p.lse = a.lse;
+  p.delta = (float*)(base + pl.off_delta);
+  p.q_of_block = (const int32_t*)(base + pl.off_qob);
+  p.offsets = (const int32_t*)(base + pl.off_off);
+  p.dk = (__nv_bfloat16*)a.dk_acc;     // the API passes the dk / dv outputs through these fields
+  p.dv = (__nv_bfloat16*)a.dv_acc;
+  p.dq_part = (__nv_bfloat16*)(base + pl.off_part);
+  p.status = device_status_ptr();
+  if (!p.status) { set_error("device status word unavailable"); return NSA_ERR_CUDA; }
+  p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.T = a.T; p.Lk = a.Lk; p.G = G; p.nq = pl.nq;
+  p.kind = a.kind; p.window = a.window; p.block_size = a.block_size;
+  p.n_ktiles = pl.n_ktiles; p.n_slots = pl.n_slots;
+  p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
+
+  const size_t rows = (size_t)a.B * a.Hq * a.T;
+  {
+    KernelScope ks("delta_kernel", st);
+    delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)a.d_o,
+                                                             (const __nv_bfloat16*)a.o,
+                                                             (float*)(base + pl.off_delta), rows, a.D);
+  }
+  NSA_LAUNCH_OK("delta_kernel");
+  int32_t* pair_of_slot = (int32_t*)(base + pl.off_pos);
+  if (a.kind == 2) {
+    int rc = build_csr_internal(a.block_idx, a.B, a.Hkv, a.T, a.S, kKeys, pl.n_ktiles,
+                                (int32_t*)(base + pl.off_qob), (int32_t*)(base + pl.off_off),
+                                (int32_t*)(base + pl.off_pbh), pair_of_slot, base + pl.off_csr_ws,
+                                pl.off_qob - pl.off_csr_ws, st);
+    if (rc != NSA_OK) return rc;
+  }
+  CUtensorMap tm_k, tm_v;
+  int rc = make_map(&tm_k, a.k, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
+  if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
+  if (rc != NSA_OK) return rc;
+  const size_t smem = bwd_smem_bytes(a.D);
+  dim3 grid(pl.n_ktiles, a.B * a.Hkv);
+  if (a.D == 128) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KernelScope ks(branch_name(kBwdNames, a.kind), st);
+    tc_bwd_kernel<128><<<grid, 128, smem, st>>>(tm_k, tm_v, p);
+  } else {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KernelScope ks(branch_name(kBwdNames, a.kind), st);
+    tc_bwd_kernel<64><<<grid, 128, smem, st>>>(tm_k, tm_v, p);
+  }
+  NSA_LAUNCH_OK("tc_bwd_kernel");
+  const size_t nthreads = (size_t)a.B * a.Hkv * a.T * G * (a.D / 8);
+  const unsigned rgrid = (unsigned)((nthreads + 255) / 256);
+  {
+    KernelScope ks(branch_name(kRedNames, a.kind), st);
+    if (a.D == 128)
+      dq_reduce_kernel<128><<<rgrid, 256, 0, st>>>(p.dq_part, pair_of_slot, (__nv_bfloat16*)a.dq, a.B, a.Hq,
+                                                  a.Hkv, a.T, G, a.kind, a.window, a.block_size, a.Lk,
+                                                  pl.n_slots, a.S);
+    else
+      dq_reduce_kernel<64><<<rgrid, 256, 0, st>>>(p.dq_part, pair_of_slot, (__nv_bfloat16*)a.dq, a.B, a.Hq,
+                                                 a.Hkv, a.T, G, a.kind, a.window, a.block_size, a.Lk,
+                                                 pl.n_slots, a.S);
+  }
+  NSA_LAUNCH_OK("dq_reduce_kernel");
+  return NSA_OK;
+}
+
+}  // namespace nsa

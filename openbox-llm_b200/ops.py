@@ -68,7 +68,7 @@ def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size):
     q, k, v, o, do = (t.contiguous() for t in (q, k, v, o, do))
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
-    nws = L.lib().nsa_range_attn_bwd_workspace_bytes(d, k.shape[2], L.IMPL[_impl])
+    nws = L.lib().nsa_range_attn_bwd_workspace_bytes(d, k.shape[2], mode, int(window), L.IMPL[_impl])
     ws = L.workspace(nws, q.device)
     L.check(L.lib().nsa_range_attn_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse),
                                        L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, k.shape[2],
