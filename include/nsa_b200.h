@@ -126,7 +126,7 @@ int nsa_block_compress_bwd(const void* x, const float* intra_pos, const float* p
  * COMPRESS mode.  importance_out (optional, may be NULL) receives [B,Hkv,T,n_blk] float32. */
 int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp, int32_t* block_idx,
                     float* importance_out, const NsaDims* dims, int n_blk, int block_size,
-                    int n_sel, void* stream);
+                    int n_sel, int impl, void* stream);
 
 /* ---- gate combine ---------------------------------------------------------------------------
  * Replaces the sigmoid blend nsa_model.py:366-368 / nsa_fused_kernel.py:572-573 and its

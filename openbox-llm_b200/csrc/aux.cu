@@ -502,9 +502,15 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
   return NSA_OK;
 }
 
+namespace nsa {
+bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel);
+int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_idx, float* imp_out,
+            const NsaDims& d, int n_blk, int block_size, int n_sel, cudaStream_t st);
+}
+
 extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp,
                                int32_t* block_idx, float* importance_out, const NsaDims* dims,
-                               int n_blk, int block_size, int n_sel, void* stream) {
+                               int n_blk, int block_size, int n_sel, int impl, void* stream) {
   NSA_CHECK_ARG(dims && q && lse_cmp && block_idx && (k_cmp || n_blk == 0), "null argument");
   NSA_CHECK_ARG(dims->Hkv > 0 && dims->Hq % dims->Hkv == 0, "Hq must be a multiple of Hkv");
   NSA_CHECK_ARG(block_size > 0 && n_sel > 0 && n_blk >= 0, "bad block_size/n_sel/n_blk");
@@ -512,6 +518,14 @@ extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* ls
   cudaStream_t st = (cudaStream_t)stream;
   const size_t units = (size_t)dims->B * dims->Hkv * dims->T;
   if (units == 0) return NSA_OK;
+  if (impl != NSA_IMPL_SIMT) {
+    if (tc_topn_ok(*dims, n_blk, n_sel))
+      return tc_topn(q, k_cmp, lse_cmp, block_idx, importance_out, *dims, n_blk, block_size, n_sel, st);
+    if (impl == NSA_IMPL_TC) {
+      set_error("scoring shape not served by the tcgen05 kernel");
+      return NSA_ERR_UNSUPPORTED;
+    }
+  }
   const size_t sm = (size_t)4 * (D + n_blk) * sizeof(float);
   NSA_CHECK_ARG(sm <= 200 * 1024, "n_blk %d too large for the scoring kernel", n_blk);
   const float scale = 1.0f / sqrtf((float)D);

@@ -1,0 +1,269 @@
+// Block scoring + top-n on the tensor cores (replaces the dense scoring pass of
+// nsa_model.py:343-355).
+//
+// Same row tile as the forward kernel: 128 rows = nq queries x Gp heads of one (batch, kv head).
+// For every 64-summary tile: S = Q Kc^T by tcgen05.mma; the thread that owns a row turns it
+// into compression-branch probabilities p = exp2(s*scale*log2e - lse*log2e) with the LSE the
+// compression forward stored; the probabilities go to shared memory, are summed over the Gp
+// heads of each query (ascending head order, fp32) and each warp keeps, for its queries, the
+// running top-n list in registers (lane k holds rank k), ordered by (importance descending,
+// block index ascending).  Slots with no causally valid block are -1.
+#include "tc_common.cuh"
+#include "tc_host.cuh"
+
+namespace nsa {
+namespace tc {
+
+struct ScoreArgs {
+  const float* lse;
+  int32_t* block_idx;
+  float* imp_out;
+  int* status;
+  int B, Hq, Hkv, T, n_blk, G, Gp, nq, block_size, n_sel, n_qtiles;
+  float scale_log2;
+};
+
+__host__ __device__ inline size_t score_smem_bytes(int D, int nq) {
+  return (size_t)(kRows * 128 + 2 * kKeys * 128) * (D / 64) + (size_t)kRows * kKeys * 4 +
+         (size_t)nq * kKeys * 4 + 256 + 1024;
+}
+
+template <int D>
+__global__ void __launch_bounds__(128, 2)
+tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const ScoreArgs p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kQBytes = kRows * 128 * kSlabs, kKBytes = kKeys * 128 * kSlabs;
+  constexpr uint32_t kTmemCols = 64;
+  constexpr uint32_t kIdescQK = idesc_bf16(128, kKeys, 0, 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kQBytes;                        // 2 stages
+  float* sP = (float*)(sK + 2 * kKBytes);            // [128][64] probabilities
+  float* sImp = sP + kRows * kKeys;                  // [nq][64] group sums
+  uint64_t* bars = (uint64_t*)(sImp + p.nq * kKeys);
+  uint64_t* bar_q = bars + 0;
+  uint64_t* bar_k = bars + 1;   // [2]
+  uint64_t* bar_s = bars + 3;
+  uint32_t* s_tmem = (uint32_t*)(bars + 4);
+  volatile int* s_abort = (volatile int*)(s_tmem + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qtile = p.n_qtiles - 1 - (int)blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.Hkv, hkv = bh % p.Hkv;
+  const int t0 = qtile * p.nq;
+  const int t_last = min(p.T - 1, t0 + p.nq - 1);
+  const int g = tid / p.nq, ql = tid % p.nq;
+  const int t = t0 + ql;
+  const bool row_ok = (g < p.G) && (t < p.T);
+
+  if (tid == 0) {
+    *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k + 0, 1); mbar_init(bar_k + 1, 1);
+    mbar_init(bar_s, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k);
+  }
+  __syncthreads();
+  if (*s_abort) return;
+
+  const int hi_last = min(p.n_blk, (t_last + 1) / p.block_size) - 1;
+  const int n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
+
+  // running top-n of the queries this warp owns: query slot s -> ql = warp + 4 s; lane k = rank k
+  constexpr int kMaxOwn = 32;                       // nq <= 128 -> at most 32 queries per warp
+  float top_v[kMaxOwn];
+  int top_i[kMaxOwn];
+#pragma unroll
+  for (int s = 0; s < kMaxOwn; ++s) { top_v[s] = -1.f; top_i[s] = -1; }
+  const int n_own = (p.nq - warp + 3) / 4;
+
+  uint32_t tmem = 0;
+  if (n_tiles > 0) {
+    if (warp == 0) {
+      tmem_alloc(s_tmem, kTmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    tmem = *s_tmem;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const float lse2 = row_ok ? __ldg(p.lse + (size_t)(b * p.Hq + hkv * p.G + g) * p.T + t) * kLog2e : 0.f;
+
+    auto load_k = [&](int i) {
+      uint64_t* bar = bar_k + (i & 1);
+      mbar_expect_tx(bar, kKBytes);
+#pragma unroll
+      for (int s = 0; s < kSlabs; ++s)
+        tma_load_3d(sK + (i & 1) * kKBytes + s * (kKeys * 128), &tm_k, bar, s * 64, i * kKeys, bh);
+    };
+    auto issue_s = [&](int i) {
+      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (i & 1) * kKBytes);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+        mma_ss(tmem, desc_kmajor(qa + slab * (kRows * 128) + in),
+               desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescQK, kk > 0);
+      }
+      tc_commit(bar_s);
+    };
+    if (tid == 0) {
+      mbar_expect_tx(bar_q, kQBytes);
+#pragma unroll
+      for (int s = 0; s < kSlabs; ++s)
+        tma_load_3d(sQ + s * (kRows * 128), &tm_q, bar_q, s * 64, t0, b * p.Hq + hkv * p.G);
+      load_k(0);
+      if (n_tiles > 1) load_k(1);
+      mbar_wait(bar_q, 0, p.status, s_abort, 1);
+      mbar_wait(bar_k, 0, p.status, s_abort, 2);
+      tc_fence_after();
+      issue_s(0);
+    }
+
+    for (int i = 0; i < n_tiles; ++i) {
+      const int key0 = i * kKeys;
+      mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
+      tc_fence_after();
+      if (tid == 0 && i + 2 < n_tiles) load_k(i + 2);
+      __syncwarp();
+      uint32_t r[64];
+      tmem_ld32(lane_base, r);
+      tmem_ld32(lane_base + 32, r + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      const int hi = row_ok ? min(kKeys - 1, min(p.n_blk, (t + 1) / p.block_size) - 1 - key0) : -1;
+      float4* dst = reinterpret_cast<float4*>(sP + tid * kKeys);
+#pragma unroll
+      for (int c4 = 0; c4 < 16; ++c4) {
+        float4 v;
+        v.x = (c4 * 4 + 0 <= hi) ? ex2(__uint_as_float(r[c4 * 4 + 0]) * p.scale_log2 - lse2) : 0.f;
+        v.y = (c4 * 4 + 1 <= hi) ? ex2(__uint_as_float(r[c4 * 4 + 1]) * p.scale_log2 - lse2) : 0.f;
+        v.z = (c4 * 4 + 2 <= hi) ? ex2(__uint_as_float(r[c4 * 4 + 2]) * p.scale_log2 - lse2) : 0.f;
+        v.w = (c4 * 4 + 3 <= hi) ? ex2(__uint_as_float(r[c4 * 4 + 3]) * p.scale_log2 - lse2) : 0.f;
+        // 16-byte chunk index XOR row: a warp's stores spread over the banks
+        dst[c4 ^ (tid & 15)] = v;
+      }
+      __syncthreads();                         // all of S is read, all of P is in shared memory
+      if (tid == 0 && i + 1 < n_tiles) {
+        tc_fence_after();
+        mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
+        issue_s(i + 1);
+      }
+      // group sums: importance[ql][c] = sum over heads, ascending
+      for (int e = tid; e < p.nq * kKeys; e += 128) {
+        const int qq = e / kKeys, c = e % kKeys;
+        float s = 0.f;
+        for (int gg = 0; gg < p.G; ++gg) {
+          const int row = gg * p.nq + qq;
+          s += sP[row * kKeys + ((((c >> 2) ^ (row & 15))) << 2) + (c & 3)];
+        }
+        sImp[e] = s;
+      }
+      __syncthreads();
+      // top-n update, one warp per query
+#pragma unroll 1
+      for (int s = 0; s < n_own; ++s) {
+        const int qq = warp + 4 * s;
+        const int tq = t0 + qq;
+        if (tq >= p.T) break;
+        const int hq = min(kKeys - 1, min(p.n_blk, (tq + 1) / p.block_size) - 1 - key0);
+        float* out = p.imp_out ? p.imp_out + ((size_t)bh * p.T + tq) * p.n_blk + key0 : nullptr;
+        float tv = top_v[s];
+        int ti = top_i[s];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int c = half * 32 + lane;
+          const float v = sImp[qq * kKeys + c];
+          if (out && key0 + c < p.n_blk) out[c] = c <= hq ? v : 0.f;
+          // the list is full once rank n_sel-1 holds a block; its value is the bar to beat
+          const float thr = __shfl_sync(0xffffffffu, tv, p.n_sel - 1);
+          const int thr_i = __shfl_sync(0xffffffffu, ti, p.n_sel - 1);
+          const bool beat = (c <= hq) && (thr_i < 0 || v > thr);
+          uint32_t todo = __ballot_sync(0xffffffffu, beat);
+          while (todo) {
+            const int src = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const float cv = __shfl_sync(0xffffffffu, v, src);
+            const int cj = key0 + half * 32 + src;
+            // entries that stay ahead: larger value, or equal value (their index is smaller);
+            // empty slots (index -1) are behind everything
+            const bool ahead = (ti >= 0) && (tv >= cv);
+            const int pos = __popc(__ballot_sync(0xffffffffu, ahead));
+            if (pos < p.n_sel) {
+              const float pv = __shfl_up_sync(0xffffffffu, tv, 1);
+              const int pi = __shfl_up_sync(0xffffffffu, ti, 1);
+              if (lane > pos) { tv = pv; ti = pi; }
+              if (lane == pos) { tv = cv; ti = cj; }
+            }
+          }
+        }
+        top_v[s] = tv;
+        top_i[s] = ti;
+      }
+      __syncthreads();                         // sP / sImp are rewritten by the next tile
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+  }
+
+  // ---- write the lists; zero the importance columns no tile covered -------------------------
+#pragma unroll 1
+  for (int s = 0; s < n_own; ++s) {
+    const int qq = warp + 4 * s;
+    const int tq = t0 + qq;
+    if (tq >= p.T) break;
+    if (lane < p.n_sel) p.block_idx[((size_t)bh * p.T + tq) * p.n_sel + lane] = top_i[s];
+    if (p.imp_out) {
+      float* out = p.imp_out + ((size_t)bh * p.T + tq) * p.n_blk;
+      for (int c = n_tiles * kKeys + lane; c < p.n_blk; c += 32) out[c] = 0.f;
+    }
+  }
+}
+
+}  // namespace tc
+
+bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel) {
+  if (d.dtype != NSA_DTYPE_BF16 || (d.D != 64 && d.D != 128)) return false;
+  if (n_sel < 1 || n_sel > 32 || n_blk < 1) return false;
+  const int G = d.Hq / d.Hkv;
+  return G <= 128;
+}
+
+int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_idx, float* imp_out,
+            const NsaDims& d, int n_blk, int block_size, int n_sel, cudaStream_t st) {
+  using namespace tc;
+  ScoreArgs p;
+  p.lse = lse; p.block_idx = block_idx; p.imp_out = imp_out;
+  p.status = device_status_ptr();
+  if (!p.status) { set_error("device status word unavailable"); return NSA_ERR_CUDA; }
+  p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.T = d.T; p.n_blk = n_blk;
+  p.G = d.Hq / d.Hkv; p.Gp = group_pad(p.G); p.nq = kRows / p.Gp;
+  p.block_size = block_size; p.n_sel = n_sel;
+  p.n_qtiles = (d.T + p.nq - 1) / p.nq;
+  p.scale_log2 = kLog2e / sqrtf((float)d.D);
+  CUtensorMap tm_q, tm_k;
+  int rc = make_map(&tm_q, q, d.D, d.T, d.B * d.Hq, p.nq, p.Gp);
+  if (rc == NSA_OK) rc = make_map(&tm_k, k_cmp, d.D, n_blk, d.B * d.Hkv, kKeys, 1);
+  if (rc != NSA_OK) return rc;
+  const size_t smem = score_smem_bytes(d.D, p.nq);
+  dim3 grid(p.n_qtiles, d.B * d.Hkv);
+  if (d.D == 128) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_score_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KernelScope ks("tc_score_topn", st);
+    tc_score_kernel<128><<<grid, 128, smem, st>>>(tm_q, tm_k, p);
+  } else {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_score_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KernelScope ks("tc_score_topn", st);
+    tc_score_kernel<64><<<grid, 128, smem, st>>>(tm_q, tm_k, p);
+  }
+  NSA_LAUNCH_OK("tc_score_kernel");
+  return NSA_OK;
+}
+
+}  // namespace nsa

@@ -198,7 +198,7 @@ def topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, return_importance=False):
     imp = torch.empty(B, Hkv, T, n_blk, device=q.device, dtype=torch.float32) if return_importance else None
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
     L.check(L.lib().nsa_topn_blocks(L.ptr(q), L.ptr(k_cmp), L.ptr(lse_cmp), L.ptr(idx), L.ptr(imp),
-                                    d, n_blk, int(block_size), int(n_sel), L.stream()))
+                                    d, n_blk, int(block_size), int(n_sel), L.IMPL[_impl], L.stream()))
     return (idx, imp) if return_importance else idx
 
 
