@@ -7,7 +7,7 @@
 //   window      queries [64 j, 64 j + 63 + W - 1]
 //   compression queries t >= (64 j + 1) * Bsz - 1
 //   selection   the queries that list block j, from the block -> query CSR
-// Q and dO rows are gathered with 16-byte cp.async into 128B-swizzled tiles (double buffered).
+// Q and dO rows are gathered with 16-byte cp.async into 128B-swizzled tiles.
 // Per row tile, five MMAs:
 //   S    = Q K^T          (A: Q  K-major,   B: K  K-major)
 //   dP   = dO V^T         (A: dO K-major,   B: V  K-major)
@@ -34,7 +34,10 @@ struct BwdArgs {
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   __nv_bfloat16* dq_part;
+  float* dk_acc;               // fp32 accumulators, used when the row tiles of a key tile are split
+  float* dv_acc;
   int* status;
+  int split_chunk;             // row tiles per CTA when split
   int B, Hq, Hkv, T, Lk, G, nq;
   int kind, window, block_size;
   int n_ktiles, n_slots;
@@ -54,23 +57,32 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 
 constexpr int kRowTileBytes = kRows * 128 * 2;   // Q or dO row tile: always two 64-element slabs
 constexpr int kPBytes = kRows * 128;             // P or dS: 128 rows x 64 keys bf16
+constexpr int kGroupThreads = 256;               // one compute group: 2 warps per TMEM lane quadrant
+constexpr int kGroupBytes = 2 * kRowTileBytes + 2 * kPBytes;   // Q, dO, P, dS of one group
 
 __host__ __device__ inline size_t bwd_smem_bytes(int D) {
   return (size_t)2 * kKeys * 128 * (D / 64)      // K, V
-         + 4 * (size_t)kRowTileBytes             // Q, dO x 2 stages
-         + 2 * (size_t)kPBytes                   // P, dS
-         + 256 + 2 * 128 * 4                     // barriers, row tables
+         + 2 * (size_t)kGroupBytes               // two groups
+         + 256 + 2 * 128 * 4                     // barriers, row index tables
          + 1024;
 }
 
+__device__ __forceinline__ void group_sync(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kGroupThreads) : "memory");
+}
+
+// Two compute groups of 256 threads share the key tile and the dK^T / dV^T accumulators and
+// take alternate row tiles, so that one group's MMAs and memory waits overlap the other
+// group's arithmetic.  Inside a group, the two warps of a TMEM lane quadrant split the 64 key
+// columns of a row between them.
 template <int D>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(512, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const BwdArgs p) {
   constexpr int kSlabs = D / 64;
   constexpr int kKVBytes = kKeys * 128 * kSlabs;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 128, kColDV = 256, kColDK = 320;
+  constexpr uint32_t kColDV = 256, kColDK = 320;   // group g: S at 128 g, dP at 128 g + 64, dQ over both
   constexpr uint32_t kIdescS = idesc_bf16(128, kKeys, 0, 0);     // rows x keys
   constexpr uint32_t kIdescT = idesc_bf16(128, kKeys, 1, 1);     // d x keys, both MN-major
   constexpr uint32_t kIdescDQ = idesc_bf16(128, D, 0, 1);        // rows x d
@@ -79,24 +91,31 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
   uint8_t* sV = sK + kKVBytes;
-  uint8_t* sQ = sV + kKVBytes;                  // [2] stages
-  uint8_t* sDO = sQ + 2 * kRowTileBytes;        // [2]
-  uint8_t* sP = sDO + 2 * kRowTileBytes;
-  uint8_t* sDS = sP + kPBytes;
-  uint64_t* bars = (uint64_t*)(sDS + kPBytes);
+  uint8_t* sGroup = sV + kKVBytes;
+  uint64_t* bars = (uint64_t*)(sGroup + 2 * kGroupBytes);
   uint64_t* bar_kv = bars + 0;
-  uint64_t* bar_sp = bars + 1;
-  uint64_t* bar_acc = bars + 2;
-  uint32_t* s_tmem = (uint32_t*)(bars + 4);
+  uint32_t* s_tmem = (uint32_t*)(bars + 6);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
-  int* s_rowt = (int*)(s_tmem + 4);             // [2][128] query position of each row, -1 = none
+  int* s_rowoff_all = (int*)(bars + 8);   // [2][128] row index into [B*Hq*T] of each tile row, -1 = none
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int j = blockIdx.x;                      // key tile
+  const int tid = threadIdx.x;
+  const int grp = tid / kGroupThreads, lt = tid % kGroupThreads;
+  const int wg = lt >> 5, lane = lt & 31;
+  const int quad = wg & 3, half = wg >> 2;           // TMEM lane quadrant, key-column half
+  const int row = quad * 32 + lane;                  // row of the tile this thread works on
+  uint8_t* sQ = sGroup + grp * kGroupBytes;
+  uint8_t* sDO = sQ + kRowTileBytes;
+  uint8_t* sP = sDO + kRowTileBytes;
+  uint8_t* sDS = sP + kPBytes;
+  uint64_t* bar_sp = bars + 1 + 2 * grp;
+  uint64_t* bar_acc = bars + 2 + 2 * grp;
+  int* s_rowoff = s_rowoff_all + grp * 128;
+
+  const int j = blockIdx.x;                          // key tile
   const int bh = blockIdx.y;
   const int b = bh / p.Hkv, hkv = bh % p.Hkv;
   const int key0 = j * kKeys;
-  const int ql = tid / p.G, g = tid % p.G;
+  const int ql = row / p.G, g = row % p.G;
   const int head = hkv * p.G + g;
   const bool row_slot_ok = ql < p.nq;
 
@@ -113,15 +132,22 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     n_q = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j + 1) - pair_base;
   }
   n_q = max(n_q, 0);
-  const int n_rt = (n_q + p.nq - 1) / p.nq;
+  const int n_rt_all = (n_q + p.nq - 1) / p.nq;
+  // gridDim.z > 1: the row tiles are split in chunks and dK / dV go through fp32 atomics
+  const int chunk = (int)gridDim.z > 1 ? p.split_chunk : n_rt_all;
+  const int rt_begin = (int)blockIdx.z * chunk;
+  const int rt_end = min(n_rt_all, rt_begin + chunk);
+  const bool split = gridDim.z > 1;
 
-  if (n_rt == 0) {   // nobody attends these keys: their gradients are zero
-    for (int i = tid; i < kKeys * D / 8; i += 128) {
-      const int key = key0 + i / (D / 8);
-      if (key < p.Lk) {
-        const size_t off = ((size_t)bh * p.Lk + key) * D + (i % (D / 8)) * 8;
-        *reinterpret_cast<uint4*>(p.dk + off) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(p.dv + off) = make_uint4(0, 0, 0, 0);
+  if (rt_end <= rt_begin) {
+    if (!split && n_rt_all == 0) {   // nobody attends these keys: their gradients are zero
+      for (int i = tid; i < kKeys * D / 8; i += blockDim.x) {
+        const int key = key0 + i / (D / 8);
+        if (key < p.Lk) {
+          const size_t off = ((size_t)bh * p.Lk + key) * D + (i % (D / 8)) * 8;
+          *reinterpret_cast<uint4*>(p.dk + off) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(p.dv + off) = make_uint4(0, 0, 0, 0);
+        }
       }
     }
     return;
@@ -130,23 +156,22 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   if (tid == 0) {
     *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
     mbar_init(bar_kv, 1);
-    mbar_init(bar_sp, 1);
-    mbar_init(bar_acc, 1);
+    for (int k = 1; k <= 4; ++k) mbar_init(bars + k, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
   }
   if (D == 64) {   // the second slab of the row tiles is never gathered: keep it zero
-    for (int i = tid; i < 4 * (kRows * 128) / 16; i += 128) {
+    for (int i = tid; i < 4 * (kRows * 128) / 16; i += blockDim.x) {
       const int buf = i / ((kRows * 128) / 16), o16 = i % ((kRows * 128) / 16);
-      uint8_t* base = (buf < 2 ? sQ + buf * kRowTileBytes : sDO + (buf - 2) * kRowTileBytes) + kRows * 128;
+      uint8_t* base = sGroup + (buf >> 1) * kGroupBytes + (buf & 1) * kRowTileBytes + kRows * 128;
       *reinterpret_cast<uint4*>(base + o16 * 16) = make_uint4(0, 0, 0, 0);
     }
   }
   __syncthreads();
   if (*s_abort) return;
 
-  if (warp == 0) {
+  if (tid < 32) {
     tmem_alloc(s_tmem, kTmemCols);
     tmem_relinquish();
   }
@@ -154,7 +179,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+  const uint32_t colS = grp * 128, colDP = grp * 128 + 64, colDQ = grp * 128;
 
   if (tid == 0) {
     mbar_expect_tx(bar_kv, 2 * kKVBytes);
@@ -164,82 +190,85 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       tma_load_3d(sV + s * (kKeys * 128), &tm_v, bar_kv, s * 64, key0, bh);
     }
   }
+  // dK^T / dV^T start at zero so that every MMA into them accumulates
+  if (grp == 0 && half == 0) {
+    uint32_t z[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) z[c] = 0u;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) tmem_st32(lane_base + kColDV + cc * 32, z);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (tid == 0 || tid == kGroupThreads) mbar_wait(bar_kv, 0, p.status, s_abort, 32);
 
-  // row metadata of tile i for this thread's row
+  // query position of this thread's row in row tile i (-1: no row)
   auto row_query = [&](int i) -> int {
     const int qi = i * p.nq + ql;
     if (!row_slot_ok || qi >= n_q) return -1;
     if (p.kind == 2) return __ldg(p.q_of_block + pair_base + qi);
     return t_lo + qi;
   };
-  // gather the Q and dO rows of tile i into stage st (16-byte chunks, 128B swizzle)
-  auto gather = [&](int st, const int* rowt) {
-    constexpr int kChunks = D / 8;                 // 16-byte chunks per row
-    constexpr int kRowsPerPass = 128 / kChunks;
-    const int c = tid % kChunks;
-    const uint32_t q_base = smem_u32(sQ + st * kRowTileBytes), do_base = smem_u32(sDO + st * kRowTileBytes);
-#pragma unroll 4
-    for (int r = tid / kChunks; r < kRows; r += kRowsPerPass) {
-      const int tq = rowt[r];
-      const int rg = r % p.G;
-      const size_t src = tq >= 0 ? ((size_t)(b * p.Hq + hkv * p.G + rg) * p.T + tq) * D + c * 8 : 0;
-      const uint32_t dst = (uint32_t)((c >> 3) * (kRows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
-      const uint32_t nbytes = tq >= 0 ? 16u : 0u;   // 0 -> the chunk is zero-filled
-      cp_async16(q_base + dst, p.q + src, nbytes);
-      cp_async16(do_base + dst, p.d_o + src, nbytes);
-    }
-    cp_async_commit();
-  };
 
-  int t_cur = row_query(0);
-  s_rowt[tid] = t_cur;
-  __syncthreads();
-  gather(0, s_rowt);
+  int i = rt_begin + grp;
+  int t_cur = i < rt_end ? row_query(i) : -1;
   float lse2_cur = 0.f, delta_cur = 0.f;
   if (t_cur >= 0) {
     const size_t ri = (size_t)(b * p.Hq + head) * p.T + t_cur;
     lse2_cur = __ldg(p.lse + ri) * kLog2e;
     delta_cur = __ldg(p.delta + ri);
   }
-
-  for (int i = 0; i < n_rt; ++i) {
-    const int st = i & 1;
-    // metadata of the next tile (global loads overlap the waits below)
-    int t_next = -1;
-    float lse2_next = 0.f, delta_next = 0.f;
-    if (i + 1 < n_rt) {
-      t_next = row_query(i + 1);
-      s_rowt[(st ^ 1) * 128 + tid] = t_next;
-      if (t_next >= 0) {
-        const size_t ri = (size_t)(b * p.Hq + head) * p.T + t_next;
-        lse2_next = __ldg(p.lse + ri) * kLog2e;
-        delta_next = __ldg(p.delta + ri);
+  uint32_t phase = 0;
+  for (; i < rt_end; i += 2, phase ^= 1) {
+    if (half == 0)
+      s_rowoff[row] = t_cur >= 0 ? (int)((size_t)(b * p.Hq + head) * p.T + t_cur) : -1;
+    group_sync(grp);     // row offsets visible; the previous tile's MMAs were waited for by all
+    {   // gather the Q and dO rows (16-byte chunks, 128B swizzle); missing rows are zero-filled
+      constexpr int kChunks = D / 8;
+      constexpr int kRowsPerPass = kGroupThreads / kChunks;
+      const int c = lt % kChunks;
+      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO);
+#pragma unroll 4
+      for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
+        const int off = s_rowoff[r];
+        const size_t src = off >= 0 ? (size_t)off * D + c * 8 : 0;
+        const uint32_t dst = (uint32_t)((c >> 3) * (kRows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+        const uint32_t nbytes = off >= 0 ? 16u : 0u;
+        cp_async16(q_base + dst, p.q + src, nbytes);
+        cp_async16(do_base + dst, p.d_o + src, nbytes);
       }
+      cp_async_commit();
     }
-    cp_async_wait_all();        // gather(i) has landed
-    fence_proxy_async();        // ... and is visible to the tensor core
-    __syncthreads();
-    if (tid == 0) {
-      if (i == 0) mbar_wait(bar_kv, 0, p.status, s_abort, 32);
+    // metadata of this group's next tile: the loads overlap the gather
+    const int t_next = (i + 2 < rt_end) ? row_query(i + 2) : -1;
+    float lse2_next = 0.f, delta_next = 0.f;
+    if (t_next >= 0) {
+      const size_t ri = (size_t)(b * p.Hq + head) * p.T + t_next;
+      lse2_next = __ldg(p.lse + ri) * kLog2e;
+      delta_next = __ldg(p.delta + ri);
+    }
+    cp_async_wait_all();
+    fence_proxy_async();
+    group_sync(grp);
+    if (lt == 0) {
       tc_fence_after();
-      const uint32_t qa = smem_u32(sQ + st * kRowTileBytes), da = smem_u32(sDO + st * kRowTileBytes);
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      const uint32_t qa = smem_u32(sQ), da = smem_u32(sDO), ka = smem_u32(sK), va = smem_u32(sV);
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + kColS, desc_kmajor(qa + slab * (kRows * 128) + in),
+        mma_ss(tmem + colS, desc_kmajor(qa + slab * (kRows * 128) + in),
                desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + kColDP, desc_kmajor(da + slab * (kRows * 128) + in),
+        mma_ss(tmem + colDP, desc_kmajor(da + slab * (kRows * 128) + in),
                desc_kmajor(va + slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
       tc_commit(bar_sp);
     }
-    if (i + 1 < n_rt) gather(st ^ 1, s_rowt + (st ^ 1) * 128);
-
     // valid key columns of this row: one range [lo, hi]
     int lo = 0, hi = -1;
     if (t_cur >= 0) {
@@ -252,15 +281,13 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         hi = min(kKeys - 1, min(t_cur, p.T - 1) - key0);
       }
     }
-    mbar_wait(bar_sp, i & 1, p.status, s_abort, 64);
+    mbar_wait(bar_sp, phase, p.status, s_abort, 64);
     tc_fence_after();
     __syncwarp();
-    const uint32_t p_row = smem_u32(sP) + tid * 128, ds_row = smem_u32(sDS) + tid * 128;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    {
       uint32_t rs[32], rp[32];
-      tmem_ld32(lane_base + kColS + half * 32, rs);
-      tmem_ld32(lane_base + kColDP + half * 32, rp);
+      tmem_ld32(lane_base + colS + half * 32, rs);
+      tmem_ld32(lane_base + colDP + half * 32, rp);
       tmem_wait_ld();
       uint32_t pp[16], pd[16];
 #pragma unroll
@@ -277,41 +304,36 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         pp[c2] = pack_bf16(pv[0], pv[1]);
         pd[c2] = pack_bf16(dv[0], dv[1]);
       }
+      const uint32_t p_row = smem_u32(sP) + row * 128, ds_row = smem_u32(sDS) + row * 128;
 #pragma unroll
       for (int k4 = 0; k4 < 4; ++k4) {
-        const uint32_t chunk = (uint32_t)((half * 4 + k4) ^ (tid & 7)) << 4;
-        st_shared_v4(p_row + chunk, pp[k4 * 4], pp[k4 * 4 + 1], pp[k4 * 4 + 2], pp[k4 * 4 + 3]);
-        st_shared_v4(ds_row + chunk, pd[k4 * 4], pd[k4 * 4 + 1], pd[k4 * 4 + 2], pd[k4 * 4 + 3]);
+        const uint32_t chunk16 = (uint32_t)((half * 4 + k4) ^ (row & 7)) << 4;
+        st_shared_v4(p_row + chunk16, pp[k4 * 4], pp[k4 * 4 + 1], pp[k4 * 4 + 2], pp[k4 * 4 + 3]);
+        st_shared_v4(ds_row + chunk16, pd[k4 * 4], pd[k4 * 4 + 1], pd[k4 * 4 + 2], pd[k4 * 4 + 3]);
       }
     }
     fence_proxy_async();
     tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
+    group_sync(grp);
+    if (lt == 0) {
       tc_fence_after();
-      const uint32_t qa = smem_u32(sQ + st * kRowTileBytes), da = smem_u32(sDO + st * kRowTileBytes);
+      const uint32_t qa = smem_u32(sQ), da = smem_u32(sDO);
       const uint32_t pa = smem_u32(sP), dsa = smem_u32(sDS), ka = smem_u32(sK);
 #pragma unroll
-      for (int kk = 0; kk < kRows / 16; ++kk) {      // contraction over the 128 rows
+      for (int kk = 0; kk < kRows / 16; ++kk)        // contraction over the 128 rows
         mma_ss(tmem + kColDV, desc_mnmajor(da + kk * 2048, kRows * 128), desc_mnmajor(pa + kk * 2048, 0),
-               kIdescT, (i > 0) || (kk > 0));
-      }
+               kIdescT, 1);
 #pragma unroll
-      for (int kk = 0; kk < kRows / 16; ++kk) {
+      for (int kk = 0; kk < kRows / 16; ++kk)
         mma_ss(tmem + kColDK, desc_mnmajor(qa + kk * 2048, kRows * 128), desc_mnmajor(dsa + kk * 2048, 0),
-               kIdescT, (i > 0) || (kk > 0));
-      }
+               kIdescT, 1);
 #pragma unroll
-      for (int kk = 0; kk < kKeys / 16; ++kk) {      // contraction over the 64 keys
-        mma_ss(tmem + kColDQ, desc_kmajor(dsa + kk * 32), desc_mnmajor(ka + kk * 2048, kKeys * 128),
+      for (int kk = 0; kk < kKeys / 16; ++kk)        // contraction over the 64 keys
+        mma_ss(tmem + colDQ, desc_kmajor(dsa + kk * 32), desc_mnmajor(ka + kk * 2048, kKeys * 128),
                kIdescDQ, kk > 0);
-      }
       tc_commit(bar_acc);
     }
-    mbar_wait(bar_acc, i & 1, p.status, s_abort, 128);
-    tc_fence_after();
-    __syncwarp();
-    // dQ partial of this (row tile, key tile)
+    // where this row's dQ partial goes
     size_t pidx = 0;
     if (t_cur >= 0) {
       if (p.kind == 2) {
@@ -321,13 +343,17 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         pidx = ((((size_t)bh * p.T + t_cur) * p.n_slots + slot) * p.G + g) * D;
       }
     }
+    mbar_wait(bar_acc, phase, p.status, s_abort, 128);
+    tc_fence_after();
+    __syncwarp();
 #pragma unroll
-    for (int cc = 0; cc < D / 32; ++cc) {
+    for (int cc = 0; cc < D / 64; ++cc) {            // this thread's half of the D columns
+      const int col0 = half * (D / 2) + cc * 32;
       uint32_t r32[32];
-      tmem_ld32(lane_base + kColDQ + cc * 32, r32);
+      tmem_ld32(lane_base + colDQ + col0, r32);
       tmem_wait_ld();
       if (t_cur >= 0) {
-        uint4* dst = reinterpret_cast<uint4*>(p.dq_part + pidx + cc * 32);
+        uint4* dst = reinterpret_cast<uint4*>(p.dq_part + pidx + col0);
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
           uint4 u;
@@ -343,30 +369,34 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     t_cur = t_next; lse2_cur = lse2_next; delta_cur = delta_next;
   }
 
-  // ---- dK^T, dV^T: lane = d, column = key ---------------------------------------------------
-  __syncwarp();
+  // ---- dK^T, dV^T: lane = d, column = key; group 0 writes dV, group 1 writes dK ---------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (half == 0) {
+    const uint32_t col = grp == 0 ? kColDV : kColDK;
+    const int d = row;
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    __nv_bfloat16* dst = which == 0 ? p.dv : p.dk;
-    const uint32_t col = which == 0 ? kColDV : kColDK;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int hc = 0; hc < 2; ++hc) {
       uint32_t r32[32];
-      tmem_ld32(lane_base + col + half * 32, r32);
+      tmem_ld32(lane_base + col + hc * 32, r32);
       tmem_wait_ld();
-      if (tid < D) {
+      if (d < D) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const int key = key0 + half * 32 + c;
-          if (key < p.Lk)
-            dst[((size_t)bh * p.Lk + key) * D + tid] = __float2bfloat16_rn(__uint_as_float(r32[c]));
+          const int key = key0 + hc * 32 + c;
+          if (key < p.Lk) {
+            const size_t o = ((size_t)bh * p.Lk + key) * D + d;
+            if (split) atomicAdd((grp == 0 ? p.dv_acc : p.dk_acc) + o, __uint_as_float(r32[c]));
+            else (grp == 0 ? p.dv : p.dk)[o] = __float2bfloat16_rn(__uint_as_float(r32[c]));
+          }
         }
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+  if (tid < 32) tmem_dealloc(tmem, kTmemCols);
 }
 
 // delta[b,h,t] = sum_d dO * O (fp32), one warp per row
@@ -437,7 +467,8 @@ static const char* const kBwdNames[3] = {"tc_bwd_win", "tc_bwd_cmp", "tc_bwd_slc
 static const char* const kRedNames[3] = {"dq_reduce_win", "dq_reduce_cmp", "dq_reduce_slc"};
 
 struct BwdPlan {
-  int n_ktiles, n_slots, nq;
+  int n_ktiles, n_slots, nq, n_splits, split_chunk;
+  size_t off_acc;
   size_t cap_pairs;          // selection: pairs the CSR may hold
   size_t off_delta, off_part, off_csr_ws, off_qob, off_off, off_pbh, off_pos, total;
 };
@@ -468,6 +499,17 @@ static BwdPlan plan_bwd(const AttnArgs& a) {
     pl.off_pbh = off; off += align_up(pl.cap_pairs * 4, 256);
     pl.off_off = off; off += align_up(units * (pl.n_ktiles + 1) * 4, 256);
     pl.off_pos = off; off += align_up(pl.cap_pairs * 4, 256);
+  }
+  // compression: a few key tiles are attended by (almost) every query; split their row tiles
+  pl.n_splits = 1;
+  pl.split_chunk = 0;
+  pl.off_acc = off;
+  if (a.kind == 1) {
+    const int max_rt = (a.T + pl.nq - 1) / pl.nq;
+    pl.split_chunk = 48;
+    pl.n_splits = (max_rt + pl.split_chunk - 1) / pl.split_chunk;
+    if (pl.n_splits > 1) off += 2 * align_up((size_t)a.B * a.Hkv * a.Lk * a.D * sizeof(float), 256);
+    else pl.n_splits = 1;
   }
   pl.total = off;
   return pl;
@@ -507,6 +549,12 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.kind = a.kind; p.window = a.window; p.block_size = a.block_size;
   p.n_ktiles = pl.n_ktiles; p.n_slots = pl.n_slots;
   p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
+  p.split_chunk = pl.split_chunk;
+  const size_t n_kv = (size_t)a.B * a.Hkv * a.Lk * a.D;
+  p.dk_acc = (float*)(base + pl.off_acc);
+  p.dv_acc = (float*)(base + pl.off_acc + align_up(n_kv * sizeof(float), 256));
+  if (pl.n_splits > 1)
+    NSA_CUDA_OK(cudaMemsetAsync(base + pl.off_acc, 0, 2 * align_up(n_kv * sizeof(float), 256), st));
 
   const size_t rows = (size_t)a.B * a.Hq * a.T;
   {
@@ -529,17 +577,22 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
   if (rc != NSA_OK) return rc;
   const size_t smem = bwd_smem_bytes(a.D);
-  dim3 grid(pl.n_ktiles, a.B * a.Hkv);
+  dim3 grid(pl.n_ktiles, a.B * a.Hkv, pl.n_splits);
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<128><<<grid, 128, smem, st>>>(tm_k, tm_v, p);
+    tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, p);
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<64><<<grid, 128, smem, st>>>(tm_k, tm_v, p);
+    tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, p);
   }
   NSA_LAUNCH_OK("tc_bwd_kernel");
+  if (pl.n_splits > 1) {
+    int rc2 = cast_f32_to(p.dk_acc, p.dk, n_kv, NSA_DTYPE_BF16, st);
+    if (rc2 == NSA_OK) rc2 = cast_f32_to(p.dv_acc, p.dv, n_kv, NSA_DTYPE_BF16, st);
+    if (rc2 != NSA_OK) return rc2;
+  }
   const size_t nthreads = (size_t)a.B * a.Hkv * a.T * G * (a.D / 8);
   const unsigned rgrid = (unsigned)((nthreads + 255) / 256);
   {
