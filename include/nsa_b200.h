@@ -148,6 +148,12 @@ long long nsa_launch_count(void);
 void nsa_profile_enable(int on);
 int nsa_profile_summary(char* buf, size_t cap);
 
+/* Tuning switches.  "sel_fwd_variant": 0 = the selection forward picks, on the device, between
+ * its query-outer kernel (cheap when neighbouring queries share blocks) and its block-outer
+ * kernel (cheap when they do not); 1 / 2 force one of them.  No counterpart in the reference
+ * beyond its USE_FSA_FWD module flag (nsa_selection_kernel.py:48). */
+int nsa_set_option(const char* name, int value);
+
 /* error flag raised by a kernel whose bounded wait ran out (0 = none); reading it synchronises
  * the stream. */
 int nsa_device_status(void* stream);

@@ -5,4 +5,4 @@ from .ops import (MODE_COMPRESS, MODE_WINDOW, SelectionAttnTriton, _RangeAttn,  
                   compression_attn_triton, gate_combine, get_impl, nsa_attention,
                   nsa_fused_forward, range_attn_backward, range_attn_forward,
                   selection_attn_triton, selection_backward_triton, selection_forward_triton,
-                  set_impl, tc_supported, topn_blocks, window_attn_triton)
+                  set_impl, set_option, tc_supported, topn_blocks, window_attn_triton)

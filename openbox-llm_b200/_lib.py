@@ -32,6 +32,7 @@ SIGNATURES = {
     "nsa_tc_supported": (_i, [_dp, _i]),
     "nsa_device_status": (_i, [_vp]),
     "nsa_launch_count": (ctypes.c_longlong, []),
+    "nsa_set_option": (_i, [ctypes.c_char_p, _i]),
     "nsa_profile_enable": (None, [_i]),
     "nsa_profile_summary": (_i, [ctypes.c_char_p, _sz]),
     "nsa_range_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _dp, _i, _i, _i, _i, _i, _vp]),

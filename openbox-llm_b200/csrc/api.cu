@@ -56,6 +56,9 @@ void kernel_end(cudaStream_t st) {
   t_open_e1 = nullptr;
 }
 
+static std::atomic<int> g_opt_sel_fwd{0};
+int get_option_sel_fwd() { return g_opt_sel_fwd.load(); }
+
 static int check_dims(const NsaDims* d) {
   NSA_CHECK_ARG(d != nullptr, "dims is null");
   NSA_CHECK_ARG(d->B >= 0 && d->T >= 0 && d->Hq > 0 && d->Hkv > 0, "bad B/T/Hq/Hkv");
@@ -134,6 +137,15 @@ extern "C" int nsa_tc_supported(const NsaDims* dims, int block_size) {
 }
 
 extern "C" long long nsa_launch_count(void) { return g_launches.load(); }
+
+extern "C" int nsa_set_option(const char* name, int value) {
+  if (name && strcmp(name, "sel_fwd_variant") == 0 && value >= 0 && value <= 2) {
+    g_opt_sel_fwd.store(value);
+    return NSA_OK;
+  }
+  set_error("unknown option or value");
+  return NSA_ERR_BAD_ARG;
+}
 
 extern "C" void nsa_profile_enable(int on) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
@@ -252,8 +264,12 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
 // ---- selection attention ---------------------------------------------------------------------
 extern "C" size_t nsa_selection_fwd_workspace_bytes(const NsaDims* dims, int S, int block_size,
                                                     int impl) {
-  (void)dims; (void)S; (void)block_size; (void)impl;
-  return 0;
+  if (check_dims(dims) != NSA_OK || S <= 0) return 0;
+  int rc;
+  if (!use_tc(dims, block_size, impl, &rc)) return 0;
+  AttnArgs a = base_args(dims, dims->T);
+  a.kind = 2; a.S = S; a.block_size = block_size;
+  return tc_sel_fwd_workspace(a);
 }
 
 static int check_sel(const NsaDims* dims, int S, int block_size) {
@@ -268,7 +284,6 @@ extern "C" int nsa_selection_fwd(const void* q, const void* k, const void* v,
                                  const int32_t* block_idx, void* o, float* lse, const NsaDims* dims,
                                  int S, int block_size, void* workspace, size_t workspace_bytes,
                                  int impl, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   int rc = check_sel(dims, S, block_size);
   if (rc != NSA_OK) return rc;
   const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
@@ -277,7 +292,8 @@ extern "C" int nsa_selection_fwd(const void* q, const void* k, const void* v,
   AttnArgs a = base_args(dims, dims->T);
   a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse; a.block_idx = block_idx;
   a.kind = 2; a.S = S; a.block_size = block_size;
-  if (use_tc(dims, block_size, impl, &rc) && S > 0) return tc_attn_fwd(a, (cudaStream_t)stream);
+  if (use_tc(dims, block_size, impl, &rc) && S > 0)
+    return tc_sel_fwd(a, workspace, workspace_bytes, (cudaStream_t)stream);
   if (rc != NSA_OK) return rc;
   return simt_attn_fwd(a, dims->dtype, (cudaStream_t)stream);
 }

@@ -97,6 +97,8 @@ int cast_f32_to(const float* src, void* dst, size_t n, int dtype, cudaStream_t s
 // ---- tcgen05 kernel family (tc.cu) ----------------------------------------------------------
 bool tc_shape_ok(const NsaDims& d, int block_size);
 int tc_attn_fwd(const AttnArgs& a, cudaStream_t st);
+size_t tc_sel_fwd_workspace(const AttnArgs& a);
+int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t tc_attn_bwd_workspace(const AttnArgs& a);
 int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
 

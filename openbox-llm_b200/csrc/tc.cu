@@ -27,6 +27,9 @@ struct FwdArgs {
   int* status;
   int B, Hq, Hkv, T, Lk, S, G, Gp, nq;
   int kind, window, block_size;
+  const unsigned long long* stats;   // selection: statistics for the variant choice (may be null)
+  const int32_t* offsets;            // selection: CSR offsets (pair count at the end)
+  int force;
   int n_qtiles, nb_sel;      // nb_sel = ceil(T / 64) blocks a selection list may name
   int nw;                    // 32-bit membership words per block = max(1, nq / 32)
   float scale_log2;
@@ -98,6 +101,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   __syncthreads();
   if (*s_abort) return;
+  if (p.kind == 2 && p.stats != nullptr &&
+      prefer_pairs(p.stats, p.offsets, p.B * p.Hkv, p.nb_sel, p.nq, p.force))
+    return;   // the block-outer variant serves this call
 
   // ---- tile list ------------------------------------------------------------------------
   int n_tiles = 0, first_key = 0;
@@ -364,9 +370,11 @@ bool tc_shape_ok(const NsaDims& d, int block_size) {
   return true;
 }
 
-int tc_attn_fwd(const AttnArgs& a, cudaStream_t st) {
+static int launch_fwd(const AttnArgs& a, const unsigned long long* stats, const int32_t* offsets,
+                      int force, cudaStream_t st) {
   using namespace tc;
   FwdArgs p;
+  p.stats = stats; p.offsets = offsets; p.force = force;
   p.block_idx = a.block_idx;
   p.o = (__nv_bfloat16*)a.o;
   p.lse = a.lse;
@@ -397,6 +405,13 @@ int tc_attn_fwd(const AttnArgs& a, cudaStream_t st) {
   }
   NSA_LAUNCH_OK("tc_fwd_kernel");
   return NSA_OK;
+}
+
+int tc_attn_fwd(const AttnArgs& a, cudaStream_t st) { return launch_fwd(a, nullptr, nullptr, 0, st); }
+
+int tc_fwd_union_launch(const AttnArgs& a, const unsigned long long* stats, const int32_t* offsets,
+                        int force, cudaStream_t st) {
+  return launch_fwd(a, stats, offsets, force, st);
 }
 
 }  // namespace nsa

@@ -204,6 +204,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// ---- which selection-forward variant does the work ------------------------------------------
+// stats[0] = number of (query tile, distinct block) pairs of the query-outer kernel.
+// The query-outer kernel runs one 64-key tile per such pair; this kernel runs one row tile per
+// nq (query, block) pairs, at about three times the cost of a query-outer tile.
+__device__ __forceinline__ bool prefer_pairs(const unsigned long long* stats, const int32_t* offsets,
+                                             int units, int n_ktiles, int nq, int force) {
+  if (force) return force == 2;
+  const unsigned long long union_tiles = stats[0];
+  const unsigned long long pairs = (unsigned long long)__ldg(offsets + (size_t)units * (n_ktiles + 1) - 1);
+  return union_tiles * (unsigned long long)nq > 3ull * pairs;
+}
+
 // byte offset of element (row, col) inside a 128B-swizzled slab sequence; col in elements
 __device__ __forceinline__ uint32_t sw128_offset(int row, int col, int rows_per_slab) {
   const int slab = col >> 6, c = col & 63;

@@ -32,6 +32,11 @@ def get_impl() -> str:
     return _impl
 
 
+def set_option(name: str, value: int):
+    """Library tuning switch (see nsa_set_option in include/nsa_b200.h)."""
+    L.check(L.lib().nsa_set_option(name.encode(), int(value)))
+
+
 def tc_supported(B, Hq, Hkv, T, D, dtype, block_size=64) -> bool:
     code = L.DTYPE_BF16 if dtype == torch.bfloat16 else L.DTYPE_F32
     return bool(L.lib().nsa_tc_supported(L.dims(B, Hq, Hkv, T, D, code), block_size))

@@ -24,6 +24,7 @@ def _impls_for(c, dtype):
 def _reset_impl():
     yield
     pkg().set_impl("auto")
+    pkg().set_option("sel_fwd_variant", 0)
 
 
 ALL = [(c, dt) for c in REF_CONFIGS for dt in DTYPES] + [(c, torch.bfloat16) for c in TC_CONFIGS]
@@ -73,6 +74,32 @@ def test_branches_forward_backward(c, dtype):
             check(dq, dq_ref, dtype, tag + " dq", abs32=4e-3)
             check(dk, dk_ref, dtype, tag + " dk", abs32=4e-3)
             check(dv, dv_ref, dtype, tag + " dv", abs32=4e-3)
+
+
+@pytest.mark.parametrize("c", TC_CONFIGS + [REF_CONFIGS[3]], ids=cfg_id)
+def test_selection_forward_variants(c):
+    """Both tcgen05 selection-forward kernels (query-outer and block-outer) and the device-side
+    choice between them, on scattered and on neighbour-sharing block lists."""
+    nsa = pkg()
+    dtype = torch.bfloat16
+    t = make_inputs(c, dtype, seed=3)
+    bs, T = c["block_size"], c["T"]
+    lists = {"random": t["block_idx"],
+             "recent": O.make_block_idx_recent(c["B"], c["Hkv"], T, bs, c["S"])}
+    nsa.set_impl("tc")
+    q_d, k_d, v_d = (dev(t[n], dtype) for n in ("q", "ks", "vs"))
+    for name, idx in lists.items():
+        o_ref, lse_ref = O.stream_attn_forward(t["q"], t["ks"], t["vs"], O.selection_keep_fn(idx, T, bs))
+        empty = lse_ref == O.LSE_EMPTY
+        for variant in (1, 2, 0):
+            nsa.set_option("sel_fwd_variant", variant)
+            o, lse = nsa.selection_forward_triton(q_d, k_d, v_d, idx.cuda(), bs, return_lse=True)
+            tag = f"{name}/variant{variant}"
+            check(o, o_ref, dtype, tag + " o")
+            assert (lse.cpu()[empty] == O.LSE_EMPTY).all() and (o.float().cpu()[empty] == 0).all(), tag
+            if (~empty).any():
+                assert (lse.cpu()[~empty] - lse_ref[~empty]).abs().max().item() <= 2e-2, tag
+    assert nsa.lib().nsa_device_status(None) == 0
 
 
 @pytest.mark.parametrize("c,dtype", ALL, ids=IDS)
