@@ -267,21 +267,43 @@ def main():
     host_out = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in [out] + list(grads)]
     h2d = sum(x.numel() * x.element_size() for x in host_in.values())
     d2h = sum(x.numel() * x.element_size() for x in host_out)
-    dbuf = {n: torch.empty_like(t[n]) for n in host_in}
+    # Two device input sets and three streams: the upload of step k+1 and the download of
+    # step k-1 overlap the kernels of step k.  Every step still uploads all of its inputs from
+    # pinned host memory and downloads all of its results.
+    dbufs = [{n: torch.empty_like(t[n]) for n in host_in} for _ in range(2)]
+    host_outs = [host_out, [torch.empty_like(x).pin_memory() for x in host_out]]
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
 
-    def e2e_step():
-        for n in host_in:
-            dbuf[n].copy_(host_in[n], non_blocking=True)
-        o, _, g = run_step(nsa, dbuf, comp, w)
-        for dst, src in zip(host_out, [o] + list(g)):
-            dst.copy_(src, non_blocking=True)
+    def e2e_run(n_steps):
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        in_free = [None, None]
+        for k in range(n_steps):
+            bi = k % 2
+            with torch.cuda.stream(s_up):
+                if in_free[bi] is not None:
+                    s_up.wait_event(in_free[bi])
+                for n in host_in:
+                    dbufs[bi][n].copy_(host_in[n], non_blocking=True)
+                in_ready[bi].record(s_up)
+            main.wait_event(in_ready[bi])
+            o, _, g = run_step(nsa, dbufs[bi], comp, w)
+            done = torch.cuda.Event()
+            done.record(main)
+            in_free[bi] = done
+            with torch.cuda.stream(s_down):
+                s_down.wait_event(done)
+                for dst, src in zip(host_outs[bi], [o] + list(g)):
+                    src.record_stream(s_down)
+                    dst.copy_(src, non_blocking=True)
+        main.wait_stream(s_down)
+        main.wait_stream(s_up)
 
-    e2e_step()
+    e2e_run(2)
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     f0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    e2e_run(args.steps)
     f1.record()
     barrier()
     ms_e2e = f0.elapsed_time(f1)

@@ -135,15 +135,18 @@ __global__ void zero_tail_kernel(T* __restrict__ dx, int T_, int D, int t_first,
   dx[(bh * T_ + t_first) * D + r] = from_float<T>(0.f);
 }
 
-// stage B: d_proj[o][i] = sum_rows d_out[row][o] * pooled[row][i]; one CTA per o
+// stage B: d_proj[o][i] = sum_rows d_out[row][o] * pooled[row][i]; CTA (o, chunk of rows),
+// chunks meet through atomicAdd on the zero-initialised output
 template <typename T>
 __global__ void compress_bwd_proj_kernel(const T* __restrict__ d_out, const float* __restrict__ pooled,
                                          float* __restrict__ d_proj, size_t rows, int D) {
   const int o = blockIdx.x, i = threadIdx.x;
   if (i >= D) return;
+  const size_t per = (rows + gridDim.y - 1) / gridDim.y;
+  const size_t r0 = (size_t)blockIdx.y * per, r1 = r0 + per < rows ? r0 + per : rows;
   float s = 0.f;
-  for (size_t r = 0; r < rows; ++r) s = fmaf(to_float(d_out[r * D + o]), pooled[r * D + i], s);
-  d_proj[(size_t)o * D + i] = s;
+  for (size_t r = r0; r < r1; ++r) s = fmaf(to_float(d_out[r * D + o]), pooled[r * D + i], s);
+  if (r1 > r0) atomicAdd(d_proj + (size_t)o * D + i, s);
 }
 
 // stage C: d_intra[pos][d] = w[pos] * sum_dpooled[d]; d_logits = w * (d_w - sum(d_w * w))
@@ -476,19 +479,19 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
   const size_t sm_f = (size_t)(block_size + D) * sizeof(float);
   const size_t sm_b = (size_t)(block_size + D + 32) * sizeof(float);
   const size_t tail = (size_t)(T - n_blk * block_size) * D * B * Hkv;
+  NSA_CUDA_OK(cudaMemsetAsync(d_proj_w, 0, (size_t)D * D * sizeof(float), st));
+  const dim3 pgrid(D, (unsigned)(rows >= 4096 ? 64 : (rows >= 64 ? rows / 64 : 1)));
   if (rows > 0) {
     if (dtype == NSA_DTYPE_BF16) {
       { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk); }
       { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk); }
-      { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D); }
+      { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<pgrid, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D); }
     } else {
       { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)nullptr, pooled, T, D, block_size, n_blk); }
       { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (const float*)d_out, (float*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk); }
-      { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<D, (D + 31) / 32 * 32, 0, st>>>((const float*)d_out, pooled, d_proj_w, rows, D); }
+      { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<pgrid, (D + 31) / 32 * 32, 0, st>>>((const float*)d_out, pooled, d_proj_w, rows, D); }
     }
     NSA_LAUNCH_OK("compress_bwd kernels");
-  } else {
-    NSA_CUDA_OK(cudaMemsetAsync(d_proj_w, 0, (size_t)D * D * sizeof(float), st));
   }
   if (tail > 0) {
     if (dtype == NSA_DTYPE_BF16)
