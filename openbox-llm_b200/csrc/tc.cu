@@ -61,7 +61,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr uint32_t kIdescPV = idesc_bf16(128, D, 0, 1);
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + L::kQBytes;
   uint8_t* sV = sK + 2 * L::kKVBytes;
@@ -186,21 +186,22 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tma_load_3d(sV + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_v, bar, s * 64, key0_of(i), bh);
     };
     auto issue_s = [&](int i) {   // S = Q K^T for tile i
-      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (i & 1) * L::kKVBytes);
+      const uint32_t qa = desc_lo_kmajor(smem_u32(sQ));
+      const uint32_t ka = desc_lo_kmajor(smem_u32(sK + (i & 1) * L::kKVBytes));
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + kColS, desc_kmajor(qa + slab * (kRows * 128) + in),
-               desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescQK, kk > 0);
+        mma_ss(tmem + kColS, desc_at(qa, slab * (kRows * 128) + in),
+               desc_at(ka, slab * (kKeys * 128) + in), kIdescQK, kk > 0);
       }
       tc_commit(bar_s);
     };
     auto issue_pv = [&](int i) {  // O (+)= P V for tile i
-      const uint32_t va = smem_u32(sV + (i & 1) * L::kKVBytes);
+      const uint32_t va = desc_lo_mnmajor(smem_u32(sV + (i & 1) * L::kKVBytes), kKeys * 128);
 #pragma unroll
       for (int kk = 0; kk < kKeys / 16; ++kk)
-        mma_ts(tmem + kColO, tmem + kColP + kk * 8, desc_mnmajor(va + kk * 2048, kKeys * 128),
-               kIdescPV, (i > 0) || (kk > 0));
+        mma_ts(tmem + kColO, tmem + kColP + kk * 8, desc_at(va, kk * 2048), kIdescPV,
+               (i > 0) || (kk > 0));
       tc_commit(bar_o);
     };
 
@@ -361,7 +362,7 @@ bool tc_shape_ok(const NsaDims& d, int block_size) {
   if (d.D != 64 && d.D != 128) return false;
   if (block_size != tc::kKeys) return false;
   const int G = d.Hq / d.Hkv;
-  if (G > 128) return false;
+  if (G < 2 || G > 128) return false;   // the backward tiles hold at most 64 queries
   if (d.T < 1) return false;
   const int nq = tc::kRows / tc::group_pad(G);
   const int nb = (d.T + tc::kKeys - 1) / tc::kKeys;

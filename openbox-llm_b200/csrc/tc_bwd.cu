@@ -42,7 +42,21 @@ struct BwdArgs {
   int kind, window, block_size;
   int n_ktiles, n_slots;
   float scale, scale_log2;
+#ifdef NSA_TRACE
+  long long* trace;            // development builds only: stage time stamps of one CTA
+#endif
 };
+
+#ifdef NSA_TRACE
+#define NSA_STAMP(k)                                                                       \
+  do {                                                                                     \
+    if (p.trace && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0 &&    \
+        lt == 33 && it_no < 48)                                                            \
+      p.trace[(grp * 48 + it_no) * 12 + (k)] = clock64();                                   \
+  } while (0)
+#else
+#define NSA_STAMP(k) do {} while (0)
+#endif
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
@@ -59,12 +73,15 @@ constexpr int kRowTileBytes = kRows * 128 * 2;   // Q or dO row tile: always two
 constexpr int kPBytes = kRows * 128;             // P or dS: 128 rows x 64 keys bf16
 constexpr int kGroupThreads = 256;               // one compute group: 2 warps per TMEM lane quadrant
 constexpr int kGroupBytes = 2 * kRowTileBytes + 2 * kPBytes;   // Q, dO, P, dS of one group
+constexpr int kMaxNq = 64;                       // queries per row tile (group size >= 2)
 
 __host__ __device__ inline size_t bwd_smem_bytes(int D) {
   return (size_t)2 * kKeys * 128 * (D / 64)      // K, V
          + 2 * (size_t)kGroupBytes               // two groups
-         + 256 + 2 * 128 * 4                     // barriers, row index tables
-         + 1024;
+         + 256                                   // barriers
+         + 2 * 2 * kMaxNq * 4                    // query positions, double buffered, per group
+         + 2 * 128 * 4                           // partial-row index of each tile row, per group
+         + 768;                                  // alignment slack (checked at run time)
 }
 
 __device__ __forceinline__ void group_sync(int group) {
@@ -74,10 +91,15 @@ __device__ __forceinline__ void group_sync(int group) {
 // Two compute groups of 256 threads share the key tile and the dK^T / dV^T accumulators and
 // take alternate row tiles, so that one group's MMAs and memory waits overlap the other
 // group's arithmetic.  Inside a group, the two warps of a TMEM lane quadrant split the 64 key
-// columns of a row between them.
+// columns of a row between them.  Row r of a tile is head r % G of the tile's query r / G: the
+// G rows of a query arrive by one TMA box each for Q and dO (128B swizzle), whatever the query
+// list looks like, and leave as bf16 dQ partials through a swizzled staging tile so that the
+// global stores are whole 256-byte rows.
 template <int D>
 __global__ void __launch_bounds__(512, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+              const __grid_constant__ CUtensorMap tm_q_run, const __grid_constant__ CUtensorMap tm_do_run,
               const BwdArgs p) {
   constexpr int kSlabs = D / 64;
   constexpr int kKVBytes = kKeys * 128 * kSlabs;
@@ -88,15 +110,16 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   constexpr uint32_t kIdescDQ = idesc_bf16(128, D, 0, 1);        // rows x d
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
   uint8_t* sK = smem;
   uint8_t* sV = sK + kKVBytes;
   uint8_t* sGroup = sV + kKVBytes;
   uint64_t* bars = (uint64_t*)(sGroup + 2 * kGroupBytes);
   uint64_t* bar_kv = bars + 0;
-  uint32_t* s_tmem = (uint32_t*)(bars + 6);
+  uint32_t* s_tmem = (uint32_t*)(bars + 8);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
-  int* s_rowoff_all = (int*)(bars + 8);   // [2][128] row index into [B*Hq*T] of each tile row, -1 = none
+  int* s_rowt_all = (int*)(bars + 10);               // [2 groups][2 buffers][kMaxNq]
+  uint32_t* s_prow_all = (uint32_t*)(s_rowt_all + 2 * 2 * kMaxNq);   // [2][128]
 
   const int tid = threadIdx.x;
   const int grp = tid / kGroupThreads, lt = tid % kGroupThreads;
@@ -107,9 +130,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint8_t* sDO = sQ + kRowTileBytes;
   uint8_t* sP = sDO + kRowTileBytes;
   uint8_t* sDS = sP + kPBytes;
-  uint64_t* bar_sp = bars + 1 + 2 * grp;
-  uint64_t* bar_acc = bars + 2 + 2 * grp;
-  int* s_rowoff = s_rowoff_all + grp * 128;
+  uint64_t* bar_sp = bars + 1 + 3 * grp;
+  uint64_t* bar_acc = bars + 2 + 3 * grp;
+  uint64_t* bar_g = bars + 3 + 3 * grp;
+  int* s_rowt = s_rowt_all + grp * 2 * kMaxNq;
+  uint32_t* s_prow = s_prow_all + grp * 128;
 
   const int j = blockIdx.x;                          // key tile
   const int bh = blockIdx.y;
@@ -154,22 +179,26 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   }
 
   if (tid == 0) {
-    *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
-    mbar_init(bar_kv, 1);
-    for (int k = 1; k <= 4; ++k) mbar_init(bars + k, 1);
-    fence_barrier_init();
-    prefetch_tensormap(&tm_k);
-    prefetch_tensormap(&tm_v);
-  }
-  if (D == 64) {   // the second slab of the row tiles is never gathered: keep it zero
-    for (int i = tid; i < 4 * (kRows * 128) / 16; i += blockDim.x) {
-      const int buf = i / ((kRows * 128) / 16), o16 = i % ((kRows * 128) / 16);
-      uint8_t* base = sGroup + (buf >> 1) * kGroupBytes + (buf & 1) * kRowTileBytes + kRows * 128;
-      *reinterpret_cast<uint4*>(base + o16 * 16) = make_uint4(0, 0, 0, 0);
+    int bad = (*(volatile int*)p.status != 0) ? 1 : 0;
+    if ((size_t)((uint8_t*)(s_prow_all + 2 * 128) - smem_raw) > bwd_smem_bytes(D)) {
+      atomicOr(p.status, 256);   // the shared-memory window is less aligned than assumed
+      bad = 1;
     }
+    *s_abort = bad;
+    for (int k = 0; k <= 6; ++k) mbar_init(bars + k, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_do);
   }
   __syncthreads();
   if (*s_abort) return;
+  // Rows past nq * G of a tile (and, for D = 64, the second slab) are never loaded: keep them 0.
+  for (int i = tid; i < 2 * 2 * kRowTileBytes / 16; i += blockDim.x) {
+    const int buf = i / (kRowTileBytes / 16), o16 = i % (kRowTileBytes / 16);
+    uint8_t* base = sGroup + (buf >> 1) * kGroupBytes + (buf & 1) * kRowTileBytes;
+    *reinterpret_cast<uint4*>(base + o16 * 16) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async();
 
   if (tid < 32) {
     tmem_alloc(s_tmem, kTmemCols);
@@ -208,64 +237,88 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   auto row_query = [&](int i) -> int {
     const int qi = i * p.nq + ql;
     if (!row_slot_ok || qi >= n_q) return -1;
-    if (p.kind == 2) return __ldg(p.q_of_block + pair_base + qi);
+    if (p.kind == 2) return ldg_s32_now(p.q_of_block + pair_base + qi);
     return t_lo + qi;
   };
+  auto row_index = [&](int t) -> size_t { return (size_t)(b * p.Hq + head) * p.T + t; };
+  // one TMA box per query and slab for Q and for dO; a missing query reads past T: zeros
+  const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs * 2);
+  auto gather = [&](const int* rowt) {
+    if (wg == 0 && p.kind != 2) {
+      // window / compression: the tile's queries are consecutive tokens, one box per slab
+      if (lane == 0) {
+        mbar_expect_tx(bar_g, gather_bytes);
+        const int tq = rowt[0] >= 0 ? rowt[0] : p.T;
+#pragma unroll
+        for (int s = 0; s < kSlabs; ++s) {
+          tma_load_3d(sQ + s * (kRows * 128), &tm_q_run, bar_g, s * 64, b * p.Hq + hkv * p.G, tq);
+          tma_load_3d(sDO + s * (kRows * 128), &tm_do_run, bar_g, s * 64, b * p.Hq + hkv * p.G, tq);
+        }
+      }
+    } else if (wg == 0) {
+      if (lane == 0) mbar_expect_tx(bar_g, gather_bytes);
+      __syncwarp();
+      for (int qq = lane; qq < p.nq; qq += 32) {
+        const int tq = rowt[qq] >= 0 ? rowt[qq] : p.T;
+#pragma unroll
+        for (int s = 0; s < kSlabs; ++s) {
+          tma_load_3d(sQ + s * (kRows * 128) + qq * p.G * 128, &tm_q, bar_g, s * 64,
+                      b * p.Hq + hkv * p.G, tq);
+          tma_load_3d(sDO + s * (kRows * 128) + qq * p.G * 128, &tm_do, bar_g, s * 64,
+                      b * p.Hq + hkv * p.G, tq);
+        }
+      }
+    }
+  };
 
+  // Row metadata runs ahead of the work: the query position two tiles ahead (t_nxt) and, one
+  // iteration later, its lse / delta, so that no dependent global load is waited for in line.
   int i = rt_begin + grp;
   int t_cur = i < rt_end ? row_query(i) : -1;
-  float lse2_cur = 0.f, delta_cur = 0.f;
+  int t_nxt = i + 2 < rt_end ? row_query(i + 2) : -1;
+  float lse_cur = 0.f, delta_cur = 0.f;
   if (t_cur >= 0) {
-    const size_t ri = (size_t)(b * p.Hq + head) * p.T + t_cur;
-    lse2_cur = __ldg(p.lse + ri) * kLog2e;
-    delta_cur = __ldg(p.delta + ri);
+    lse_cur = __ldg(p.lse + row_index(t_cur));
+    delta_cur = __ldg(p.delta + row_index(t_cur));
+  }
+  int buf = 0;
+  if (i < rt_end) {
+    if (g == 0 && half == 0 && row_slot_ok) s_rowt[ql] = t_cur;
+    group_sync(grp);
+    gather(s_rowt);
   }
   uint32_t phase = 0;
-  for (; i < rt_end; i += 2, phase ^= 1) {
-    if (half == 0)
-      s_rowoff[row] = t_cur >= 0 ? (int)((size_t)(b * p.Hq + head) * p.T + t_cur) : -1;
-    group_sync(grp);     // row offsets visible; the previous tile's MMAs were waited for by all
-    {   // gather the Q and dO rows (16-byte chunks, 128B swizzle); missing rows are zero-filled
-      constexpr int kChunks = D / 8;
-      constexpr int kRowsPerPass = kGroupThreads / kChunks;
-      const int c = lt % kChunks;
-      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO);
-#pragma unroll 4
-      for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
-        const int off = s_rowoff[r];
-        const size_t src = off >= 0 ? (size_t)off * D + c * 8 : 0;
-        const uint32_t dst = (uint32_t)((c >> 3) * (kRows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
-        const uint32_t nbytes = off >= 0 ? 16u : 0u;
-        cp_async16(q_base + dst, p.q + src, nbytes);
-        cp_async16(do_base + dst, p.d_o + src, nbytes);
-      }
-      cp_async_commit();
+  int it_no = 0;
+  (void)it_no;
+  for (; i < rt_end; i += 2, phase ^= 1, ++it_no, buf ^= 1) {
+    NSA_STAMP(0);
+    const int t_nn = (i + 4 < rt_end) ? row_query(i + 4) : -1;
+    float lse_nxt = 0.f, delta_nxt = 0.f;
+    if (t_nxt >= 0) {
+      lse_nxt = ldg_f32_now(p.lse + row_index(t_nxt));
+      delta_nxt = ldg_f32_now(p.delta + row_index(t_nxt));
     }
-    // metadata of this group's next tile: the loads overlap the gather
-    const int t_next = (i + 2 < rt_end) ? row_query(i + 2) : -1;
-    float lse2_next = 0.f, delta_next = 0.f;
-    if (t_next >= 0) {
-      const size_t ri = (size_t)(b * p.Hq + head) * p.T + t_next;
-      lse2_next = __ldg(p.lse + ri) * kLog2e;
-      delta_next = __ldg(p.delta + ri);
-    }
-    cp_async_wait_all();
-    fence_proxy_async();
-    group_sync(grp);
+    // query positions of this group's next tile, for the gather issued further down
+    if (g == 0 && half == 0 && row_slot_ok) s_rowt[(buf ^ 1) * kMaxNq + ql] = t_nxt;
+    mbar_wait(bar_g, phase, p.status, s_abort, 512);
+    NSA_STAMP(1);
+    group_sync(grp);       // also: the staging tile of the previous iteration has been read
+    NSA_STAMP(2);
     if (lt == 0) {
       tc_fence_after();
-      const uint32_t qa = smem_u32(sQ), da = smem_u32(sDO), ka = smem_u32(sK), va = smem_u32(sV);
+      const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), da = desc_lo_kmajor(smem_u32(sDO));
+      const uint32_t ka = desc_lo_kmajor(smem_u32(sK)), va = desc_lo_kmajor(smem_u32(sV));
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + colS, desc_kmajor(qa + slab * (kRows * 128) + in),
-               desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescS, kk > 0);
+        mma_ss(tmem + colS, desc_at(qa, slab * (kRows * 128) + in),
+               desc_at(ka, slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + colDP, desc_kmajor(da + slab * (kRows * 128) + in),
-               desc_kmajor(va + slab * (kKeys * 128) + in), kIdescS, kk > 0);
+        mma_ss(tmem + colDP, desc_at(da, slab * (kRows * 128) + in),
+               desc_at(va, slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
       tc_commit(bar_sp);
     }
@@ -281,7 +334,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         hi = min(kKeys - 1, min(t_cur, p.T - 1) - key0);
       }
     }
+    const float lse2_cur = lse_cur * kLog2e;
     mbar_wait(bar_sp, phase, p.status, s_abort, 64);
+    NSA_STAMP(3);
     tc_fence_after();
     __syncwarp();
     {
@@ -314,59 +369,98 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     fence_proxy_async();
     tc_fence_before();
+    NSA_STAMP(4);
     group_sync(grp);
     if (lt == 0) {
       tc_fence_after();
-      const uint32_t qa = smem_u32(sQ), da = smem_u32(sDO);
-      const uint32_t pa = smem_u32(sP), dsa = smem_u32(sDS), ka = smem_u32(sK);
+      const uint32_t qa = desc_lo_mnmajor(smem_u32(sQ), kRows * 128);
+      const uint32_t da = desc_lo_mnmajor(smem_u32(sDO), kRows * 128);
+      const uint32_t pa = desc_lo_mnmajor(smem_u32(sP), 0), dsa = desc_lo_mnmajor(smem_u32(sDS), 0);
+      const uint32_t dsk = desc_lo_kmajor(smem_u32(sDS)), ka = desc_lo_mnmajor(smem_u32(sK), kKeys * 128);
 #pragma unroll
       for (int kk = 0; kk < kRows / 16; ++kk)        // contraction over the 128 rows
-        mma_ss(tmem + kColDV, desc_mnmajor(da + kk * 2048, kRows * 128), desc_mnmajor(pa + kk * 2048, 0),
-               kIdescT, 1);
+        mma_ss(tmem + kColDV, desc_at(da, kk * 2048), desc_at(pa, kk * 2048), kIdescT, 1);
 #pragma unroll
       for (int kk = 0; kk < kRows / 16; ++kk)
-        mma_ss(tmem + kColDK, desc_mnmajor(qa + kk * 2048, kRows * 128), desc_mnmajor(dsa + kk * 2048, 0),
-               kIdescT, 1);
+        mma_ss(tmem + kColDK, desc_at(qa, kk * 2048), desc_at(dsa, kk * 2048), kIdescT, 1);
 #pragma unroll
       for (int kk = 0; kk < kKeys / 16; ++kk)        // contraction over the 64 keys
-        mma_ss(tmem + colDQ, desc_kmajor(dsa + kk * 32), desc_mnmajor(ka + kk * 2048, kKeys * 128),
-               kIdescDQ, kk > 0);
+        mma_ss(tmem + colDQ, desc_at(dsk, kk * 32), desc_at(ka, kk * 2048), kIdescDQ, kk > 0);
       tc_commit(bar_acc);
     }
-    // where this row's dQ partial goes
-    size_t pidx = 0;
-    if (t_cur >= 0) {
-      if (p.kind == 2) {
-        pidx = ((size_t)(pair_base + i * p.nq + ql) * p.G + g) * D;
-      } else {
-        const int slot = p.kind == 0 ? j - (max(0, t_cur - p.window + 1) >> 6) : j;
-        pidx = ((((size_t)bh * p.T + t_cur) * p.n_slots + slot) * p.G + g) * D;
+    // row of the partial buffer that takes this row's dQ
+    if (half == 0) {
+      uint32_t prow = 0xffffffffu;
+      if (t_cur >= 0) {
+        if (p.kind == 2) {
+          prow = (uint32_t)((size_t)(pair_base + i * p.nq + ql) * p.G + g);
+        } else {
+          const int slot = p.kind == 0 ? j % p.n_slots : j;
+          prow = (uint32_t)((((size_t)bh * p.T + t_cur) * p.n_slots + slot) * p.G + g);
+        }
       }
+      s_prow[row] = prow;
     }
     mbar_wait(bar_acc, phase, p.status, s_abort, 128);
+    NSA_STAMP(5);
     tc_fence_after();
+    // the row tiles are free again: fetch this group's next tile
+    if (i + 2 < rt_end) gather(s_rowt + (buf ^ 1) * kMaxNq);
+    NSA_STAMP(6);
     __syncwarp();
+    // dQ: TMEM -> bf16 -> staging tile (P/dS region, 256-byte rows, 16-byte chunks XOR row)
+    {
+      const uint32_t stage_row = smem_u32(sP) + row * 256;
 #pragma unroll
-    for (int cc = 0; cc < D / 64; ++cc) {            // this thread's half of the D columns
-      const int col0 = half * (D / 2) + cc * 32;
-      uint32_t r32[32];
-      tmem_ld32(lane_base + colDQ + col0, r32);
-      tmem_wait_ld();
-      if (t_cur >= 0) {
-        uint4* dst = reinterpret_cast<uint4*>(p.dq_part + pidx + col0);
+      for (int cc = 0; cc < D / 64; ++cc) {          // this thread's half of the D columns
+        const int col0 = half * (D / 2) + cc * 32;
+        uint32_t r32[32];
+        tmem_ld32(lane_base + colDQ + col0, r32);
+        tmem_wait_ld();
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
-          uint4 u;
-          u.x = pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1]));
-          u.y = pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3]));
-          u.z = pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5]));
-          u.w = pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7]));
-          dst[v4] = u;
+          const uint32_t chunk = (uint32_t)((col0 >> 3) + v4);
+          st_shared_v4(stage_row + ((chunk ^ (row & 15)) << 4),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1])),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3])),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5])),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7])));
         }
       }
     }
     tc_fence_before();
-    t_cur = t_next; lse2_cur = lse2_next; delta_cur = delta_next;
+    NSA_STAMP(8);
+    group_sync(grp);
+    NSA_STAMP(9);
+    {   // whole rows out: 16 lanes write the 256 (D = 128) or 128 bytes of one row
+      constexpr int kChunks = D / 8;
+      constexpr int kRowsPerPass = kGroupThreads / kChunks;
+      const int c = lt % kChunks;
+#if defined(NSA_EXP) && NSA_EXP == 3
+      if (c == 12345)
+#endif
+#pragma unroll 4
+      for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
+#if defined(NSA_EXP) && NSA_EXP == 2
+        const uint32_t prow = (uint32_t)(r + it_no * 128 + j * 1024);
+#else
+        const uint32_t prow = s_prow[r];
+#endif
+        if (prow != 0xffffffffu) {
+#if defined(NSA_EXP) && NSA_EXP == 2
+          const uint4 v = make_uint4(r, c, r, c);
+#else
+          const uint4 v = *reinterpret_cast<const uint4*>(sP + r * 256 + ((c ^ (r & 15)) << 4));
+#endif
+#if defined(NSA_EXP) && NSA_EXP == 1
+          if (v.x == 0x12345678u)
+#endif
+          *reinterpret_cast<uint4*>(p.dq_part + (size_t)prow * D + c * 8) = v;
+        }
+      }
+    }
+    NSA_STAMP(7);
+    t_cur = t_nxt; t_nxt = t_nn; lse_cur = lse_nxt; delta_cur = delta_nxt;
   }
 
   // ---- dK^T, dV^T: lane = d, column = key; group 0 writes dV, group 1 writes dK ---------------
@@ -452,7 +546,7 @@ __global__ void dq_reduce_kernel(const __nv_bfloat16* __restrict__ part, const i
     if (kind == 0) { first = max(0, t - window + 1) >> 6; last = t >> 6; }
     else { first = 0; last = (min(Lk, (t + 1) / block_size) - 1); last = last < 0 ? -1 : last >> 6; }
     for (int jt = first; jt <= last; ++jt) {
-      const int slot = kind == 0 ? jt - first : jt;
+      const int slot = kind == 0 ? jt % n_slots : jt;
       add((bh * T + t) * n_slots + slot);
     }
   }
@@ -462,6 +556,18 @@ __global__ void dq_reduce_kernel(const __nv_bfloat16* __restrict__ part, const i
   u.z = pack_bf16(acc[4], acc[5]); u.w = pack_bf16(acc[6], acc[7]);
   *reinterpret_cast<uint4*>(dq + (((size_t)b * Hq + hkv * G + g) * T + t) * D + v * 8) = u;
 }
+
+#ifdef NSA_TRACE
+}  // namespace tc
+}  // namespace nsa
+static long long* g_trace_dev = nullptr;
+extern "C" long long* nsa_trace_buffer() {
+  if (!g_trace_dev) { cudaMalloc(&g_trace_dev, 2 * 48 * 12 * sizeof(long long)); cudaMemset(g_trace_dev, 0, 2 * 48 * 12 * sizeof(long long)); }
+  return g_trace_dev;
+}
+namespace nsa {
+namespace tc {
+#endif
 
 static const char* const kBwdNames[3] = {"tc_bwd_win", "tc_bwd_cmp", "tc_bwd_slc"};
 static const char* const kRedNames[3] = {"dq_reduce_win", "dq_reduce_cmp", "dq_reduce_slc"};
@@ -550,6 +656,9 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.n_ktiles = pl.n_ktiles; p.n_slots = pl.n_slots;
   p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
   p.split_chunk = pl.split_chunk;
+#ifdef NSA_TRACE
+  p.trace = nsa_trace_buffer();
+#endif
   const size_t n_kv = (size_t)a.B * a.Hkv * a.Lk * a.D;
   p.dk_acc = (float*)(base + pl.off_acc);
   p.dv_acc = (float*)(base + pl.off_acc + align_up(n_kv * sizeof(float), 256));
@@ -572,20 +681,25 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
                                 pl.off_qob - pl.off_csr_ws, st);
     if (rc != NSA_OK) return rc;
   }
-  CUtensorMap tm_k, tm_v;
+  CUtensorMap tm_k, tm_v, tm_q, tm_do;
   int rc = make_map(&tm_k, a.k, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
   if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
+  if (rc == NSA_OK) rc = make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
+  if (rc == NSA_OK) rc = make_map_query_rows(&tm_do, a.d_o, a.D, a.T, a.B * a.Hq, G);
+  CUtensorMap tm_q_run, tm_do_run;
+  if (rc == NSA_OK) rc = make_map_query_rows(&tm_q_run, a.q, a.D, a.T, a.B * a.Hq, G, pl.nq);
+  if (rc == NSA_OK) rc = make_map_query_rows(&tm_do_run, a.d_o, a.D, a.T, a.B * a.Hq, G, pl.nq);
   if (rc != NSA_OK) return rc;
   const size_t smem = bwd_smem_bytes(a.D);
   dim3 grid(pl.n_ktiles, a.B * a.Hkv, pl.n_splits);
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, p);
+    tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, p);
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, p);
+    tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, p);
   }
   NSA_LAUNCH_OK("tc_bwd_kernel");
   if (pl.n_splits > 1) {

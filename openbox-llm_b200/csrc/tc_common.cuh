@@ -162,6 +162,19 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr, uint32_t lbo_byte
   d |= 2ull << 61;   // SWIZZLE_128B
   return d;
 }
+// The upper word of every descriptor used here is the same constant (SBO = 1024 bytes, version,
+// 128B swizzle); the lower word is address >> 4 plus the LBO field, so stepping a descriptor by
+// a byte offset that is a multiple of 16 is one 32-bit add.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3fffu) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t saddr, uint32_t slab_bytes) {
+  return ((saddr >> 4) & 0x3fffu) | (((slab_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ uint64_t desc_at(uint32_t lo, uint32_t byte_offset) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo + (byte_offset >> 4)), "r"(kDescHi));
+  return d;
+}
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) { return desc_sw128(saddr, 16, 1024); }
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t slab_bytes) {
   return desc_sw128(saddr, slab_bytes, 1024);
@@ -192,6 +205,19 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// Loads that must be issued where they are written: ptxas otherwise sinks a prefetch down to its
+// first use (a whole loop iteration later) and the warp then waits out the full memory latency.
+__device__ __forceinline__ float ldg_f32_now(const float* ptr) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
+  return v;
+}
+__device__ __forceinline__ int ldg_s32_now(const int32_t* ptr) {
+  int v;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
 }
 
 __device__ __forceinline__ float ex2(float x) {

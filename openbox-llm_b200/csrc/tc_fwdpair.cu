@@ -36,35 +36,40 @@ __device__ __forceinline__ void cp_async16p(uint32_t dst, const void* src, uint3
 
 constexpr int kPairGroupThreads = 256;
 
+constexpr int kPairMaxNq = 64;
+
 __host__ __device__ inline size_t pair_smem_bytes(int D) {
-  return (size_t)2 * kKeys * 128 * (D / 64) + 2 * ((size_t)kRows * 128 * (D / 64) + kRows * 128) +
-         256 + 2 * 128 * 4 + 2 * 128 * 2 * 4 + 1024;
+  return (size_t)2 * kKeys * 128 * (D / 64) +
+         2 * ((size_t)kRows * 128 * (D / 64) + kRows * 128 + kRows * 256) +   // Q, P, staging
+         256 + 2 * 2 * kPairMaxNq * 4 + 2 * 128 * 4 + 2 * 128 * 2 * 4 + 1024;
 }
 
 template <int D>
 __global__ void __launch_bounds__(512, 1)
 tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                  const PairArgs p) {
+                  const __grid_constant__ CUtensorMap tm_q, const PairArgs p) {
   constexpr int kSlabs = D / 64;
   constexpr int kKVBytes = kKeys * 128 * kSlabs;
   constexpr int kQBytes = kRows * 128 * kSlabs;
   constexpr int kPBytes = kRows * 128;
-  constexpr int kGroupBytes = kQBytes + kPBytes;
+  constexpr int kStageBytes = kRows * 256;
+  constexpr int kGroupBytes = kQBytes + kPBytes + kStageBytes;
   constexpr uint32_t kTmemCols = 256;
   constexpr uint32_t kIdescS = idesc_bf16(128, kKeys, 0, 0);
   constexpr uint32_t kIdescPV = idesc_bf16(128, D, 0, 1);
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
   uint8_t* sK = smem;
   uint8_t* sV = sK + kKVBytes;
   uint8_t* sGroup = sV + kKVBytes;
   uint64_t* bars = (uint64_t*)(sGroup + 2 * kGroupBytes);
   uint64_t* bar_kv = bars + 0;
-  uint32_t* s_tmem = (uint32_t*)(bars + 6);
+  uint32_t* s_tmem = (uint32_t*)(bars + 8);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
-  int* s_rowoff_all = (int*)(bars + 8);                 // [2][128]
-  float* s_max_all = (float*)(s_rowoff_all + 2 * 128);  // [2][128][2]
+  int* s_rowt_all = (int*)(bars + 10);                  // [2 groups][2 buffers][kPairMaxNq]
+  uint32_t* s_prow_all = (uint32_t*)(s_rowt_all + 2 * 2 * kPairMaxNq);   // [2][128]
+  float* s_max_all = (float*)(s_prow_all + 2 * 128);    // [2][128][2]
 
   const int tid = threadIdx.x;
   const int grp = tid / kPairGroupThreads, lt = tid % kPairGroupThreads;
@@ -73,9 +78,12 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   const int row = quad * 32 + lane;
   uint8_t* sQ = sGroup + grp * kGroupBytes;
   uint8_t* sP = sQ + kQBytes;
-  uint64_t* bar_s = bars + 1 + 2 * grp;
-  uint64_t* bar_o = bars + 2 + 2 * grp;
-  int* s_rowoff = s_rowoff_all + grp * 128;
+  uint8_t* sStage = sP + kPBytes;
+  uint64_t* bar_s = bars + 1 + 3 * grp;
+  uint64_t* bar_o = bars + 2 + 3 * grp;
+  uint64_t* bar_g = bars + 3 + 3 * grp;
+  int* s_rowt = s_rowt_all + grp * 2 * kPairMaxNq;
+  uint32_t* s_prow = s_prow_all + grp * 128;
   float* s_max = s_max_all + grp * 256;
 
   const int j = blockIdx.x, bh = blockIdx.y;
@@ -93,13 +101,20 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 
   if (tid == 0) {
     *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
-    for (int k = 0; k <= 4; ++k) mbar_init(bars + k, 1);
+    for (int k = 0; k <= 6; ++k) mbar_init(bars + k, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
+    prefetch_tensormap(&tm_q);
   }
   __syncthreads();
   if (*s_abort) return;
+  // rows past nq * G of a tile are never loaded: keep them zero
+  for (int i = tid; i < 2 * kQBytes / 16; i += blockDim.x) {
+    uint8_t* base = sGroup + (i / (kQBytes / 16)) * kGroupBytes;
+    *reinterpret_cast<uint4*>(base + (i % (kQBytes / 16)) * 16) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async();
   if (tid < 32) {
     tmem_alloc(s_tmem, kTmemCols);
     tmem_relinquish();
@@ -124,42 +139,47 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   auto row_query = [&](int i) -> int {
     const int qi = i * p.nq + ql;
     if (!row_slot_ok || qi >= n_q) return -1;
-    return __ldg(p.q_of_block + pair_base + qi);
+    return ldg_s32_now(p.q_of_block + pair_base + qi);
+  };
+
+  const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs);
+  auto gather = [&](const int* rowt) {      // one TMA box per query and slab; no query: zeros
+    if (wg == 0) {
+      if (lane == 0) mbar_expect_tx(bar_g, gather_bytes);
+      __syncwarp();
+      for (int qq = lane; qq < p.nq; qq += 32) {
+        const int tq = rowt[qq] >= 0 ? rowt[qq] : p.T;
+#pragma unroll
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(sQ + s * (kRows * 128) + qq * p.G * 128, &tm_q, bar_g, s * 64,
+                      b * p.Hq + hkv * p.G, tq);
+      }
+    }
   };
 
   int i = grp;
   int t_cur = i < n_rt ? row_query(i) : -1;
-  uint32_t phase = 0;
-  for (; i < n_rt; i += 2, phase ^= 1) {
-    if (half == 0)
-      s_rowoff[row] = t_cur >= 0 ? (int)((size_t)(b * p.Hq + head) * p.T + t_cur) : -1;
+  int t_nxt = i + 2 < n_rt ? row_query(i + 2) : -1;
+  int buf = 0;
+  if (i < n_rt) {
+    if (g == 0 && half == 0 && row_slot_ok) s_rowt[ql] = t_cur;
     asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(kPairGroupThreads) : "memory");
-    {
-      constexpr int kChunks = D / 8;
-      constexpr int kRowsPerPass = kPairGroupThreads / kChunks;
-      const int c = lt % kChunks;
-      const uint32_t q_base = smem_u32(sQ);
-#pragma unroll 4
-      for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
-        const int off = s_rowoff[r];
-        const size_t src = off >= 0 ? (size_t)off * D + c * 8 : 0;
-        const uint32_t dst = (uint32_t)((c >> 3) * (kRows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
-        cp_async16p(q_base + dst, p.q + src, off >= 0 ? 16u : 0u);
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    const int t_next = (i + 2 < n_rt) ? row_query(i + 2) : -1;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    fence_proxy_async();
+    gather(s_rowt);
+  }
+  uint32_t phase = 0;
+  for (; i < n_rt; i += 2, phase ^= 1, buf ^= 1) {
+    const int t_nn = (i + 4 < n_rt) ? row_query(i + 4) : -1;
+    if (g == 0 && half == 0 && row_slot_ok) s_rowt[(buf ^ 1) * kPairMaxNq + ql] = t_nxt;
+    mbar_wait(bar_g, phase, p.status, s_abort, 512);
     asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(kPairGroupThreads) : "memory");
     if (lt == 0) {
       tc_fence_after();
-      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
+      const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), ka = desc_lo_kmajor(smem_u32(sK));
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + col0, desc_kmajor(qa + slab * (kRows * 128) + in),
-               desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescS, kk > 0);
+        mma_ss(tmem + col0, desc_at(qa, slab * (kRows * 128) + in),
+               desc_at(ka, slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
       tc_commit(bar_s);
     }
@@ -170,6 +190,9 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     uint32_t rs[32];
     tmem_ld32(lane_base + col0 + half * 32, rs);
     tmem_wait_ld();
+    // S is done, so the Q tile is free: fetch this group's next tile
+    if (i + 2 < n_rt) gather(s_rowt + (buf ^ 1) * kPairMaxNq);
+    __syncwarp();
     float x[32];
     float mx = -INFINITY;
 #pragma unroll
@@ -202,11 +225,10 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(kPairGroupThreads) : "memory");
     if (lt == 0) {
       tc_fence_after();
-      const uint32_t pa = smem_u32(sP), va = smem_u32(sV);
+      const uint32_t pa = desc_lo_kmajor(smem_u32(sP)), va = desc_lo_mnmajor(smem_u32(sV), kKeys * 128);
 #pragma unroll
       for (int kk = 0; kk < kKeys / 16; ++kk)
-        mma_ss(tmem + col0, desc_kmajor(pa + kk * 32), desc_mnmajor(va + kk * 2048, kKeys * 128),
-               kIdescPV, kk > 0);
+        mma_ss(tmem + col0, desc_at(pa, kk * 32), desc_at(va, kk * 2048), kIdescPV, kk > 0);
       tc_commit(bar_o);
     }
     const size_t prow = (size_t)(pair_base + i * p.nq + ql) * p.G + g;
@@ -214,30 +236,47 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       if (half == 0) p.ml[prow * 3] = m;
       p.ml[prow * 3 + 1 + half] = lsum;
     }
+    if (half == 0) s_prow[row] = t_cur >= 0 ? (uint32_t)prow : 0xffffffffu;
     mbar_wait(bar_o, phase, p.status, s_abort, 128);
     tc_fence_after();
     __syncwarp();
+    {   // O_part: TMEM -> bf16 -> staging tile (256-byte rows, 16-byte chunks XOR row)
+      const uint32_t stage_row = smem_u32(sStage) + row * 256;
 #pragma unroll
-    for (int cc = 0; cc < D / 64; ++cc) {
-      const int c0 = half * (D / 2) + cc * 32;
-      uint32_t r32[32];
-      tmem_ld32(lane_base + col0 + c0, r32);
-      tmem_wait_ld();
-      if (t_cur >= 0) {
-        uint4* dst = reinterpret_cast<uint4*>(p.o_part + prow * D + c0);
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c0 = half * (D / 2) + cc * 32;
+        uint32_t r32[32];
+        tmem_ld32(lane_base + col0 + c0, r32);
+        tmem_wait_ld();
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
-          uint4 u;
-          u.x = pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1]));
-          u.y = pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3]));
-          u.z = pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5]));
-          u.w = pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7]));
-          dst[v4] = u;
+          const uint32_t chunk = (uint32_t)((c0 >> 3) + v4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((chunk ^ (row & 15)) << 4)),
+                       "r"(pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1]))),
+                       "r"(pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3]))),
+                       "r"(pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5]))),
+                       "r"(pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7])))
+                       : "memory");
         }
       }
     }
     tc_fence_before();
-    t_cur = t_next;
+    asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(kPairGroupThreads) : "memory");
+    {   // whole rows out
+      constexpr int kChunks = D / 8;
+      constexpr int kRowsPerPass = kPairGroupThreads / kChunks;
+      const int c = lt % kChunks;
+#pragma unroll 4
+      for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
+        const uint32_t pr = s_prow[r];
+        if (pr != 0xffffffffu) {
+          const uint4 v = *reinterpret_cast<const uint4*>(sStage + r * 256 + ((c ^ (r & 15)) << 4));
+          *reinterpret_cast<uint4*>(p.o_part + (size_t)pr * D + c * 8) = v;
+        }
+      }
+    }
+    tc_fence_before();
+    t_cur = t_nxt; t_nxt = t_nn;
   }
   tc_fence_before();
   __syncthreads();
@@ -408,9 +447,10 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.T = a.T; p.G = G; p.nq = pl.nq;
   p.n_ktiles = pl.n_ktiles; p.nq_union = nq_union; p.force = force;
   p.scale_log2 = a.scale * kLog2e;
-  CUtensorMap tm_k, tm_v;
+  CUtensorMap tm_k, tm_v, tm_q;
   rc = make_map(&tm_k, a.k, a.D, a.T, a.B * a.Hkv, kKeys, 1);
   if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.T, a.B * a.Hkv, kKeys, 1);
+  if (rc == NSA_OK) rc = make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
   if (rc != NSA_OK) return rc;
   const size_t smem = pair_smem_bytes(a.D);
   dim3 grid(pl.n_ktiles, a.B * a.Hkv);
@@ -418,14 +458,14 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   const unsigned cgrid = (unsigned)((nthreads + 255) / 256);
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, p); }
+    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, p); }
     { KernelScope ks("sel_combine_kernel", st);
       sel_combine_kernel<128><<<cgrid, 256, 0, st>>>(p.o_part, p.ml, pair_of_slot, offsets, stats,
                                                     (__nv_bfloat16*)a.o, a.lse, a.B, a.Hq, a.Hkv, a.T, G,
                                                     a.S, pl.n_ktiles, nq_union, p.force); }
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, p); }
+    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, p); }
     { KernelScope ks("sel_combine_kernel", st);
       sel_combine_kernel<64><<<cgrid, 256, 0, st>>>(p.o_part, p.ml, pair_of_slot, offsets, stats,
                                                    (__nv_bfloat16*)a.o, a.lse, a.B, a.Hq, a.Hkv, a.T, G,

@@ -41,6 +41,24 @@ static inline int make_map(CUtensorMap* m, const void* base, int D, int rows, in
   return NSA_OK;
 }
 
+// 3-D map over the same [heads, T, D] tensor with the head index as second dimension and the
+// token index as third: a box of 64 elements x G heads x 1 token brings the G rows of one query
+// of a GQA group into G consecutive 128-byte rows of shared memory.
+static inline int make_map_query_rows(CUtensorMap* m, const void* base, int D, int T, int heads, int G,
+                                      int box_tokens = 1) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available"); return NSA_ERR_CUDA; }
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)T};
+  cuuint64_t strides[2] = {(cuuint64_t)T * D * 2, (cuuint64_t)D * 2};
+  cuuint32_t box[3] = {64u, (cuuint32_t)G, (cuuint32_t)box_tokens};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (query rows) failed with %d", (int)r); return NSA_ERR_CUDA; }
+  return NSA_OK;
+}
+
 static inline int group_pad(int G) {
   int gp = 1;
   while (gp < G) gp <<= 1;

@@ -38,7 +38,7 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t kIdescQK = idesc_bf16(128, kKeys, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kQBytes;                        // 2 stages
   float* sP = (float*)(sK + 2 * kKBytes);            // [128][64] probabilities
@@ -103,12 +103,12 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_3d(sK + (i & 1) * kKBytes + s * (kKeys * 128), &tm_k, bar, s * 64, i * kKeys, bh);
     };
     auto issue_s = [&](int i) {
-      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (i & 1) * kKBytes);
+      const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), ka = desc_lo_kmajor(smem_u32(sK + (i & 1) * kKBytes));
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem, desc_kmajor(qa + slab * (kRows * 128) + in),
-               desc_kmajor(ka + slab * (kKeys * 128) + in), kIdescQK, kk > 0);
+        mma_ss(tmem, desc_at(qa, slab * (kRows * 128) + in), desc_at(ka, slab * (kKeys * 128) + in),
+               kIdescQK, kk > 0);
       }
       tc_commit(bar_s);
     };
