@@ -98,6 +98,24 @@ int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int Hkv, int T
                                  int32_t* pair_bh, void* workspace, size_t workspace_bytes,
                                  void* stream);
 
+/* The same CSR for callers that may not allocate device memory and have no scratch buffer to
+ * hand over: code running under a memory arena it does not own (an inference server's fixed
+ * pool, a plugin loaded into another framework's process), or a latency-critical thread that
+ * must not reach the driver's allocator, where a cudaMalloc can block on other streams' work.
+ * The scratch is a fixed array inside the library, nsa_csr_builtin_scratch_bytes() (8 MiB) per
+ * GPU that loads the library, held until the process exits; shapes whose
+ * nsa_csr_workspace_bytes exceeds it are refused with NSA_ERR_WORKSPACE and a message.  The
+ * call allocates nothing (no cudaMalloc / cudaFree, no allocating library routine); inputs and
+ * the three outputs are still the caller's.  The first call on a device looks up the array's
+ * device address; make that call outside any stream capture.  All calls on a device share the
+ * one array: it is cleared at the start of every call, and two calls whose kernels may overlap
+ * on the GPU (different streams, no ordering between them) would corrupt each other.
+ * This entry point has no counterpart in the reference. */
+size_t nsa_csr_builtin_scratch_bytes(void);
+int nsa_build_block_to_query_csr_noalloc(const int32_t* block_idx, int B, int Hkv, int T, int S,
+                                         int block_size, int32_t* q_of_block,
+                                         int32_t* block_offsets, int32_t* pair_bh, void* stream);
+
 /* ---- compression summaries ------------------------------------------------------------------
  * Mean pooling replaces block_mean_pool (nsa_fused_kernel.py:549-554); the learned pooling
  * replaces BlockCompressor.forward (nsa_model.py:118-123) as called at nsa_model.py:336-337:

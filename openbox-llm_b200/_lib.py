@@ -44,6 +44,8 @@ SIGNATURES = {
     "nsa_selection_bwd": (_i, [_vp] * 10 + [_dp, _i, _i, _vp, _sz, _i, _vp]),
     "nsa_csr_workspace_bytes": (_sz, [_i] * 5),
     "nsa_build_block_to_query_csr": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "nsa_csr_builtin_scratch_bytes": (_sz, []),
+    "nsa_build_block_to_query_csr_noalloc": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "nsa_block_mean_pool_fwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_block_mean_pool_bwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_block_compress_fwd": (_i, [_vp] * 5 + [_i] * 6 + [_vp]),

@@ -621,6 +621,41 @@ extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int
                             (cudaStream_t)stream);
 }
 
+// ---- CSR without caller-provided scratch -----------------------------------------------------
+// The scratch of the CSR build (bitmap, counts, row starts) lives in this fixed device array.
+// In host code the array's name is only a handle: the device address is looked up once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+constexpr size_t kCsrBuiltinScratchBytes = (size_t)8 << 20;
+static __device__ __align__(256) unsigned char g_csr_builtin_scratch[kCsrBuiltinScratchBytes];
+
+extern "C" size_t nsa_csr_builtin_scratch_bytes(void) { return kCsrBuiltinScratchBytes; }
+
+extern "C" int nsa_build_block_to_query_csr_noalloc(const int32_t* block_idx, int B, int Hkv, int T,
+                                                    int S, int block_size, int32_t* q_of_block,
+                                                    int32_t* block_offsets, int32_t* pair_bh,
+                                                    void* stream) {
+  NSA_CHECK_ARG(block_size > 0 && B >= 0 && Hkv >= 0 && T >= 0 && S >= 0, "bad sizes");
+  const size_t need = nsa_csr_workspace_bytes(B, Hkv, T, S, block_size);
+  if (need > kCsrBuiltinScratchBytes) {
+    set_error("this CSR needs %zu bytes of scratch but the built-in scratch holds %zu: use "
+              "nsa_build_block_to_query_csr with a caller-provided workspace", need,
+              kCsrBuiltinScratchBytes);
+    return NSA_ERR_WORKSPACE;
+  }
+  static void* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  NSA_CUDA_OK(cudaGetDevice(&dev));
+  NSA_CHECK_ARG(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+  if (scratch_of_device[dev] == nullptr) {   // first call on this device, with it current
+    void* ptr = nullptr;
+    NSA_CUDA_OK(cudaGetSymbolAddress(&ptr, g_csr_builtin_scratch));
+    scratch_of_device[dev] = ptr;
+  }
+  return build_csr_internal(block_idx, B, Hkv, T, S, block_size, T / block_size, q_of_block,
+                            block_offsets, pair_bh, nullptr, scratch_of_device[dev],
+                            kCsrBuiltinScratchBytes, (cudaStream_t)stream);
+}
+
 extern "C" int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const void* o_win,
                                     const void* gate_logits, void* out, const NsaDims* dims,
                                     void* stream) {
