@@ -331,6 +331,12 @@ def main():
         flop_tab["tc_bwd_dkdv_" + br] = 8 * D * pairs[br]    # S, dP, dV, dK
         flop_tab["simt_fwd_" + br] = 4 * D * pairs[br]
         flop_tab["simt_bwd_" + br] = 10 * D * pairs[br]
+    # DRAM bytes per launch from the one-pass ncu capture of this workload
+    # (profiles/dram_traffic_pair_kernels_c4_t32k.md); other workloads: not captured
+    traffic_tab = {"tc_bwd_slc": 33.47e9, "tc_bwd_win": 14.06e9, "tc_bwd_cmp": 15.03e9,
+                   "tc_fwd_slc_pairs": 24.10e9, "sel_combine_kernel": 18.81e9,
+                   "dq_reduce_slc": 18.00e9, "dq_reduce_win": 10.63e9, "dq_reduce_cmp": 5.88e9} \
+        if args.workload == "c4_t32k" else {}
     total_ms = sum(v[1] for v in prof.values()) or 1.0
     top = max(prof.items(), key=lambda kv: kv[1][1]) if prof else (None, (0, 0.0))
     roof = None
@@ -340,13 +346,20 @@ def main():
         if name in flop_tab:
             achieved = flop_tab[name] / (per_launch_ms * 1e-3) / 1e12
             roof = {"kernel": name, "bound": "tensor", "achieved": achieved, "peak": pk["tflops"],
-                    "unit": "TFLOP/s", "frac": achieved / pk["tflops"], "traffic": None,
+                    "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                    "traffic": traffic_tab.get(name),
                     "peak_source": pk["source"] + " (sustained bf16 GEMM)",
                     "launch_ms": per_launch_ms, "share_of_kernel_time": tms / total_ms}
+            if name in traffic_tab:
+                gbs = traffic_tab[name] / (per_launch_ms * 1e-3) / 1e9
+                roof["dram_gbs"] = gbs
+                roof["dram_frac_of_measured_hbm"] = gbs / pk["hbm"]
         else:
-            roof = {"kernel": name, "bound": "hbm", "achieved": None, "peak": pk["hbm"], "unit": "GB/s",
-                    "frac": None, "traffic": None, "launch_ms": per_launch_ms,
-                    "share_of_kernel_time": tms / total_ms}
+            tr = traffic_tab.get(name)
+            ach = tr / (per_launch_ms * 1e-3) / 1e9 if tr else None
+            roof = {"kernel": name, "bound": "hbm", "achieved": ach, "peak": pk["hbm"], "unit": "GB/s",
+                    "frac": ach / pk["hbm"] if ach else None, "traffic": tr,
+                    "launch_ms": per_launch_ms, "share_of_kernel_time": tms / total_ms}
     total_flops = 14 * D * sum(pairs.values())
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,

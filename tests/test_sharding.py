@@ -1,0 +1,74 @@
+"""Multi-GPU path on CPU: two gloo ranks each take their (batch, kv-head) units, run the op
+(here: the oracle, there is no GPU) on their slice only, and the merged result equals the
+unsharded one.  No data-path collective is involved; all_gather is only the test's way of
+collecting the parts."""
+import importlib
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import nsa_oracle as O
+
+S = importlib.import_module("openbox-llm_b200.shard")
+
+
+def test_unit_ranges_cover_everything_once():
+    for n in (1, 3, 4, 16, 17):
+        for world in (1, 2, 3, 4, 8):
+            seen = []
+            for r in range(world):
+                a, b = S.unit_range(n, world, r)
+                assert 0 <= a <= b <= n and b - a in (n // world, n // world + 1)
+                seen += list(range(a, b))
+            assert seen == list(range(n))
+
+
+def _inputs():
+    g = torch.Generator().manual_seed(0)
+    B, Hq, Hkv, T, D = 2, 4, 2, 96, 16
+    mk = lambda h: torch.randn(B, h, T, D, generator=g)
+    t = {"q": mk(Hq)}
+    for n in ("kc", "vc", "ks", "vs", "kw", "vw"):
+        t[n] = mk(Hkv)
+    t["gate"] = torch.randn(B, Hq, T, 3, generator=g)
+    return t, (B, Hq, Hkv, T, D)
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    t, (B, Hq, Hkv, T, D) = _inputs()
+    a, b = S.unit_range(B * Hkv, world, rank)
+    loc = {n: S.slice_units(x, Hkv, a, b) for n, x in t.items()}      # [units, G or 1, T, *]
+    res = O.stream_nsa_forward(loc["q"], loc["kc"], loc["vc"], loc["ks"], loc["vs"], loc["kw"],
+                               loc["vw"], loc["gate"], 16, 3, 24)
+    parts = [None] * world
+    dist.all_gather_object(parts, res["out"])
+    idx_parts = [None] * world
+    dist.all_gather_object(idx_parts, res["block_idx"])
+    if rank == 0:
+        out.put((S.merge_units(parts, B, Hkv), torch.cat(idx_parts, 0).reshape(B, Hkv, T, 3)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_reproduce_the_unsharded_op():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    merged, idx = out.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    t, (B, Hq, Hkv, T, D) = _inputs()
+    full = O.stream_nsa_forward(t["q"], t["kc"], t["vc"], t["ks"], t["vs"], t["kw"], t["vw"],
+                                t["gate"], 16, 3, 24)
+    assert torch.equal(idx, full["block_idx"])
+    assert (merged - full["out"]).abs().max().item() <= 1e-6
