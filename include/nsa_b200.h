@@ -156,6 +156,10 @@ int nsa_gate_combine_bwd(const void* o_cmp, const void* o_slc, const void* o_win
                          const void* gate_logits, const void* d_out, void* do_cmp, void* do_slc,
                          void* do_win, void* d_gate_logits, const NsaDims* dims, void* stream);
 
+/* out = a + b + c over n elements (fp32 accumulation): the sum of the three branches' dq that
+ * autograd forms when one q feeds three branch Functions (nsa_model.py:330,338,360). */
+int nsa_sum3(const void* a, const void* b, const void* c, void* out, size_t n, int dtype, void* stream);
+
 /* ---- accounting ------------------------------------------------------------------------------
  * nsa_launch_count: kernels launched by this library in this process so far.
  * nsa_profile_enable(1) makes every later kernel launch be bracketed by CUDA events on its own

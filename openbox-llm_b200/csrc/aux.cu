@@ -398,6 +398,30 @@ __global__ void gate_bwd_kernel(const T* __restrict__ oc, const T* __restrict__ 
   }
 }
 
+// out = a + b + c, fp32 accumulation, 8 elements per thread (bf16) or 4 (fp32)
+__global__ void sum3_bf16_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
+                                 const uint4* __restrict__ c, uint4* __restrict__ out, size_t n8) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 x = __ldg(a + i), y = __ldg(b + i), z = __ldg(c + i);
+  const __nv_bfloat162* xs = reinterpret_cast<const __nv_bfloat162*>(&x);
+  const __nv_bfloat162* ys = reinterpret_cast<const __nv_bfloat162*>(&y);
+  const __nv_bfloat162* zs = reinterpret_cast<const __nv_bfloat162*>(&z);
+  uint4 r;
+  __nv_bfloat162* rs = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 fx = __bfloat1622float2(xs[e]), fy = __bfloat1622float2(ys[e]), fz = __bfloat1622float2(zs[e]);
+    rs[e] = __floats2bfloat162_rn(fx.x + fy.x + fz.x, fx.y + fy.y + fz.y);
+  }
+  out[i] = r;
+}
+__global__ void sum3_f32_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                const float* __restrict__ c, float* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = a[i] + b[i] + c[i];
+}
+
 inline unsigned blocks_for(size_t n, int per) { return (unsigned)((n + per - 1) / per); }
 
 }  // namespace
@@ -654,6 +678,23 @@ extern "C" int nsa_build_block_to_query_csr_noalloc(const int32_t* block_idx, in
   return build_csr_internal(block_idx, B, Hkv, T, S, block_size, T / block_size, q_of_block,
                             block_offsets, pair_bh, nullptr, scratch_of_device[dev],
                             kCsrBuiltinScratchBytes, (cudaStream_t)stream);
+}
+
+extern "C" int nsa_sum3(const void* a, const void* b, const void* c, void* out, size_t n, int dtype,
+                        void* stream) {
+  if (n == 0) return NSA_OK;
+  NSA_CHECK_ARG(a && b && c && out, "null tensor");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == NSA_DTYPE_BF16) {
+    NSA_CHECK_ARG(n % 8 == 0, "element count must be a multiple of 8");
+    KernelScope ks("sum3_kernel", st);
+    sum3_bf16_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>((const uint4*)a, (const uint4*)b, (const uint4*)c, (uint4*)out, n / 8);
+  } else {
+    KernelScope ks("sum3_kernel", st);
+    sum3_f32_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const float*)a, (const float*)b, (const float*)c, (float*)out, n);
+  }
+  NSA_LAUNCH_OK("sum3_kernel");
+  return NSA_OK;
 }
 
 extern "C" int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const void* o_win,

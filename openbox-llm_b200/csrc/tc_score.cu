@@ -21,11 +21,25 @@ struct ScoreArgs {
   int* status;
   int B, Hq, Hkv, T, n_blk, G, Gp, nq, block_size, n_sel, n_qtiles;
   float scale_log2;
+#ifdef NSA_TRACE
+  long long* trace;
+#endif
 };
+
+#ifdef NSA_TRACE
+extern "C" long long* nsa_trace_buffer();
+#define SC_STAMP(k)                                                                         \
+  do {                                                                                      \
+    if (p.trace && blockIdx.x == 100 && blockIdx.y == 0 && tid == 33 && i < 8)               \
+      p.trace[i * 12 + (k)] = clock64();                                                    \
+  } while (0)
+#else
+#define SC_STAMP(k) do {} while (0)
+#endif
 
 __host__ __device__ inline size_t score_smem_bytes(int D, int nq) {
   return (size_t)(kRows * 128 + 2 * kKeys * 128) * (D / 64) + (size_t)kRows * kKeys * 4 +
-         (size_t)nq * kKeys * 4 + 256 + 1024;
+         (size_t)nq * kKeys * 4 + 256 + 4 * 32 * 8 + 1024;
 }
 
 template <int D>
@@ -49,6 +63,8 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_s = bars + 3;
   uint32_t* s_tmem = (uint32_t*)(bars + 4);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
+  float* s_top_v = (float*)(bars + 6);               // [4 warps][32] merge scratch
+  int* s_top_i = (int*)(s_top_v + 4 * 32);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qtile = p.n_qtiles - 1 - (int)blockIdx.x;
@@ -74,13 +90,19 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int hi_last = min(p.n_blk, (t_last + 1) / p.block_size) - 1;
   const int n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
 
-  // running top-n of the queries this warp owns: query slot s -> ql = warp + 4 s; lane k = rank k
-  constexpr int kMaxOwn = 32;                       // nq <= 128 -> at most 32 queries per warp
-  float top_v[kMaxOwn];
-  int top_i[kMaxOwn];
+  // Running top-16 lists: the 128 threads are dealt out Lq = 128 / nq per query; each keeps, in
+  // registers, the best 16 of the candidates it has scanned (64 / Lq per tile), ordered by
+  // (importance descending, block index ascending).  The Lq lists of a query are merged at the
+  // end by a 16-round tournament over their heads.
+  constexpr int kList = 16;
+  const int Lq = kRows / p.nq;
+  const int my_q = tid / Lq, my_sub = tid % Lq;
+  const int per_lane = kKeys / Lq;
+  const int my_t = t0 + my_q;
+  float lv[kList];
+  int li[kList];
 #pragma unroll
-  for (int s = 0; s < kMaxOwn; ++s) { top_v[s] = -1.f; top_i[s] = -1; }
-  const int n_own = (p.nq - warp + 3) / 4;
+  for (int k = 0; k < kList; ++k) { lv[k] = -1.f; li[k] = -1; }
 
   uint32_t tmem = 0;
   if (n_tiles > 0) {
@@ -127,7 +149,9 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     for (int i = 0; i < n_tiles; ++i) {
       const int key0 = i * kKeys;
+      SC_STAMP(0);
       mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
+      SC_STAMP(1);
       tc_fence_after();
       if (tid == 0 && i + 2 < n_tiles) load_k(i + 2);
       __syncwarp();
@@ -148,81 +172,86 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // 16-byte chunk index XOR row: a warp's stores spread over the banks
         dst[c4 ^ (tid & 15)] = v;
       }
+      SC_STAMP(2);
       __syncthreads();                         // all of S is read, all of P is in shared memory
+      SC_STAMP(3);
       if (tid == 0 && i + 1 < n_tiles) {
         tc_fence_after();
         mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
         issue_s(i + 1);
       }
-      // group sums: importance[ql][c] = sum over heads, ascending
-      for (int e = tid; e < p.nq * kKeys; e += 128) {
-        const int qq = e / kKeys, c = e % kKeys;
-        float s = 0.f;
+      // group sums: importance[ql][c] = sum over heads, ascending; four columns per thread
+      for (int e = tid; e < p.nq * (kKeys / 4); e += 128) {
+        const int qq = e / (kKeys / 4), c4 = e % (kKeys / 4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int gg = 0; gg < p.G; ++gg) {
           const int row = gg * p.nq + qq;
-          s += sP[row * kKeys + ((((c >> 2) ^ (row & 15))) << 2) + (c & 3)];
+          const float4 v = *reinterpret_cast<const float4*>(sP + row * kKeys + ((c4 ^ (row & 15)) << 2));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        sImp[e] = s;
-      }
-      __syncthreads();
-      // top-n update, one warp per query
-#pragma unroll 1
-      for (int s = 0; s < n_own; ++s) {
-        const int qq = warp + 4 * s;
-        const int tq = t0 + qq;
-        if (tq >= p.T) break;
-        const int hq = min(kKeys - 1, min(p.n_blk, (tq + 1) / p.block_size) - 1 - key0);
-        float* out = p.imp_out ? p.imp_out + ((size_t)bh * p.T + tq) * p.n_blk + key0 : nullptr;
-        float tv = top_v[s];
-        int ti = top_i[s];
+        *reinterpret_cast<float4*>(sImp + qq * kKeys + c4 * 4) = acc;
+        if (p.imp_out && t0 + qq < p.T) {
+          const int hq = min(p.n_blk, (t0 + qq + 1) / p.block_size) - 1 - key0;   // last valid column
+          float* out = p.imp_out + ((size_t)bh * p.T + t0 + qq) * p.n_blk + key0 + c4 * 4;
+          const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int c = half * 32 + lane;
-          const float v = sImp[qq * kKeys + c];
-          if (out && key0 + c < p.n_blk) out[c] = c <= hq ? v : 0.f;
-          // the list is full once rank n_sel-1 holds a block; its value is the bar to beat
-          const float thr = __shfl_sync(0xffffffffu, tv, p.n_sel - 1);
-          const int thr_i = __shfl_sync(0xffffffffu, ti, p.n_sel - 1);
-          const bool beat = (c <= hq) && (thr_i < 0 || v > thr);
-          uint32_t todo = __ballot_sync(0xffffffffu, beat);
-          while (todo) {
-            const int src = __ffs(todo) - 1;
-            todo &= todo - 1;
-            const float cv = __shfl_sync(0xffffffffu, v, src);
-            const int cj = key0 + half * 32 + src;
-            // entries that stay ahead: larger value, or equal value (their index is smaller);
-            // empty slots (index -1) are behind everything
-            const bool ahead = (ti >= 0) && (tv >= cv);
-            const int pos = __popc(__ballot_sync(0xffffffffu, ahead));
-            if (pos < p.n_sel) {
-              const float pv = __shfl_up_sync(0xffffffffu, tv, 1);
-              const int pi = __shfl_up_sync(0xffffffffu, ti, 1);
-              if (lane > pos) { tv = pv; ti = pi; }
-              if (lane == pos) { tv = cv; ti = cj; }
+          for (int e = 0; e < 4; ++e)
+            if (key0 + c4 * 4 + e < p.n_blk) out[e] = (c4 * 4 + e <= hq) ? vals[e] : 0.f;
+        }
+      }
+      SC_STAMP(4);
+      __syncthreads();
+      SC_STAMP(5);
+      // top-16 update: this thread scans its share of the query's 64 candidates
+      {
+        const int hq = my_t < p.T ? min(kKeys - 1, min(p.n_blk, (my_t + 1) / p.block_size) - 1 - key0) : -1;
+        for (int k = 0; k < per_lane; ++k) {
+          const int c = my_sub * per_lane + k;
+          if (c > hq) break;
+          const float cv = sImp[my_q * kKeys + c];
+          if (cv > lv[kList - 1]) {          // beats the list's last entry (empty slots hold -1)
+            const int cj = key0 + c;
+#pragma unroll
+            for (int r = kList - 1; r >= 1; --r) {   // strict '>' keeps earlier (lower) indices ahead
+              const bool up = cv > lv[r - 1];
+              const bool here = cv > lv[r];
+              li[r] = up ? li[r - 1] : (here ? cj : li[r]);
+              lv[r] = up ? lv[r - 1] : (here ? cv : lv[r]);
             }
+            if (cv > lv[0]) { lv[0] = cv; li[0] = cj; }
           }
         }
-        top_v[s] = tv;
-        top_i[s] = ti;
       }
+      SC_STAMP(6);
       __syncthreads();                         // sP / sImp are rewritten by the next tile
+      SC_STAMP(7);
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, kTmemCols);
   }
 
-  // ---- write the lists; zero the importance columns no tile covered -------------------------
-#pragma unroll 1
-  for (int s = 0; s < n_own; ++s) {
-    const int qq = warp + 4 * s;
-    const int tq = t0 + qq;
-    if (tq >= p.T) break;
-    if (lane < p.n_sel) p.block_idx[((size_t)bh * p.T + tq) * p.n_sel + lane] = top_i[s];
-    if (p.imp_out) {
-      float* out = p.imp_out + ((size_t)bh * p.T + tq) * p.n_blk;
-      for (int c = n_tiles * kKeys + lane; c < p.n_blk; c += 32) out[c] = 0.f;
+  // ---- merge the Lq lists of each query: n_sel rounds, each takes the best head ------------------
+  for (int r = 0; r < p.n_sel; ++r) {
+    float bv = lv[0];
+    int bj = li[0];
+    for (int o = 1; o < Lq; o <<= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
+      if (ov > bv || (ov == bv && oj >= 0 && (bj < 0 || oj < bj))) { bv = ov; bj = oj; }
     }
+    if (bj >= 0 && li[0] == bj) {            // this list gave the winner: pop its head
+#pragma unroll
+      for (int k = 0; k < kList - 1; ++k) { lv[k] = lv[k + 1]; li[k] = li[k + 1]; }
+      lv[kList - 1] = -1.f;
+      li[kList - 1] = -1;
+    }
+    if (my_sub == 0 && my_t < p.T) p.block_idx[((size_t)bh * p.T + my_t) * p.n_sel + r] = bj;
+  }
+  // importance columns no tile covered are zero
+  if (p.imp_out && my_t < p.T) {
+    float* out = p.imp_out + ((size_t)bh * p.T + my_t) * p.n_blk;
+    for (int c = n_tiles * kKeys + my_sub; c < p.n_blk; c += Lq) out[c] = 0.f;
   }
 }
 
@@ -230,9 +259,9 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel) {
   if (d.dtype != NSA_DTYPE_BF16 || (d.D != 64 && d.D != 128)) return false;
-  if (n_sel < 1 || n_sel > 32 || n_blk < 1) return false;
+  if (n_sel < 1 || n_sel > 16 || n_blk < 1) return false;
   const int G = d.Hq / d.Hkv;
-  return G <= 128;
+  return G <= 32;   // at least 4 queries per tile, so the lanes of one query sit in one warp
 }
 
 int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_idx, float* imp_out,
@@ -247,6 +276,9 @@ int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_i
   p.block_size = block_size; p.n_sel = n_sel;
   p.n_qtiles = (d.T + p.nq - 1) / p.nq;
   p.scale_log2 = kLog2e / sqrtf((float)d.D);
+#ifdef NSA_TRACE
+  p.trace = nsa_trace_buffer();
+#endif
   CUtensorMap tm_q, tm_k;
   int rc = make_map(&tm_q, q, d.D, d.T, d.B * d.Hq, p.nq, p.Gp);
   if (rc == NSA_OK) rc = make_map(&tm_k, k_cmp, d.D, n_blk, d.B * d.Hkv, kKeys, 1);

@@ -391,7 +391,10 @@ class _NSAAttention(torch.autograd.Function):
                                                  MODE_COMPRESS, 0, block_size)
         dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, do_slc, o_slc, lse_slc)
         dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, do_win, MODE_WINDOW, window, 0)
-        dq = dq.float().add_(dq2).add_(dq3).to(q.dtype) if q.dtype != torch.float32 else dq.add_(dq2).add_(dq3)
+        dq_sum = torch.empty_like(dq)
+        L.check(L.lib().nsa_sum3(L.ptr(dq), L.ptr(dq2), L.ptr(dq3), L.ptr(dq_sum), dq.numel(),
+                                 L.dtype_code(dq), L.stream()))
+        dq = dq_sum
         pgrads = [None] * 6
         if learned:
             dkc, a, b, c = _compress_bwd(kc, cp[0], cp[1], cp[2], dk_cmp, block_size)
