@@ -62,6 +62,10 @@ int nsa_tc_supported(const NsaDims* dims, int block_size);
  * mode WINDOW: query t attends keys [max(0,t-window+1), t]; Lk = T.
  * mode COMPRESS: query t attends summaries j with (j+1)*block_size-1 <= t; Lk = n_blk.
  * The forward also writes lse (the reference recomputes it in backward). */
+/* Backward of a gated branch: when row_scale / row_dot [B,Hq,T] float32 are given (both or
+ * neither), d_o is the upstream gradient of the whole op, the branch's own gradient is
+ * row_scale * d_o and its delta is row_scale * row_dot, row_dot = sum_d d_o * o_branch; o is then
+ * not read.  nsa_gate_combine_bwd_rows produces both arrays for the three branches. */
 int nsa_range_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                        const NsaDims* dims, int Lk, int mode, int window, int block_size,
                        int impl, void* stream);
@@ -69,6 +73,7 @@ size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int mode,
 int nsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
                        const void* d_o, void* dq, void* dk, void* dv,
                        const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                       const float* row_scale, const float* row_dot,
                        void* workspace, size_t workspace_bytes, int impl, void* stream);
 
 /* ---- selected-block attention --------------------------------------------------------------
@@ -85,6 +90,7 @@ size_t nsa_selection_bwd_workspace_bytes(const NsaDims* dims, int S, int block_s
 int nsa_selection_bwd(const void* q, const void* k, const void* v, const int32_t* block_idx,
                       const void* o, const float* lse, const void* d_o,
                       void* dq, void* dk, void* dv, const NsaDims* dims, int S, int block_size,
+                      const float* row_scale, const float* row_dot,
                       void* workspace, size_t workspace_bytes, int impl, void* stream);
 
 /* ---- block -> query CSR ---------------------------------------------------------------------
@@ -155,6 +161,12 @@ int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const void* o_win
 int nsa_gate_combine_bwd(const void* o_cmp, const void* o_slc, const void* o_win,
                          const void* gate_logits, const void* d_out, void* do_cmp, void* do_slc,
                          void* do_win, void* d_gate_logits, const NsaDims* dims, void* stream);
+
+/* Row statistics of the gate backward for the fused op: row_scale[3][B*Hq*T] = sigmoid(gate) and
+ * row_dot[3][B*Hq*T] = <d_out, o_branch> (branch order cmp, slc, win), and d_gate_logits. */
+int nsa_gate_combine_bwd_rows(const void* o_cmp, const void* o_slc, const void* o_win,
+                              const void* gate_logits, const void* d_out, float* row_scale,
+                              float* row_dot, void* d_gate_logits, const NsaDims* dims, void* stream);
 
 /* out = a + b + c over n elements (fp32 accumulation): the sum of the three branches' dq that
  * autograd forms when one q feeds three branch Functions (nsa_model.py:330,338,360). */

@@ -37,11 +37,11 @@ SIGNATURES = {
     "nsa_profile_summary": (_i, [ctypes.c_char_p, _sz]),
     "nsa_range_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _dp, _i, _i, _i, _i, _i, _vp]),
     "nsa_range_attn_bwd_workspace_bytes": (_sz, [_dp, _i, _i, _i, _i]),
-    "nsa_range_attn_bwd": (_i, [_vp] * 9 + [_dp, _i, _i, _i, _i, _vp, _sz, _i, _vp]),
+    "nsa_range_attn_bwd": (_i, [_vp] * 9 + [_dp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _i, _vp]),
     "nsa_selection_fwd_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
     "nsa_selection_fwd": (_i, [_vp] * 6 + [_dp, _i, _i, _vp, _sz, _i, _vp]),
     "nsa_selection_bwd_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
-    "nsa_selection_bwd": (_i, [_vp] * 10 + [_dp, _i, _i, _vp, _sz, _i, _vp]),
+    "nsa_selection_bwd": (_i, [_vp] * 10 + [_dp, _i, _i, _vp, _vp, _vp, _sz, _i, _vp]),
     "nsa_csr_workspace_bytes": (_sz, [_i] * 5),
     "nsa_build_block_to_query_csr": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "nsa_csr_builtin_scratch_bytes": (_sz, []),
@@ -52,6 +52,7 @@ SIGNATURES = {
     "nsa_block_compress_bwd_workspace_bytes": (_sz, [_i] * 5),
     "nsa_block_compress_bwd": (_i, [_vp] * 9 + [_i] * 6 + [_vp, _sz, _vp]),
     "nsa_topn_blocks": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _i, _vp]),
+    "nsa_gate_combine_bwd_rows": (_i, [_vp] * 8 + [_dp, _vp]),
     "nsa_sum3": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "nsa_gate_combine_fwd": (_i, [_vp] * 5 + [_dp, _vp]),
     "nsa_gate_combine_bwd": (_i, [_vp] * 9 + [_dp, _vp]),

@@ -231,6 +231,7 @@ extern "C" size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk
 extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o,
                                   const float* lse, const void* d_o, void* dq, void* dk, void* dv,
                                   const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                                  const float* row_scale, const float* row_dot,
                                   void* workspace, size_t workspace_bytes, int impl, void* stream) {
   int rc = check_dims(dims);
   if (rc != NSA_OK) return rc;
@@ -252,6 +253,8 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
   AttnArgs a = base_args(dims, Lk);
   a.q = q; a.k = k; a.v = v; a.o = (void*)o; a.lse = (float*)lse; a.d_o = d_o; a.dq = dq;
   a.kind = mode; a.window = window; a.block_size = block_size;
+  a.row_scale = row_scale; a.row_dot = row_dot;
+  NSA_CHECK_ARG((row_scale == nullptr) == (row_dot == nullptr), "row_scale and row_dot go together");
   if (use_tc(dims, 64, impl, &rc)) {
     a.dk_acc = (float*)dk;   // tc path writes dk/dv itself; pass the outputs through
     a.dv_acc = (float*)dv;
@@ -314,8 +317,8 @@ extern "C" size_t nsa_selection_bwd_workspace_bytes(const NsaDims* dims, int S, 
 extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
                                  const int32_t* block_idx, const void* o, const float* lse,
                                  const void* d_o, void* dq, void* dk, void* dv, const NsaDims* dims,
-                                 int S, int block_size, void* workspace, size_t workspace_bytes,
-                                 int impl, void* stream) {
+                                 int S, int block_size, const float* row_scale, const float* row_dot,
+                                 void* workspace, size_t workspace_bytes, int impl, void* stream) {
   int rc = check_sel(dims, S, block_size);
   if (rc != NSA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
@@ -326,6 +329,8 @@ extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
   AttnArgs a = base_args(dims, dims->T);
   a.q = q; a.k = k; a.v = v; a.o = (void*)o; a.lse = (float*)lse; a.d_o = d_o; a.dq = dq;
   a.block_idx = block_idx; a.kind = 2; a.S = S; a.block_size = block_size;
+  a.row_scale = row_scale; a.row_dot = row_dot;
+  NSA_CHECK_ARG((row_scale == nullptr) == (row_dot == nullptr), "row_scale and row_dot go together");
   if (use_tc(dims, block_size, impl, &rc) && S > 0) {
     a.dk_acc = (float*)dk;
     a.dv_acc = (float*)dv;

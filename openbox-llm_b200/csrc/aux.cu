@@ -422,6 +422,37 @@ __global__ void sum3_f32_kernel(const float* __restrict__ a, const float* __rest
   if (i < n) out[i] = a[i] + b[i] + c[i];
 }
 
+// per row: gate values, <dO, o_branch> and d_gate; the branch backward kernels then work from the
+// op's upstream gradient directly
+template <typename T>
+__global__ void gate_bwd_rows_kernel(const T* __restrict__ oc, const T* __restrict__ os,
+                                     const T* __restrict__ ow, const T* __restrict__ gate,
+                                     const T* __restrict__ d_out, float* __restrict__ row_scale,
+                                     float* __restrict__ row_dot, T* __restrict__ d_gate, size_t rows, int D) {
+  const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const size_t i = row * D + d;
+    const float g = to_float(d_out[i]);
+    a0 = fmaf(g, to_float(oc[i]), a0);
+    a1 = fmaf(g, to_float(os[i]), a1);
+    a2 = fmaf(g, to_float(ow[i]), a2);
+  }
+  a0 = warp_sum(a0); a1 = warp_sum(a1); a2 = warp_sum(a2);
+  if (lane == 0) {
+    const float g0 = sigmoidf_(to_float(gate[row * 3 + 0]));
+    const float g1 = sigmoidf_(to_float(gate[row * 3 + 1]));
+    const float g2 = sigmoidf_(to_float(gate[row * 3 + 2]));
+    row_scale[row] = g0; row_scale[rows + row] = g1; row_scale[2 * rows + row] = g2;
+    row_dot[row] = a0; row_dot[rows + row] = a1; row_dot[2 * rows + row] = a2;
+    d_gate[row * 3 + 0] = from_float<T>(a0 * g0 * (1.f - g0));
+    d_gate[row * 3 + 1] = from_float<T>(a1 * g1 * (1.f - g1));
+    d_gate[row * 3 + 2] = from_float<T>(a2 * g2 * (1.f - g2));
+  }
+}
+
 inline unsigned blocks_for(size_t n, int per) { return (unsigned)((n + per - 1) / per); }
 
 }  // namespace
@@ -678,6 +709,23 @@ extern "C" int nsa_build_block_to_query_csr_noalloc(const int32_t* block_idx, in
   return build_csr_internal(block_idx, B, Hkv, T, S, block_size, T / block_size, q_of_block,
                             block_offsets, pair_bh, nullptr, scratch_of_device[dev],
                             kCsrBuiltinScratchBytes, (cudaStream_t)stream);
+}
+
+extern "C" int nsa_gate_combine_bwd_rows(const void* o_cmp, const void* o_slc, const void* o_win,
+                                         const void* gate_logits, const void* d_out, float* row_scale,
+                                         float* row_dot, void* d_gate_logits, const NsaDims* dims,
+                                         void* stream) {
+  NSA_CHECK_ARG(dims && row_scale && row_dot && d_gate_logits, "null argument");
+  const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
+  if (rows == 0) return NSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  KernelScope ks("gate_bwd_rows_kernel", st);
+  if (dims->dtype == NSA_DTYPE_BF16)
+    gate_bwd_rows_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (const __nv_bfloat16*)d_out, row_scale, row_dot, (__nv_bfloat16*)d_gate_logits, rows, dims->D);
+  else
+    gate_bwd_rows_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (const float*)d_out, row_scale, row_dot, (float*)d_gate_logits, rows, dims->D);
+  NSA_LAUNCH_OK("gate_bwd_rows_kernel");
+  return NSA_OK;
 }
 
 extern "C" int nsa_sum3(const void* a, const void* b, const void* c, void* out, size_t n, int dtype,

@@ -85,6 +85,7 @@ struct AttnArgs {
   const void* q; const void* k; const void* v; const int32_t* block_idx;
   void* o; float* lse;
   const void* d_o; void* dq; float* dk_acc; float* dv_acc;   // backward
+  const float* row_scale; const float* row_dot;   // backward of a gated branch (may be null)
   int B, Hq, Hkv, T, Lk, D, S;
   int kind;          // 0 window, 1 compress, 2 selection
   int window, block_size;

@@ -159,14 +159,17 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_kernel(AttnArgs a) {
   const T* qrow = reinterpret_cast<const T*>(a.q) + row * D;
   const T* dorow = reinterpret_cast<const T*>(a.d_o) + row * D;
   const T* orow = reinterpret_cast<const T*>(a.o) + row * D;
+  // a gated branch receives the op's upstream gradient and its own gate value per row:
+  // dO_branch = row_scale * dO and delta = row_scale * row_dot (row_dot = sum_d dO * O_branch)
+  const float rs = a.row_scale ? a.row_scale[row] : 1.f;
   float dpart = 0.f;
   for (int d = lane; d < D; d += 32) {
     qs[warp][d] = to_float(qrow[d]) * a.scale;
-    const float g = to_float(dorow[d]);
+    const float g = to_float(dorow[d]) * rs;
     dos[warp][d] = g;
-    dpart = fmaf(g, to_float(orow[d]), dpart);
+    if (!a.row_dot) dpart = fmaf(g, to_float(orow[d]), dpart);
   }
-  const float delta = warp_sum(dpart);
+  const float delta = a.row_dot ? rs * a.row_dot[row] : warp_sum(dpart);
   const float lse = a.lse[row];
   __syncwarp();
   const size_t kvoff = (size_t)(b * a.Hkv + hkv) * a.Lk * D;

@@ -28,7 +28,8 @@ struct BwdArgs {
   const __nv_bfloat16* q;
   const __nv_bfloat16* d_o;
   const float* lse;
-  const float* delta;
+  const float* delta;          // sum_d dO * O per row (unscaled)
+  const float* row_scale;      // gate value per row of a gated branch, or null
   const int32_t* q_of_block;
   const int32_t* offsets;      // [B*Hkv, n_ktiles + 1] global pair offsets (selection)
   __nv_bfloat16* dk;
@@ -276,10 +277,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   int i = rt_begin + grp;
   int t_cur = i < rt_end ? row_query(i) : -1;
   int t_nxt = i + 2 < rt_end ? row_query(i + 2) : -1;
-  float lse_cur = 0.f, delta_cur = 0.f;
+  float lse_cur = 0.f, delta_cur = 0.f, gate_cur = 1.f;
   if (t_cur >= 0) {
     lse_cur = __ldg(p.lse + row_index(t_cur));
     delta_cur = __ldg(p.delta + row_index(t_cur));
+    if (p.row_scale) gate_cur = __ldg(p.row_scale + row_index(t_cur));
   }
   int buf = 0;
   if (i < rt_end) {
@@ -293,10 +295,11 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   for (; i < rt_end; i += 2, phase ^= 1, ++it_no, buf ^= 1) {
     NSA_STAMP(0);
     const int t_nn = (i + 4 < rt_end) ? row_query(i + 4) : -1;
-    float lse_nxt = 0.f, delta_nxt = 0.f;
+    float lse_nxt = 0.f, delta_nxt = 0.f, gate_nxt = 1.f;
     if (t_nxt >= 0) {
       lse_nxt = ldg_f32_now(p.lse + row_index(t_nxt));
       delta_nxt = ldg_f32_now(p.delta + row_index(t_nxt));
+      if (p.row_scale) gate_nxt = ldg_f32_now(p.row_scale + row_index(t_nxt));
     }
     // query positions of this group's next tile, for the gather issued further down
     if (g == 0 && half == 0 && row_slot_ok) s_rowt[(buf ^ 1) * kMaxNq + ql] = t_nxt;
@@ -352,7 +355,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int e = 0; e < 2; ++e) {
           const int c = half * 32 + c2 * 2 + e;
           const bool ok = (c >= lo) && (c <= hi);
-          const float pr = ok ? ex2(__uint_as_float(rs[c2 * 2 + e]) * p.scale_log2 - lse2_cur) : 0.f;
+          // gate_cur * p: the branch's dO is gate * dO, so dV takes (gate p)^T dO and
+          // dS = scale * gate * p * (dO.v - dO.o)
+          const float pr = ok ? gate_cur * ex2(__uint_as_float(rs[c2 * 2 + e]) * p.scale_log2 - lse2_cur) : 0.f;
           pv[e] = pr;
           dv[e] = pr * (__uint_as_float(rp[c2 * 2 + e]) - delta_cur) * p.scale;
         }
@@ -460,7 +465,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
     }
     NSA_STAMP(7);
-    t_cur = t_nxt; t_nxt = t_nn; lse_cur = lse_nxt; delta_cur = delta_nxt;
+    t_cur = t_nxt; t_nxt = t_nn; lse_cur = lse_nxt; delta_cur = delta_nxt; gate_cur = gate_nxt;
   }
 
   // ---- dK^T, dV^T: lane = d, column = key; group 0 writes dV, group 1 writes dK ---------------
@@ -643,7 +648,8 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.q = (const __nv_bfloat16*)a.q;
   p.d_o = (const __nv_bfloat16*)a.d_o;
   p.lse = a.lse;
-  p.delta = (float*)(base + pl.off_delta);
+  p.delta = a.row_dot ? a.row_dot : (float*)(base + pl.off_delta);
+  p.row_scale = a.row_scale;
   p.q_of_block = (const int32_t*)(base + pl.off_qob);
   p.offsets = (const int32_t*)(base + pl.off_off);
   p.dk = (__nv_bfloat16*)a.dk_acc;     // the API passes the dk / dv outputs through these fields
@@ -666,7 +672,7 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
     NSA_CUDA_OK(cudaMemsetAsync(base + pl.off_acc, 0, 2 * align_up(n_kv * sizeof(float), 256), st));
 
   const size_t rows = (size_t)a.B * a.Hq * a.T;
-  {
+  if (!a.row_dot) {
     KernelScope ks("delta_kernel", st);
     delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)a.d_o,
                                                              (const __nv_bfloat16*)a.o,

@@ -68,7 +68,9 @@ def range_attn_forward(q, k, v, mode, window, block_size):
     return o, lse
 
 
-def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size):
+def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size, row_scale=None, row_dot=None):
+    """dq, dk, dv of a range branch.  With row_scale / row_dot (see nsa_gate_combine_bwd_rows) `do`
+    is the whole op's upstream gradient and the gate factor is applied inside the kernel."""
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     q, k, v, o, do = (t.contiguous() for t in (q, k, v, o, do))
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -77,8 +79,8 @@ def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size):
     ws = L.workspace(nws, q.device)
     L.check(L.lib().nsa_range_attn_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse),
                                        L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, k.shape[2],
-                                       mode, int(window), int(block_size), L.ptr(ws), nws,
-                                       L.IMPL[_impl], L.stream()))
+                                       mode, int(window), int(block_size), L.ptr(row_scale),
+                                       L.ptr(row_dot), L.ptr(ws), nws, L.IMPL[_impl], L.stream()))
     return dq, dk, dv
 
 
@@ -101,7 +103,7 @@ def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False):
     return (o, lse) if return_lse else o
 
 
-def _selection_backward(q, k, v, block_idx, block_size, do, o, lse):
+def _selection_backward(q, k, v, block_idx, block_size, do, o, lse, row_scale=None, row_dot=None):
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     S = block_idx.shape[-1]
     assert block_size >= 16
@@ -113,7 +115,8 @@ def _selection_backward(q, k, v, block_idx, block_size, do, o, lse):
     ws = L.workspace(nws, q.device)
     L.check(L.lib().nsa_selection_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
                                       L.ptr(lse), L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, S,
-                                      int(block_size), L.ptr(ws), nws, L.IMPL[_impl], L.stream()))
+                                      int(block_size), L.ptr(row_scale), L.ptr(row_dot), L.ptr(ws),
+                                      nws, L.IMPL[_impl], L.stream()))
     return dq, dk, dv
 
 
@@ -386,11 +389,21 @@ class _NSAAttention(torch.autograd.Function):
          lse_cmp, lse_slc, lse_win, block_idx, *cp) = ctx.saved_tensors
         block_size, window, learned, gate_dtype, pdt = ctx.cfg
         T = q.shape[2]
-        do_cmp, do_slc, do_win, d_gate = _gate_bwd(o_cmp, o_slc, o_win, gate, d_out)
-        dq, dk_cmp, dv_cmp = range_attn_backward(q, k_cmp, v_cmp, o_cmp, lse_cmp, do_cmp,
-                                                 MODE_COMPRESS, 0, block_size)
-        dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, do_slc, o_slc, lse_slc)
-        dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, do_win, MODE_WINDOW, window, 0)
+        # gate backward as per-row statistics; the branch kernels apply the gate factor themselves
+        B, Hq = q.shape[0], q.shape[1]
+        d_out = d_out.contiguous()
+        rs = torch.empty(3, B, Hq, T, device=q.device, dtype=torch.float32)
+        rd = torch.empty(3, B, Hq, T, device=q.device, dtype=torch.float32)
+        d_gate = torch.empty_like(gate)
+        L.check(L.lib().nsa_gate_combine_bwd_rows(
+            L.ptr(o_cmp), L.ptr(o_slc), L.ptr(o_win), L.ptr(gate), L.ptr(d_out), L.ptr(rs), L.ptr(rd),
+            L.ptr(d_gate), L.dims(B, Hq, 1, T, q.shape[3], L.dtype_code(q)), L.stream()))
+        dq, dk_cmp, dv_cmp = range_attn_backward(q, k_cmp, v_cmp, o_cmp, lse_cmp, d_out,
+                                                 MODE_COMPRESS, 0, block_size, rs[0], rd[0])
+        dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
+                                            rs[1], rd[1])
+        dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, d_out, MODE_WINDOW, window, 0,
+                                            rs[2], rd[2])
         dq_sum = torch.empty_like(dq)
         L.check(L.lib().nsa_sum3(L.ptr(dq), L.ptr(dq2), L.ptr(dq3), L.ptr(dq_sum), dq.numel(),
                                  L.dtype_code(dq), L.stream()))
