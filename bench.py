@@ -40,6 +40,12 @@ NAMES = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
 COMP = ["k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj"]
 
 
+def config_of(args, w):
+    return dict(workload=args.workload, **w, compression="learned block pooling, stride = block",
+                kv_tensors="six independent (kc,vc,ks,vs,kw,vw)",
+                l2="inputs (2.9 GB per step at c4_t32k) exceed the 126 MB L2")
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -71,8 +77,8 @@ def device_inputs(w, seed, device):
 
 
 def run_step(nsa, t, comp, w):
-    ins = [t[n].requires_grad_(True) for n in NAMES]
-    cps = {k: v.requires_grad_(True) for k, v in comp.items()}
+    ins = [t[n].detach().requires_grad_(True) for n in NAMES]
+    cps = {k: v.detach().requires_grad_(True) for k, v in comp.items()}
     out, idx = nsa.nsa_attention(*ins, w["block_size"], w["n_sel"], w["window"], compressor=cps,
                                  return_block_idx=True)
     grads = torch.autograd.grad(out, ins + [cps[k] for k in COMP], t["do"])
@@ -104,7 +110,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
@@ -196,7 +202,7 @@ def reference_arm(args, w, rank):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": dict(workload=args.workload, **w),
+            "config": config_of(args, w),
             "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
                              "sample": sample},
             "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0,
@@ -207,7 +213,7 @@ def reference_arm(args, w, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c4_t32k", choices=sorted(WORKLOADS))
@@ -363,9 +369,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": dict(workload=args.workload, **w, compression="learned block pooling, stride = block",
-                       kv_tensors="six independent (kc,vc,ks,vs,kw,vw)",
-                       l2="inputs (2.9 GB per step) exceed the 126 MB L2"),
+        "config": config_of(args, w),
         "tflops_algorithmic": total_flops * world / (ms / args.steps * 1e-3) / 1e12,
         "frac_of_tensor_peak": total_flops / (ms / args.steps * 1e-3) / 1e12 / pk["tflops"],
         "clocks": clocks,
