@@ -245,9 +245,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   // one TMA box per query and slab for Q and for dO; a missing query reads past T: zeros
   const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs * 2);
   auto gather = [&](const int* rowt) {
-    if (wg == 0 && p.kind != 2) {
+    if (p.kind != 2) {
       // window / compression: the tile's queries are consecutive tokens, one box per slab
-      if (lane == 0) {
+      if (lt == 0) {
         mbar_expect_tx(bar_g, gather_bytes);
         const int tq = rowt[0] >= 0 ? rowt[0] : p.T;
 #pragma unroll
@@ -256,18 +256,22 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           tma_load_3d(sDO + s * (kRows * 128), &tm_do_run, bar_g, s * 64, b * p.Hq + hkv * p.G, tq);
         }
       }
-    } else if (wg == 0) {
-      if (lane == 0) mbar_expect_tx(bar_g, gather_bytes);
-      __syncwarp();
-      for (int qq = lane; qq < p.nq; qq += 32) {
-        const int tq = rowt[qq] >= 0 ? rowt[qq] : p.T;
-#pragma unroll
-        for (int s = 0; s < kSlabs; ++s) {
-          tma_load_3d(sQ + s * (kRows * 128) + qq * p.G * 128, &tm_q, bar_g, s * 64,
-                      b * p.Hq + hkv * p.G, tq);
+    } else {
+      // selection: one box per (query, slab, tensor); the boxes are dealt out over the eight
+      // warps of the group (a few lanes each) because one warp issues them one after another
+      if (lt == 0) mbar_expect_tx(bar_g, gather_bytes);
+      const int op = lane * 8 + wg;                       // op id -> (query, slab, Q or dO)
+      const int n_ops = p.nq * kSlabs * 2;
+      for (int o = op; o < n_ops; o += kGroupThreads) {
+        const int qq = o / (kSlabs * 2), k = o % (kSlabs * 2);
+        const int s = k >> 1;
+        const int tq = rowt[qq] >= 0 ? rowt[qq] : p.T;   // a missing query reads past T: zeros
+        if (k & 1)
           tma_load_3d(sDO + s * (kRows * 128) + qq * p.G * 128, &tm_do, bar_g, s * 64,
                       b * p.Hq + hkv * p.G, tq);
-        }
+        else
+          tma_load_3d(sQ + s * (kRows * 128) + qq * p.G * 128, &tm_q, bar_g, s * 64,
+                      b * p.Hq + hkv * p.G, tq);
       }
     }
   };

@@ -144,16 +144,15 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 
   const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs);
   auto gather = [&](const int* rowt) {      // one TMA box per query and slab; no query: zeros
-    if (wg == 0) {
-      if (lane == 0) mbar_expect_tx(bar_g, gather_bytes);
-      __syncwarp();
-      for (int qq = lane; qq < p.nq; qq += 32) {
-        const int tq = rowt[qq] >= 0 ? rowt[qq] : p.T;
-#pragma unroll
-        for (int s = 0; s < kSlabs; ++s)
-          tma_load_3d(sQ + s * (kRows * 128) + qq * p.G * 128, &tm_q, bar_g, s * 64,
-                      b * p.Hq + hkv * p.G, tq);
-      }
+    // the boxes are dealt out over the eight warps of the group (a few lanes each): one warp
+    // issues its boxes one after another
+    if (lt == 0) mbar_expect_tx(bar_g, gather_bytes);
+    const int n_ops = p.nq * kSlabs;
+    for (int o = lane * 8 + wg; o < n_ops; o += kPairGroupThreads) {
+      const int qq = o / kSlabs, s = o % kSlabs;
+      const int tq = rowt[qq] >= 0 ? rowt[qq] : p.T;
+      tma_load_3d(sQ + s * (kRows * 128) + qq * p.G * 128, &tm_q, bar_g, s * 64,
+                  b * p.Hq + hkv * p.G, tq);
     }
   };
 
