@@ -300,24 +300,39 @@ __global__ void sel_combine_kernel(const __nv_bfloat16* __restrict__ o_part, con
   const int t = (int)((gid / ((size_t)kVec * G)) % T);
   const size_t bh = gid / ((size_t)kVec * G * T);
   const int32_t* ps = pair_of_slot + (bh * T + t) * S;
-  float M = -INFINITY;
-  for (int s = 0; s < S; ++s) {
-    const int pr = __ldg(ps + s);
-    if (pr >= 0) M = fmaxf(M, __ldg(ml + ((size_t)pr * G + g) * 3));
-  }
+  // one pass with a running maximum: o = sum_j 2^(m_j - M) O_j / sum_j 2^(m_j - M) l_j
+  float M = -INFINITY, L = 0.f;
   float acc[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  float L = 0.f;
-  if (M > -INFINITY) {
-    for (int s = 0; s < S; ++s) {
-      const int pr = __ldg(ps + s);
-      if (pr < 0) continue;
-      const size_t prow = (size_t)pr * G + g;
-      const float w = ex2(__ldg(ml + prow * 3) - M);
-      L += w * (__ldg(ml + prow * 3 + 1) + __ldg(ml + prow * 3 + 2));
-      const uint4 u = __ldg(reinterpret_cast<const uint4*>(o_part + prow * D + v * 8));
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  // four slots per trip: all loads of a trip are issued before the first is used
+  for (int s0 = 0; s0 < S; s0 += 4) {
+    int pr[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pr[j] = s0 + j < S ? __ldg(ps + s0 + j) : -1;
+    float m[4], l[4];
+    uint4 u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      m[j] = -INFINITY; l[j] = 0.f; u[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (pr[j] >= 0) {
+        const size_t prow = (size_t)pr[j] * G + g;
+        m[j] = __ldg(ml + prow * 3);
+        l[j] = __ldg(ml + prow * 3 + 1) + __ldg(ml + prow * 3 + 2);
+        u[j] = __ldg(reinterpret_cast<const uint4*>(o_part + prow * D + v * 8));
+      }
+    }
+    const float Mn = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), M);
+    if (Mn == -INFINITY) continue;                          // nothing in this trip, nothing before
+    const float a_old = ex2(M - Mn);                        // M = -inf: 0
+    L *= a_old;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] *= a_old;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float w = ex2(m[j] - Mn);                       // absent slot: 0
+      L = fmaf(w, l[j], L);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[j]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 f = __bfloat1622float2(h[e]);
@@ -325,6 +340,7 @@ __global__ void sel_combine_kernel(const __nv_bfloat16* __restrict__ o_part, con
         acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
       }
     }
+    M = Mn;
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
   const int b = (int)(bh / Hkv), hkv = (int)(bh % Hkv);
