@@ -125,6 +125,220 @@ __global__ void compress_bwd_block_kernel(const T* __restrict__ x, const float* 
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// bf16 fast path of the learned pooling for D in {16,32,64,128}: one CTA of 256 threads takes
+// kCompRows consecutive blocks, streams their tokens with 16-byte loads (D/8 threads per token
+// row, 256/(D/8) token rows at a time) and keeps the projection matrix in shared memory
+// ------------------------------------------------------------------------------------------
+constexpr int kCompRows = 8;
+constexpr int kCompThreads = 256;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 t = __bfloat1622float2(h[e]);
+    f[2 * e] = t.x; f[2 * e + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void pool_weights(const float* __restrict__ logits, float* w, int bs) {
+  float mx = -INFINITY;
+  for (int r = 0; r < bs; ++r) mx = fmaxf(mx, logits[r]);
+  float den = 0.f;
+  for (int r = 0; r < bs; ++r) den += expf(logits[r] - mx);
+  for (int r = threadIdx.x; r < bs; r += blockDim.x) w[r] = expf(logits[r] - mx) / den;
+}
+
+// shared memory: w[bs] | cvec[D] | pooled[kCompRows][D] | part[kCompRows][8][D] | projT[D][D+1]
+__global__ void __launch_bounds__(kCompThreads)
+compress_fast_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ intra,
+                         const float* __restrict__ logits, const float* __restrict__ proj,
+                         __nv_bfloat16* __restrict__ out, float* __restrict__ pooled_out, int T_, int D,
+                         int bs, int n_blk, size_t rows) {
+  extern __shared__ float sm[];
+  float* w = sm;
+  float* cvec = w + bs;
+  float* pooled = cvec + D;
+  float* part = pooled + kCompRows * D;
+  float* projT = part + kCompRows * 8 * D;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int VL = D >> 3, RG = kCompThreads / VL;
+  const int vl = tid % VL, rg = tid / VL;
+  const size_t row0 = (size_t)blockIdx.x * kCompRows;
+  if (out)
+    for (int idx = tid; idx < D * D; idx += kCompThreads) projT[(idx % D) * (D + 1) + idx / D] = proj[idx];
+  pool_weights(logits, w, bs);
+  __syncthreads();
+  // the block-independent part: sum_r w[r] * intra[r][:]
+  {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = rg; r < bs; r += RG) {
+      const float4 lo = *reinterpret_cast<const float4*>(intra + (size_t)r * D + vl * 8);
+      const float4 hi = *reinterpret_cast<const float4*>(intra + (size_t)r * D + vl * 8 + 4);
+      const float wr = w[r];
+      a[0] = fmaf(wr, lo.x, a[0]); a[1] = fmaf(wr, lo.y, a[1]); a[2] = fmaf(wr, lo.z, a[2]); a[3] = fmaf(wr, lo.w, a[3]);
+      a[4] = fmaf(wr, hi.x, a[4]); a[5] = fmaf(wr, hi.y, a[5]); a[6] = fmaf(wr, hi.z, a[6]); a[7] = fmaf(wr, hi.w, a[7]);
+    }
+    // threads of a warp that hold the same columns (VL apart) meet by shuffles
+    for (int o = 16; o >= VL; o >>= 1)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(0xffffffffu, a[e], o);
+    if ((tid & 31) < VL)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part[warp * D + vl * 8 + e] = a[e];
+  }
+  __syncthreads();
+  if (tid < D) {
+    float c = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) c += part[k * D + tid];
+    cvec[tid] = c;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int b = 0; b < kCompRows; ++b) {
+    const size_t row = row0 + b;
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (row < rows) {
+      const size_t bh = row / n_blk;
+      const int j = (int)(row % n_blk);
+      const __nv_bfloat16* xb = x + (bh * T_ + (size_t)j * bs) * D + vl * 8;
+      for (int r = rg; r < bs; r += RG) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(xb + (size_t)r * D));
+        float f[8];
+        unpack8(u, f);
+        const float wr = w[r];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = fmaf(wr, f[e], a[e]);
+      }
+    }
+    for (int o = 16; o >= VL; o >>= 1)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(0xffffffffu, a[e], o);
+    if ((tid & 31) < VL)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part[(b * 8 + warp) * D + vl * 8 + e] = a[e];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < kCompRows * D; idx += kCompThreads) {
+    const int b = idx / D, d = idx % D;
+    float s = cvec[d];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += part[(b * 8 + k) * D + d];
+    pooled[idx] = s;
+    if (pooled_out && row0 + b < rows) pooled_out[(row0 + b) * D + d] = s;
+  }
+  if (!out) return;
+  __syncthreads();
+  // out[row][o] = sum_i proj[o][i] * pooled[row][i], four rows per thread
+  for (int idx = tid; idx < (kCompRows / 4) * D; idx += kCompThreads) {
+    const int b0 = (idx / D) * 4, o = idx % D;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < D; ++i) {
+      const float pv = projT[i * (D + 1) + o];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[k] = fmaf(pv, pooled[(b0 + k) * D + i], acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (row0 + b0 + k < rows) out[(row0 + b0 + k) * D + o] = __float2bfloat16(acc[k]);
+  }
+}
+
+// backward of the same: d_pooled = d_out @ W, dx = w[pos] * d_pooled, sum_dpooled += d_pooled,
+// d_w[pos] += sum_d d_pooled[d] * x[pos][d] (the intra_pos share of d_w is added by the final
+// kernel from sum_dpooled).  shared memory: w[bs] | dw[bs] | go[rows][D] | dp[rows][D] | proj[D][D]
+__global__ void __launch_bounds__(kCompThreads)
+compress_fast_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ logits,
+                         const float* __restrict__ proj, const __nv_bfloat16* __restrict__ d_out,
+                         __nv_bfloat16* __restrict__ dx, float* __restrict__ d_pooled_out,
+                         float* __restrict__ sum_dpooled, float* __restrict__ d_w, int T_, int D, int bs,
+                         int n_blk, size_t rows) {
+  extern __shared__ float sm[];
+  float* w = sm;
+  float* dw = w + bs;
+  float* go = dw + bs;
+  float* dp = go + kCompRows * D;
+  float* pj = dp + kCompRows * D;
+  const int tid = threadIdx.x;
+  const int VL = D >> 3, RG = kCompThreads / VL;
+  const int vl = tid % VL, rg = tid / VL;
+  const size_t row0 = (size_t)blockIdx.x * kCompRows;
+  for (int idx = tid; idx < D * D; idx += kCompThreads) pj[idx] = proj[idx];
+  for (int idx = tid; idx < kCompRows * D; idx += kCompThreads)
+    go[idx] = row0 + idx / D < rows ? __bfloat162float(d_out[row0 * D + idx]) : 0.f;
+  for (int r = tid; r < bs; r += kCompThreads) dw[r] = 0.f;
+  pool_weights(logits, w, bs);
+  __syncthreads();
+  for (int idx = tid; idx < (kCompRows / 4) * D; idx += kCompThreads) {
+    const int b0 = (idx / D) * 4, d = idx % D;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int o = 0; o < D; ++o) {
+      const float pv = pj[o * D + d];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[k] = fmaf(go[(b0 + k) * D + o], pv, acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      dp[(b0 + k) * D + d] = acc[k];
+      if (row0 + b0 + k < rows) d_pooled_out[(row0 + b0 + k) * D + d] = acc[k];
+    }
+  }
+  __syncthreads();
+  if (tid < D) {
+    float s = 0.f;
+#pragma unroll
+    for (int b = 0; b < kCompRows; ++b) s += dp[b * D + tid];   // rows past the end hold zeros
+    atomicAdd(sum_dpooled + tid, s);
+  }
+#pragma unroll 2
+  for (int b = 0; b < kCompRows; ++b) {
+    const size_t row = row0 + b;
+    if (row >= rows) break;
+    const size_t bh = row / n_blk;
+    const int j = (int)(row % n_blk);
+    const size_t base = (bh * T_ + (size_t)j * bs) * D + vl * 8;
+    float g[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] = dp[b * D + vl * 8 + e];
+    for (int r0 = 0; r0 < bs; r0 += RG) {
+      const int r = r0 + rg;
+      float dot = 0.f;
+      if (r < bs) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(x + base + (size_t)r * D));
+        float f[8];
+        unpack8(u, f);
+        const float wr = w[r];
+        uint4 o;
+        o.x = pack2(wr * g[0], wr * g[1]); o.y = pack2(wr * g[2], wr * g[3]);
+        o.z = pack2(wr * g[4], wr * g[5]); o.w = pack2(wr * g[6], wr * g[7]);
+        *reinterpret_cast<uint4*>(dx + base + (size_t)r * D) = o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot = fmaf(g[e], f[e], dot);
+      }
+      for (int o = VL >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (vl == 0 && r < bs) atomicAdd(dw + r, dot);
+    }
+  }
+  __syncthreads();
+  for (int r = tid; r < bs; r += kCompThreads) atomicAdd(d_w + r, dw[r]);
+}
+
+bool compress_fast_ok(int D, int bs, int dtype) {
+  return dtype == NSA_DTYPE_BF16 && (D == 16 || D == 32 || D == 64 || D == 128) && bs >= 1 && bs <= 1024;
+}
+size_t compress_fast_fwd_smem(int D, int bs, bool with_proj) {
+  return ((size_t)bs + D + kCompRows * D + kCompRows * 8 * D + (with_proj ? (size_t)D * (D + 1) : 0)) * sizeof(float);
+}
+size_t compress_fast_bwd_smem(int D, int bs) {
+  return (2 * (size_t)bs + 2 * kCompRows * D + (size_t)D * D) * sizeof(float);
+}
+
 // tail tokens past the last complete block get zero gradient
 template <typename T>
 __global__ void zero_tail_kernel(T* __restrict__ dx, int T_, int D, int t_first, size_t n_bh) {
@@ -152,9 +366,18 @@ __global__ void compress_bwd_proj_kernel(const T* __restrict__ d_out, const floa
 // stage C: d_intra[pos][d] = w[pos] * sum_dpooled[d]; d_logits = w * (d_w - sum(d_w * w))
 __global__ void compress_bwd_final_kernel(const float* __restrict__ logits,
                                           const float* __restrict__ sum_dpooled,
-                                          const float* __restrict__ d_w, float* __restrict__ d_intra,
+                                          float* __restrict__ d_w, const float* __restrict__ intra,
+                                          float* __restrict__ d_intra,
                                           float* __restrict__ d_logits, int D, int bs) {
   extern __shared__ float w[];
+  if (intra) {   // the streaming kernel left out sum_d sum_dpooled[d] * intra_pos[pos][d]
+    for (int r = threadIdx.x; r < bs; r += blockDim.x) {
+      float s = 0.f;
+      for (int d = 0; d < D; ++d) s = fmaf(sum_dpooled[d], intra[(size_t)r * D + d], s);
+      d_w[r] += s;
+    }
+    __syncthreads();
+  }
   float mx = -INFINITY;
   for (int r = 0; r < bs; ++r) mx = fmaxf(mx, logits[r]);
   float den = 0.f;
@@ -262,17 +485,27 @@ __global__ void csr_mark_kernel(const int32_t* __restrict__ idx, uint32_t* __res
   atomicOr(bitmap + (bh * n_blk + j) * words + (t >> 5), 1u << (t & 31));
 }
 
-// one warp per (bh, block) row: population count
+// one warp per (bh, block) row: population count, and for every bitmap word the number of set
+// bits before it in the row
 __global__ void csr_count_kernel(const uint32_t* __restrict__ bitmap, int32_t* __restrict__ counts,
-                                 int words, size_t rows) {
+                                 int32_t* __restrict__ prefix, int words, size_t rows) {
   const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
-  int c = 0;
-  for (int w = lane; w < words; w += 32) c += __popc(bitmap[row * words + w]);
+  int run = 0;
+  for (int w0 = 0; w0 < words; w0 += 32) {
+    const int w = w0 + lane;
+    const int c = w < words ? __popc(bitmap[row * words + w]) : 0;
+    int incl = c;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-  if (lane == 0) counts[row] = c;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (w < words) prefix[row * words + w] = run + incl - c;
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) counts[row] = run;
 }
 
 // single CTA exclusive scan of counts[rows] into block_offsets laid out [BH][n_blk+1]
@@ -306,44 +539,32 @@ __global__ void csr_scan_kernel(const int32_t* __restrict__ counts, int32_t* __r
   }
 }
 
-// one warp per row: emit set bits in ascending t
-__global__ void csr_fill_kernel(const uint32_t* __restrict__ bitmap, const int32_t* __restrict__ row_start,
+// one thread per (b, hkv, t, slot) entry: its pair index is the row start plus the rank of t
+// among the set bits of row (b, hkv, block); a block listed twice by one query keeps its first slot
+__global__ void csr_fill_kernel(const int32_t* __restrict__ idx, const uint32_t* __restrict__ bitmap,
+                                const int32_t* __restrict__ prefix, const int32_t* __restrict__ row_start,
                                 int32_t* __restrict__ q_of_block, int32_t* __restrict__ pair_bh,
-                                int n_blk, int words, size_t rows, const int32_t* __restrict__ idx,
-                                int32_t* __restrict__ pair_of_slot, int T_, int S) {
-  const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  int pos = row_start[row];
-  const int bh = (int)(row / n_blk);
-  for (int w0 = 0; w0 < words; w0 += 32) {
-    const int w = w0 + lane;
-    const uint32_t bits = w < words ? bitmap[row * words + w] : 0u;
-    const int c = __popc(bits);
-    int incl = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
+                                int32_t* __restrict__ pair_of_slot, int T_, int S, int bs, int n_blk,
+                                int words, size_t n_entries) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_entries) return;
+  const int j = idx[i];
+  const int slot = (int)(i % S);
+  const int t = (int)((i / S) % T_);
+  const size_t bh = i / ((size_t)S * T_);
+  int p = -1;
+  if (j >= 0 && j < n_blk && (long long)j * bs <= t) {
+    bool dup = false;
+    for (int s2 = 0; s2 < slot; ++s2) dup |= idx[i - slot + s2] == j;
+    if (!dup) {
+      const size_t row = bh * n_blk + j;
+      const uint32_t bits = bitmap[row * words + (t >> 5)];
+      p = row_start[row] + prefix[row * words + (t >> 5)] + __popc(bits & ((1u << (t & 31)) - 1u));
+      q_of_block[p] = t;
+      pair_bh[p] = (int)bh;
     }
-    int p = pos + incl - c;
-    uint32_t rem = bits;
-    while (rem) {
-      const int bit = __ffs(rem) - 1;
-      rem &= rem - 1;
-      const int tq = w * 32 + bit;
-      q_of_block[p] = tq;
-      pair_bh[p] = bh;
-      if (pair_of_slot) {   // which slot of query tq names this block
-        const int jb = (int)(row % n_blk);
-        const size_t e0 = ((size_t)bh * T_ + tq) * S;
-        for (int sl = 0; sl < S; ++sl)
-          if (idx[e0 + sl] == jb) { pair_of_slot[e0 + sl] = p; break; }
-      }
-      ++p;
-    }
-    pos += __shfl_sync(0xffffffffu, incl, 31);
   }
+  if (pair_of_slot) pair_of_slot[i] = p;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -499,7 +720,14 @@ extern "C" int nsa_block_compress_fwd(const void* x, const float* intra_pos, con
   if (ctas == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t sm = (size_t)(block_size + D) * sizeof(float);
-  if (dtype == NSA_DTYPE_BF16)
+  if (compress_fast_ok(D, block_size, dtype)) {
+    const size_t fsm = compress_fast_fwd_smem(D, block_size, true);
+    NSA_CUDA_OK(cudaFuncSetAttribute(compress_fast_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fsm));
+    KernelScope ks("compress_fast_fwd_kernel", st);
+    compress_fast_fwd_kernel<<<(unsigned)((ctas + kCompRows - 1) / kCompRows), kCompThreads, fsm, st>>>(
+        (const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D,
+        block_size, n_blk, ctas);
+  } else if (dtype == NSA_DTYPE_BF16)
     { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D, block_size, n_blk); }
   else
     { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)out, (float*)nullptr, T, D, block_size, n_blk); }
@@ -536,8 +764,23 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
   const size_t tail = (size_t)(T - n_blk * block_size) * D * B * Hkv;
   NSA_CUDA_OK(cudaMemsetAsync(d_proj_w, 0, (size_t)D * D * sizeof(float), st));
   const dim3 pgrid(D, (unsigned)(rows >= 4096 ? 64 : (rows >= 64 ? rows / 64 : 1)));
+  const bool fast = compress_fast_ok(D, block_size, dtype);
   if (rows > 0) {
-    if (dtype == NSA_DTYPE_BF16) {
+    if (fast) {
+      const size_t fsm = compress_fast_fwd_smem(D, block_size, false), bsm = compress_fast_bwd_smem(D, block_size);
+      NSA_CUDA_OK(cudaFuncSetAttribute(compress_fast_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)compress_fast_fwd_smem(D, block_size, true)));
+      NSA_CUDA_OK(cudaFuncSetAttribute(compress_fast_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsm));
+      const unsigned grid = (unsigned)((rows + kCompRows - 1) / kCompRows);
+      { KernelScope ks("compress_fast_fwd_kernel", st);
+        compress_fast_fwd_kernel<<<grid, kCompThreads, fsm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w,
+                                                                 (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk, rows); }
+      { KernelScope ks("compress_fast_bwd_kernel", st);
+        compress_fast_bwd_kernel<<<grid, kCompThreads, bsm, st>>>((const __nv_bfloat16*)x, pool_logits, proj_w,
+                                                                 (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled,
+                                                                 sum_dp, d_w, T, D, block_size, n_blk, rows); }
+      { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<pgrid, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D); }
+    } else if (dtype == NSA_DTYPE_BF16) {
       { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk); }
       { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk); }
       { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<pgrid, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D); }
@@ -555,7 +798,7 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
       { KernelScope ks("zero_tail_kernel", st); zero_tail_kernel<<<blocks_for(tail, 256), 256, 0, st>>>((float*)dx, T, D, n_blk * block_size, (size_t)B * Hkv); }
     NSA_LAUNCH_OK("zero_tail_kernel");
   }
-  { KernelScope ks("compress_bwd_final_kernel", st); compress_bwd_final_kernel<<<1, 256, block_size * sizeof(float), st>>>(pool_logits, sum_dp, d_w, d_intra_pos, d_pool_logits, D, block_size); }
+  { KernelScope ks("compress_bwd_final_kernel", st); compress_bwd_final_kernel<<<1, 256, block_size * sizeof(float), st>>>(pool_logits, sum_dp, d_w, fast && rows > 0 ? intra_pos : nullptr, d_intra_pos, d_pool_logits, D, block_size); }
   NSA_LAUNCH_OK("compress_bwd_final_kernel");
   return NSA_OK;
 }
@@ -625,7 +868,7 @@ extern "C" size_t nsa_csr_workspace_bytes(int B, int Hkv, int T, int S, int bloc
   const size_t n_blk = block_size > 0 ? (T + block_size - 1) / block_size : 0;
   const size_t rows = (size_t)B * Hkv * n_blk;
   const size_t words = (T + 31) / 32;
-  return align_up(rows * words * 4, 256) + 2 * align_up(rows * 4, 256);
+  return 2 * align_up(rows * words * 4, 256) + 2 * align_up(rows * 4, 256);
 }
 
 namespace nsa {
@@ -642,25 +885,27 @@ int build_csr_internal(const int32_t* block_idx, int B, int Hkv, int T, int S, i
     NSA_CUDA_OK(cudaMemsetAsync(block_offsets, 0, (size_t)B * Hkv * sizeof(int32_t), st));
     return NSA_OK;
   }
-  const size_t need = align_up(rows * words * 4, 256) + 2 * align_up(rows * 4, 256);
+  const size_t need = 2 * align_up(rows * words * 4, 256) + 2 * align_up(rows * 4, 256);
   if (!workspace || workspace_bytes < need) {
     set_error("csr workspace too small");
     return NSA_ERR_WORKSPACE;
   }
   uint32_t* bitmap = (uint32_t*)workspace;
-  int32_t* counts = (int32_t*)((char*)workspace + align_up(rows * words * 4, 256));
+  int32_t* prefix = (int32_t*)((char*)workspace + align_up(rows * words * 4, 256));
+  int32_t* counts = (int32_t*)((char*)prefix + align_up(rows * words * 4, 256));
   int32_t* row_start = (int32_t*)((char*)counts + align_up(rows * 4, 256));
   NSA_CUDA_OK(cudaMemsetAsync(bitmap, 0, rows * words * 4, st));
   const size_t n_entries = (size_t)B * Hkv * T * S;
-  if (pair_of_slot && n_entries)
-    NSA_CUDA_OK(cudaMemsetAsync(pair_of_slot, 0xff, n_entries * sizeof(int32_t), st));
   if (n_entries) {
     KernelScope ks("csr_mark_kernel", st);
     csr_mark_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(block_idx, bitmap, T, S, block_size, n_blk, words, n_entries);
   }
-  { KernelScope ks("csr_count_kernel", st); csr_count_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, counts, words, rows); }
+  { KernelScope ks("csr_count_kernel", st); csr_count_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, counts, prefix, words, rows); }
   { KernelScope ks("csr_scan_kernel", st); csr_scan_kernel<<<1, 1024, 0, st>>>(counts, block_offsets, row_start, n_blk, rows); }
-  { KernelScope ks("csr_fill_kernel", st); csr_fill_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(bitmap, row_start, q_of_block, pair_bh, n_blk, words, rows, block_idx, pair_of_slot, T, S); }
+  if (n_entries) {
+    KernelScope ks("csr_fill_kernel", st);
+    csr_fill_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(block_idx, bitmap, prefix, row_start, q_of_block, pair_bh, pair_of_slot, T, S, block_size, n_blk, words, n_entries);
+  }
   NSA_LAUNCH_OK("csr kernels");
   return NSA_OK;
 }
@@ -677,7 +922,8 @@ extern "C" int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int
 }
 
 // ---- CSR without caller-provided scratch -----------------------------------------------------
-// The scratch of the CSR build (bitmap, counts, row starts) lives in this fixed device array.
+// The scratch of the CSR build (bitmap, bit-rank prefixes, counts, row starts) lives in this fixed
+// device array.
 // In host code the array's name is only a handle: the device address is looked up once per
 // device with cudaGetSymbolAddress and that pointer is what the kernels receive.
 constexpr size_t kCsrBuiltinScratchBytes = (size_t)8 << 20;
