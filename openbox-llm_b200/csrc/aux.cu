@@ -619,6 +619,75 @@ __global__ void gate_bwd_kernel(const T* __restrict__ oc, const T* __restrict__ 
   }
 }
 
+// bf16 rows of D = 8 * VL elements (VL a power of two <= 32): VL threads per row, 16 bytes each
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 t = __bfloat1622float2(h[e]);
+    f[2 * e] = t.x; f[2 * e + 1] = t.y;
+  }
+}
+
+__global__ void gate_fwd_vec_kernel(const __nv_bfloat16* __restrict__ oc, const __nv_bfloat16* __restrict__ os,
+                                    const __nv_bfloat16* __restrict__ ow, const __nv_bfloat16* __restrict__ gate,
+                                    __nv_bfloat16* __restrict__ out, size_t rows, int VL) {
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t row = gid / VL;
+  if (row >= rows) return;
+  const size_t i = gid * 8;
+  float a[8], b[8], c[8];
+  load8(oc + i, a); load8(os + i, b); load8(ow + i, c);
+  const float g0 = sigmoidf_(__bfloat162float(gate[row * 3 + 0]));
+  const float g1 = sigmoidf_(__bfloat162float(gate[row * 3 + 1]));
+  const float g2 = sigmoidf_(__bfloat162float(gate[row * 3 + 2]));
+  uint4 r;
+  __nv_bfloat162* rs = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    rs[e] = __floats2bfloat162_rn(g0 * a[2 * e] + g1 * b[2 * e] + g2 * c[2 * e],
+                                  g0 * a[2 * e + 1] + g1 * b[2 * e + 1] + g2 * c[2 * e + 1]);
+  *reinterpret_cast<uint4*>(out + i) = r;
+}
+
+__global__ void gate_bwd_rows_vec_kernel(const __nv_bfloat16* __restrict__ oc, const __nv_bfloat16* __restrict__ os,
+                                         const __nv_bfloat16* __restrict__ ow, const __nv_bfloat16* __restrict__ gate,
+                                         const __nv_bfloat16* __restrict__ d_out, float* __restrict__ row_scale,
+                                         float* __restrict__ row_dot, __nv_bfloat16* __restrict__ d_gate,
+                                         size_t rows, int VL) {
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t row = gid / VL;                    // the grid is padded to whole warps: no early return
+  const bool live = row < rows;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+  if (live) {
+    const size_t i = gid * 8;
+    float g[8], a[8], b[8], c[8];
+    load8(d_out + i, g); load8(oc + i, a); load8(os + i, b); load8(ow + i, c);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { a0 = fmaf(g[e], a[e], a0); a1 = fmaf(g[e], b[e], a1); a2 = fmaf(g[e], c[e], a2); }
+  }
+  for (int o = VL >> 1; o > 0; o >>= 1) {
+    a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+    a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+  }
+  if (live && gid % VL == 0) {
+    const float g0 = sigmoidf_(__bfloat162float(gate[row * 3 + 0]));
+    const float g1 = sigmoidf_(__bfloat162float(gate[row * 3 + 1]));
+    const float g2 = sigmoidf_(__bfloat162float(gate[row * 3 + 2]));
+    row_scale[row] = g0; row_scale[rows + row] = g1; row_scale[2 * rows + row] = g2;
+    row_dot[row] = a0; row_dot[rows + row] = a1; row_dot[2 * rows + row] = a2;
+    d_gate[row * 3 + 0] = __float2bfloat16(a0 * g0 * (1.f - g0));
+    d_gate[row * 3 + 1] = __float2bfloat16(a1 * g1 * (1.f - g1));
+    d_gate[row * 3 + 2] = __float2bfloat16(a2 * g2 * (1.f - g2));
+  }
+}
+
+inline bool gate_vec_ok(int D, int dtype) {
+  return dtype == NSA_DTYPE_BF16 && D >= 8 && D <= 256 && (D & (D - 1)) == 0;
+}
+
 // out = a + b + c, fp32 accumulation, 8 elements per thread (bf16) or 4 (fp32)
 __global__ void sum3_bf16_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
                                  const uint4* __restrict__ c, uint4* __restrict__ out, size_t n8) {
@@ -966,7 +1035,9 @@ extern "C" int nsa_gate_combine_bwd_rows(const void* o_cmp, const void* o_slc, c
   if (rows == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   KernelScope ks("gate_bwd_rows_kernel", st);
-  if (dims->dtype == NSA_DTYPE_BF16)
+  if (gate_vec_ok(dims->D, dims->dtype))
+    gate_bwd_rows_vec_kernel<<<blocks_for(rows * (dims->D / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (const __nv_bfloat16*)d_out, row_scale, row_dot, (__nv_bfloat16*)d_gate_logits, rows, dims->D / 8);
+  else if (dims->dtype == NSA_DTYPE_BF16)
     gate_bwd_rows_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (const __nv_bfloat16*)d_out, row_scale, row_dot, (__nv_bfloat16*)d_gate_logits, rows, dims->D);
   else
     gate_bwd_rows_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (const float*)d_out, row_scale, row_dot, (float*)d_gate_logits, rows, dims->D);
@@ -998,7 +1069,9 @@ extern "C" int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const 
   const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
   if (rows == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dims->dtype == NSA_DTYPE_BF16)
+  if (gate_vec_ok(dims->D, dims->dtype))
+    { KernelScope ks("gate_fwd_kernel", st); gate_fwd_vec_kernel<<<blocks_for(rows * (dims->D / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (__nv_bfloat16*)out, rows, dims->D / 8); }
+  else if (dims->dtype == NSA_DTYPE_BF16)
     { KernelScope ks("gate_fwd_kernel", st); gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const __nv_bfloat16*)o_cmp, (const __nv_bfloat16*)o_slc, (const __nv_bfloat16*)o_win, (const __nv_bfloat16*)gate_logits, (__nv_bfloat16*)out, rows, dims->D); }
   else
     { KernelScope ks("gate_fwd_kernel", st); gate_fwd_kernel<<<blocks_for(rows, 8), 256, 0, st>>>((const float*)o_cmp, (const float*)o_slc, (const float*)o_win, (const float*)gate_logits, (float*)out, rows, dims->D); }
