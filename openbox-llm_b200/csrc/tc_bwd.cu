@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(512, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_q_run, const __grid_constant__ CUtensorMap tm_do_run,
-              const BwdArgs p) {
+              const __grid_constant__ CUtensorMap tm_dq, const BwdArgs p) {
   constexpr int kSlabs = D / 64;
   constexpr int kKVBytes = kKeys * 128 * kSlabs;
   constexpr uint32_t kTmemCols = 512;
@@ -186,10 +186,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       bad = 1;
     }
     *s_abort = bad;
-    for (int k = 0; k <= 6; ++k) mbar_init(bars + k, 1);
+    // S / dP ready (bars 1 and 4) = the MMAs have completed and the previous tile's dQ store
+    // has left the staging tile, which is the P / dS tile: two arrivals
+    for (int k = 0; k <= 6; ++k) mbar_init(bars + k, (k == 1 || k == 4) ? 2 : 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
-    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_do);
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_do); prefetch_tensormap(&tm_dq);
   }
   __syncthreads();
   if (*s_abort) return;
@@ -328,6 +330,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                desc_at(va, slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
       tc_commit(bar_sp);
+      bulk_wait_read();
+      mbar_arrive(bar_sp);
     }
     // valid key columns of this row: one range [lo, hi]
     int lo = 0, hi = -1;
@@ -417,9 +421,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (i + 2 < rt_end) gather(s_rowt + (buf ^ 1) * kMaxNq);
     NSA_STAMP(6);
     __syncwarp();
-    // dQ: TMEM -> bf16 -> staging tile (P/dS region, 256-byte rows, 16-byte chunks XOR row)
+    // dQ: TMEM -> bf16 -> staging tile (the P / dS region): one slab of 128-byte rows per 64
+    // columns, 16-byte chunks XOR row, which is the layout of a 128B-swizzled TMA box
     {
-      const uint32_t stage_row = smem_u32(sP) + row * 256;
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) {          // this thread's half of the D columns
         const int col0 = half * (D / 2) + cc * 32;
@@ -429,7 +433,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
           const uint32_t chunk = (uint32_t)((col0 >> 3) + v4);
-          st_shared_v4(stage_row + ((chunk ^ (row & 15)) << 4),
+          st_shared_v4(smem_u32(sP) + (chunk >> 3) * (kRows * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4),
                        pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1])),
                        pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3])),
                        pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5])),
@@ -437,33 +441,32 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
       }
     }
+    fence_proxy_async();
     tc_fence_before();
     NSA_STAMP(8);
     group_sync(grp);
     NSA_STAMP(9);
-    {   // whole rows out: 16 lanes write the 256 (D = 128) or 128 bytes of one row
+    if ((i + 1) * p.nq <= n_q) {
+      // a full tile: its rows are consecutive in the partial buffer, one TMA store per slab
+      if (lt == 0) {
+        const int slot = p.kind == 2 ? 0 : (p.kind == 0 ? j % p.n_slots : j);
+        const int mid = p.kind == 2 ? pair_base + i * p.nq : t_lo + i * p.nq;
+        const int outer = p.kind == 2 ? 0 : bh;
+#pragma unroll
+        for (int sl = 0; sl < kSlabs; ++sl)
+          tma_store_5d(&tm_dq, sP + sl * (kRows * 128), sl * 64, 0, slot, mid, outer);
+        bulk_commit();
+      }
+    } else {   // the ragged last tile: 16 lanes write the 256 (D = 128) or 128 bytes of one row
       constexpr int kChunks = D / 8;
       constexpr int kRowsPerPass = kGroupThreads / kChunks;
       const int c = lt % kChunks;
-#if defined(NSA_EXP) && NSA_EXP == 3
-      if (c == 12345)
-#endif
 #pragma unroll 4
       for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
-#if defined(NSA_EXP) && NSA_EXP == 2
-        const uint32_t prow = (uint32_t)(r + it_no * 128 + j * 1024);
-#else
         const uint32_t prow = s_prow[r];
-#endif
         if (prow != 0xffffffffu) {
-#if defined(NSA_EXP) && NSA_EXP == 2
-          const uint4 v = make_uint4(r, c, r, c);
-#else
-          const uint4 v = *reinterpret_cast<const uint4*>(sP + r * 256 + ((c ^ (r & 15)) << 4));
-#endif
-#if defined(NSA_EXP) && NSA_EXP == 1
-          if (v.x == 0x12345678u)
-#endif
+          const uint4 v = *reinterpret_cast<const uint4*>(sP + (c >> 3) * (kRows * 128) + r * 128 +
+                                                          (((c & 7) ^ (r & 7)) << 4));
           *reinterpret_cast<uint4*>(p.dq_part + (size_t)prow * D + c * 8) = v;
         }
       }
@@ -472,6 +475,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     t_cur = t_nxt; t_nxt = t_nn; lse_cur = lse_nxt; delta_cur = delta_nxt; gate_cur = gate_nxt;
   }
 
+  if (lt == 0) bulk_wait_all();
   // ---- dK^T, dV^T: lane = d, column = key; group 0 writes dV, group 1 writes dK ---------------
   tc_fence_before();
   __syncthreads();
@@ -699,17 +703,21 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   CUtensorMap tm_q_run, tm_do_run;
   if (rc == NSA_OK) rc = make_map_query_rows(&tm_q_run, a.q, a.D, a.T, a.B * a.Hq, G, pl.nq);
   if (rc == NSA_OK) rc = make_map_query_rows(&tm_do_run, a.d_o, a.D, a.T, a.B * a.Hq, G, pl.nq);
+  CUtensorMap tm_dq;
+  if (rc == NSA_OK)
+    rc = a.kind == 2 ? make_map_partial(&tm_dq, p.dq_part, a.D, G, 1, pl.cap_pairs ? pl.cap_pairs : 1, 1, pl.nq)
+                     : make_map_partial(&tm_dq, p.dq_part, a.D, G, pl.n_slots, a.T, (size_t)a.B * a.Hkv, pl.nq);
   if (rc != NSA_OK) return rc;
   const size_t smem = bwd_smem_bytes(a.D);
   dim3 grid(pl.n_ktiles, a.B * a.Hkv, pl.n_splits);
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, p);
+    tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, p);
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, p);
+    tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, p);
   }
   NSA_LAUNCH_OK("tc_bwd_kernel");
   if (pl.n_splits > 1) {

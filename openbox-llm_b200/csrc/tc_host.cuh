@@ -59,6 +59,24 @@ static inline int make_map_query_rows(CUtensorMap* m, const void* base, int D, i
   return NSA_OK;
 }
 
+// 5-D map over a bf16 partial buffer [outer][mid][slots][G][D] for stores of boxes
+// 64 elements x G x 1 x box_mid x 1: the G rows of box_mid consecutive `mid` entries of one slot.
+static inline int make_map_partial(CUtensorMap* m, void* base, int D, int G, size_t slots, size_t mid,
+                                   size_t outer, int box_mid) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available"); return NSA_ERR_CUDA; }
+  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)G, (cuuint64_t)slots, (cuuint64_t)mid, (cuuint64_t)outer};
+  const cuuint64_t row = (cuuint64_t)D * 2;
+  cuuint64_t strides[4] = {row, row * G, row * G * slots, row * G * slots * mid};
+  cuuint32_t box[5] = {64u, (cuuint32_t)G, 1u, (cuuint32_t)box_mid, 1u};
+  cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (partials) failed with %d", (int)r); return NSA_ERR_CUDA; }
+  return NSA_OK;
+}
+
 static inline int group_pad(int G) {
   int gp = 1;
   while (gp < G) gp <<= 1;
