@@ -47,7 +47,8 @@ __host__ __device__ inline size_t pair_smem_bytes(int D) {
 template <int D>
 __global__ void __launch_bounds__(512, 1)
 tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                  const __grid_constant__ CUtensorMap tm_q, const PairArgs p) {
+                  const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_o,
+                  const PairArgs p) {
   constexpr int kSlabs = D / 64;
   constexpr int kKVBytes = kKeys * 128 * kSlabs;
   constexpr int kQBytes = kRows * 128 * kSlabs;
@@ -106,6 +107,7 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
     prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_o);
   }
   __syncthreads();
   if (*s_abort) return;
@@ -221,6 +223,7 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                    : "memory");
     }
     fence_proxy_async();
+    if (lt == 0) bulk_wait_read();   // the previous tile's store has left the staging tile
     asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(kPairGroupThreads) : "memory");
     if (lt == 0) {
       tc_fence_after();
@@ -239,8 +242,8 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     mbar_wait(bar_o, phase, p.status, s_abort, 128);
     tc_fence_after();
     __syncwarp();
-    {   // O_part: TMEM -> bf16 -> staging tile (256-byte rows, 16-byte chunks XOR row)
-      const uint32_t stage_row = smem_u32(sStage) + row * 256;
+    {   // O_part: TMEM -> bf16 -> staging tile: one slab of 128-byte rows per 64 columns, 16-byte
+        // chunks XOR row, the layout of a 128B-swizzled TMA box
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) {
         const int c0 = half * (D / 2) + cc * 32;
@@ -250,7 +253,9 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
           const uint32_t chunk = (uint32_t)((c0 >> 3) + v4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((chunk ^ (row & 15)) << 4)),
+          const uint32_t dst = smem_u32(sStage) + (chunk >> 3) * (kRows * 128) + row * 128 +
+                               (((chunk & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
                        "r"(pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1]))),
                        "r"(pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3]))),
                        "r"(pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5]))),
@@ -259,9 +264,18 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         }
       }
     }
+    fence_proxy_async();
     tc_fence_before();
     asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(kPairGroupThreads) : "memory");
-    {   // whole rows out
+    if ((i + 1) * p.nq <= n_q) {
+      // a full tile: its pairs are consecutive rows of the partial buffer, one TMA store per slab
+      if (lt == 0) {
+#pragma unroll
+        for (int sl = 0; sl < kSlabs; ++sl)
+          tma_store_5d(&tm_o, sStage + sl * (kRows * 128), sl * 64, 0, 0, pair_base + i * p.nq, 0);
+        bulk_commit();
+      }
+    } else {   // the ragged last tile: whole rows out by hand
       constexpr int kChunks = D / 8;
       constexpr int kRowsPerPass = kPairGroupThreads / kChunks;
       const int c = lt % kChunks;
@@ -269,7 +283,8 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
         const uint32_t pr = s_prow[r];
         if (pr != 0xffffffffu) {
-          const uint4 v = *reinterpret_cast<const uint4*>(sStage + r * 256 + ((c ^ (r & 15)) << 4));
+          const uint4 v = *reinterpret_cast<const uint4*>(sStage + (c >> 3) * (kRows * 128) + r * 128 +
+                                                          (((c & 7) ^ (r & 7)) << 4));
           *reinterpret_cast<uint4*>(p.o_part + (size_t)pr * D + c * 8) = v;
         }
       }
@@ -277,6 +292,7 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     tc_fence_before();
     t_cur = t_nxt; t_nxt = t_nn;
   }
+  if (lt == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
   if (tid < 32) tmem_dealloc(tmem, kTmemCols);
@@ -466,6 +482,8 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   rc = make_map(&tm_k, a.k, a.D, a.T, a.B * a.Hkv, kKeys, 1);
   if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.T, a.B * a.Hkv, kKeys, 1);
   if (rc == NSA_OK) rc = make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
+  CUtensorMap tm_o;
+  if (rc == NSA_OK) rc = make_map_partial(&tm_o, p.o_part, a.D, G, 1, pl.cap_pairs ? pl.cap_pairs : 1, 1, pl.nq);
   if (rc != NSA_OK) return rc;
   const size_t smem = pair_smem_bytes(a.D);
   dim3 grid(pl.n_ktiles, a.B * a.Hkv);
@@ -473,14 +491,14 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   const unsigned cgrid = (unsigned)((nthreads + 255) / 256);
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, p); }
+    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p); }
     { KernelScope ks("sel_combine_kernel", st);
       sel_combine_kernel<128><<<cgrid, 256, 0, st>>>(p.o_part, p.ml, pair_of_slot, offsets, stats,
                                                     (__nv_bfloat16*)a.o, a.lse, a.B, a.Hq, a.Hkv, a.T, G,
                                                     a.S, pl.n_ktiles, nq_union, p.force); }
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, p); }
+    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p); }
     { KernelScope ks("sel_combine_kernel", st);
       sel_combine_kernel<64><<<cgrid, 256, 0, st>>>(p.o_part, p.ml, pair_of_slot, offsets, stats,
                                                    (__nv_bfloat16*)a.o, a.lse, a.B, a.Hq, a.Hkv, a.T, G,
