@@ -36,6 +36,13 @@ WORKLOADS = {
     "tiny": dict(B=1, T=2048, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
 }
 METRIC = "NSA fwd+bwd tokens/s per B200 at T=32K bf16; % of tensor-pipe peak"
+
+# DRAM bytes (read + write) per launch at c4_t32k, one-pass ncu capture
+# (profiles/dram_traffic_pair_kernels_c4_t32k.md)
+TRAFFIC_C4 = {"tc_bwd_slc": 32.90e9, "tc_bwd_win": 13.93e9, "tc_bwd_cmp": 15.08e9,
+              "tc_fwd_slc_pairs": 24.13e9, "sel_combine_kernel": 18.80e9,
+              "dq_reduce_slc": 18.00e9, "dq_reduce_win": 10.63e9, "dq_reduce_cmp": 5.88e9}
+
 NAMES = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
 COMP = ["k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj"]
 
@@ -326,8 +333,11 @@ def main():
     tokens = world * w["B"] * w["T"] * args.steps
     pk = peaks()
     # ---- roofline of the dominant kernel ---------------------------------------------------
-    # algorithmic FLOPs: 4*D per attended (query head, key) pair forward (QK^T and PV),
-    # backward 2.5x that (recomputed S, dP, dV, dK, dQ); masked or padded MMA work not counted.
+    # Contractions (tc_* / simt_* attention kernels): bound = tensor pipe, achieved = algorithmic
+    # FLOPs per launch / measured launch time.  Algorithmic FLOPs: 4*D per attended (query head,
+    # key) pair forward (QK^T and PV), backward 2.5x that (recomputed S, dP, dV, dK, dQ); masked
+    # or padded MMA work is not counted.  Streaming kernels: bound = HBM, achieved = the bytes
+    # the kernel has to move once (its inputs and outputs) / launch time.
     pairs = {k: v * G for k, v in counts.items()}
     D = w["D"]
     flop_tab = {}
@@ -337,32 +347,45 @@ def main():
         flop_tab["simt_fwd_" + br] = 4 * D * pairs[br]
         flop_tab["simt_bwd_" + br] = 10 * D * pairs[br]
     flop_tab["tc_fwd_slc_pairs"] = 4 * D * pairs["slc"]
+    B_, T_, Hq_, Hkv_, S_ = w["B"], w["T"], w["Hq"], w["Hkv"], w["n_sel"]
+    tt = torch.arange(T_, device=idx.device).view(1, 1, T_, 1)
+    n_pairs = int(((idx >= 0) & (idx.long() * w["block_size"] <= tt)).sum().item())   # (query, block) pairs
+    full = B_ * Hq_ * T_ * D * 2                           # one [B,Hq,T,D] bf16 tensor
+    row = G * D * 2                                        # the G head rows of one query
+    t1 = torch.arange(T_)
+    win_slots = int(((t1 >> 6) - (torch.clamp(t1 - w["window"] + 1, min=0) >> 6) + 1).sum().item())
+    cmp_slots = int(((torch.clamp((t1 + 1) // w["block_size"], max=T_ // w["block_size"]) + 63) // 64).sum().item())
+    bytes_tab = {
+        "sel_combine_kernel": n_pairs * (row + G * 12) + B_ * Hkv_ * T_ * S_ * 4 + full + B_ * Hq_ * T_ * 4,
+        "dq_reduce_slc": n_pairs * row + B_ * Hkv_ * T_ * S_ * 4 + full,
+        "dq_reduce_win": B_ * Hkv_ * win_slots * row + full,
+        "dq_reduce_cmp": B_ * Hkv_ * cmp_slots * row + full,
+        "gate_fwd_kernel": 4 * full, "gate_bwd_rows_kernel": 4 * full, "sum3_kernel": 4 * full,
+    }
     # DRAM bytes per launch from the one-pass ncu capture of this workload
     # (profiles/dram_traffic_pair_kernels_c4_t32k.md); other workloads: not captured
-    traffic_tab = {"tc_bwd_slc": 33.47e9, "tc_bwd_win": 14.06e9, "tc_bwd_cmp": 15.03e9,
-                   "tc_fwd_slc_pairs": 24.10e9, "sel_combine_kernel": 18.81e9,
-                   "dq_reduce_slc": 18.00e9, "dq_reduce_win": 10.63e9, "dq_reduce_cmp": 5.88e9} \
-        if args.workload == "c4_t32k" else {}
+    traffic_tab = TRAFFIC_C4 if args.workload == "c4_t32k" else {}
     total_ms = sum(v[1] for v in prof.values()) or 1.0
     top = max(prof.items(), key=lambda kv: kv[1][1]) if prof else (None, (0, 0.0))
     roof = None
     if top[0] is not None:
         name, (cnt, tms) = top
-        per_launch_ms = tms / max(cnt, 1)
-        tf = flop_tab[name] / (per_launch_ms * 1e-3) / 1e12 if name in flop_tab else None
-        gb = traffic_tab[name] / (per_launch_ms * 1e-3) / 1e9 if name in traffic_tab else None
-        tensor_frac = tf / pk["tflops"] if tf is not None else None
-        dram_frac = gb / pk["hbm"] if gb is not None else None
-        # the bound reported is the one the kernel sits closer to
-        use_hbm = dram_frac is not None and (tensor_frac is None or dram_frac >= tensor_frac)
-        roof = {"kernel": name, "bound": "hbm" if use_hbm else "tensor",
-                "achieved": gb if use_hbm else tf, "peak": pk["hbm"] if use_hbm else pk["tflops"],
-                "unit": "GB/s" if use_hbm else "TFLOP/s",
-                "frac": dram_frac if use_hbm else tensor_frac,
-                "traffic": traffic_tab.get(name),
-                "peak_source": pk["source"] + (" (copy bandwidth)" if use_hbm else " (sustained bf16 GEMM)"),
-                "tensor_tflops": tf, "tensor_frac": tensor_frac, "dram_gbs": gb, "dram_frac": dram_frac,
-                "launch_ms": per_launch_ms, "share_of_kernel_time": tms / total_ms}
+        sec = tms / max(cnt, 1) * 1e-3
+        traffic = traffic_tab.get(name)
+        if name in flop_tab:
+            ach = flop_tab[name] / sec / 1e12
+            roof = {"kernel": name, "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
+                    "unit": "TFLOP/s", "frac": ach / pk["tflops"],
+                    "peak_source": pk["source"] + " (sustained bf16 GEMM)"}
+        else:
+            ach = bytes_tab[name] / sec / 1e9 if name in bytes_tab else None
+            roof = {"kernel": name, "bound": "hbm", "achieved": ach, "peak": pk["hbm"], "unit": "GB/s",
+                    "frac": ach / pk["hbm"] if ach is not None else None,
+                    "peak_source": pk["source"] + " (copy bandwidth)"}
+        roof.update({"traffic": traffic,
+                     "dram_gbs": traffic / sec / 1e9 if traffic else None,
+                     "dram_frac_of_copy_peak": traffic / sec / 1e9 / pk["hbm"] if traffic else None,
+                     "launch_ms": sec * 1e3, "share_of_kernel_time": tms / total_ms})
     total_flops = 14 * D * sum(pairs.values())
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,

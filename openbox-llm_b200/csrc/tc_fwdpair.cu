@@ -91,7 +91,6 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   const int b = bh / p.Hkv, hkv = bh % p.Hkv;
   const int key0 = j * kKeys;
   const int ql = row / p.G, g = row % p.G;
-  const int head = hkv * p.G + g;
   const bool row_slot_ok = ql < p.nq;
 
   if (!prefer_pairs(p.stats, p.offsets, p.B * p.Hkv, p.n_ktiles, p.nq_union, p.force)) return;

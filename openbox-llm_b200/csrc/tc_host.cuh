@@ -14,7 +14,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static inline EncodeTiledFn encode_fn() {
-  static inline EncodeTiledFn fn = nullptr;
+  static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;

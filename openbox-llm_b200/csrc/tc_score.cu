@@ -4,10 +4,11 @@
 // Same row tile as the forward kernel: 128 rows = nq queries x Gp heads of one (batch, kv head).
 // For every 64-summary tile: S = Q Kc^T by tcgen05.mma; the thread that owns a row turns it
 // into compression-branch probabilities p = exp2(s*scale*log2e - lse*log2e) with the LSE the
-// compression forward stored; the probabilities go to shared memory, are summed over the Gp
-// heads of each query (ascending head order, fp32) and each warp keeps, for its queries, the
-// running top-n list in registers (lane k holds rank k), ordered by (importance descending,
-// block index ascending).  Slots with no causally valid block are -1.
+// compression forward stored; the probabilities go to shared memory and are summed over the Gp
+// heads of each query (ascending head order, fp32).  The 128 threads are dealt out 128 / nq per
+// query; each keeps in registers the best 16 of the candidates it scanned, ordered by
+// (importance descending, block index ascending), and a tournament over the lists' heads writes
+// the query's top-n at the end.  Slots with no causally valid block are -1.
 #include "tc_common.cuh"
 #include "tc_host.cuh"
 
@@ -63,10 +64,8 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_s = bars + 3;
   uint32_t* s_tmem = (uint32_t*)(bars + 4);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
-  float* s_top_v = (float*)(bars + 6);               // [4 warps][32] merge scratch
-  int* s_top_i = (int*)(s_top_v + 4 * 32);
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int qtile = p.n_qtiles - 1 - (int)blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / p.Hkv, hkv = bh % p.Hkv;
