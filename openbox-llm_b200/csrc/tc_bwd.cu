@@ -37,6 +37,7 @@ struct BwdArgs {
   __nv_bfloat16* dq_part;
   float* dk_acc;               // fp32 accumulators, used when the row tiles of a key tile are split
   float* dv_acc;
+  const SelWorkHeader* work;   // selection: work items {bh, block, first row tile, chunks of the block}
   int* status;
   int split_chunk;             // row tiles per CTA when split
   int B, Hq, Hkv, T, Lk, G, nq;
@@ -137,8 +138,13 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   int* s_rowt = s_rowt_all + grp * 2 * kMaxNq;
   uint32_t* s_prow = s_prow_all + grp * 128;
 
-  const int j = blockIdx.x;                          // key tile
-  const int bh = blockIdx.y;
+  int4 item = make_int4((int)blockIdx.y, (int)blockIdx.x, 0, 1);
+  if (p.kind == 2) {                                 // selection: one work item per CTA
+    if ((int)blockIdx.x >= p.work->n_items) return;
+    item = reinterpret_cast<const int4*>(p.work + 1)[blockIdx.x];
+  }
+  const int j = item.y;                              // key tile
+  const int bh = item.x;
   const int b = bh / p.Hkv, hkv = bh % p.Hkv;
   const int key0 = j * kKeys;
   const int ql = row / p.G, g = row % p.G;
@@ -160,10 +166,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   n_q = max(n_q, 0);
   const int n_rt_all = (n_q + p.nq - 1) / p.nq;
   // gridDim.z > 1: the row tiles are split in chunks and dK / dV go through fp32 atomics
-  const int chunk = (int)gridDim.z > 1 ? p.split_chunk : n_rt_all;
-  const int rt_begin = (int)blockIdx.z * chunk;
+  const int chunk = p.kind == 2 ? kSelChunkTiles : ((int)gridDim.z > 1 ? p.split_chunk : n_rt_all);
+  const int rt_begin = p.kind == 2 ? item.z : (int)blockIdx.z * chunk;
   const int rt_end = min(n_rt_all, rt_begin + chunk);
-  const bool split = gridDim.z > 1;
+  const bool split = p.kind == 2 ? item.w > 1 : gridDim.z > 1;
 
   if (rt_end <= rt_begin) {
     if (!split && n_rt_all == 0) {   // nobody attends these keys: their gradients are zero
@@ -582,6 +588,30 @@ namespace nsa {
 namespace tc {
 #endif
 
+// Selection blocks whose row tiles were split over several work items collect dK / dV in the fp32
+// accumulators: this kernel clears the accumulator rows of those blocks before the backward
+// kernel (finalize = 0) and turns them into the bf16 outputs after it (finalize = 1).
+__global__ void sel_split_blocks_kernel(const int32_t* __restrict__ offsets, float* __restrict__ dk_acc,
+                                        float* __restrict__ dv_acc, __nv_bfloat16* __restrict__ dk,
+                                        __nv_bfloat16* __restrict__ dv, int n_ktiles, int nq, int Lk, int D,
+                                        int finalize) {
+  const int j = blockIdx.x, bh = blockIdx.y;
+  const int n_q = offsets[(size_t)bh * (n_ktiles + 1) + j + 1] - offsets[(size_t)bh * (n_ktiles + 1) + j];
+  const int n_rt = (n_q + nq - 1) / nq;
+  if (n_rt <= kSelChunkTiles) return;                 // one work item: written directly
+  const int rows = min(kKeys, Lk - j * kKeys);
+  const size_t base = ((size_t)bh * Lk + (size_t)j * kKeys) * D;
+  for (int i = threadIdx.x; i < rows * D; i += blockDim.x) {
+    if (finalize) {
+      dk[base + i] = __float2bfloat16_rn(dk_acc[base + i]);
+      dv[base + i] = __float2bfloat16_rn(dv_acc[base + i]);
+    } else {
+      dk_acc[base + i] = 0.f;
+      dv_acc[base + i] = 0.f;
+    }
+  }
+}
+
 static const char* const kBwdNames[3] = {"tc_bwd_win", "tc_bwd_cmp", "tc_bwd_slc"};
 static const char* const kRedNames[3] = {"dq_reduce_win", "dq_reduce_cmp", "dq_reduce_slc"};
 
@@ -589,8 +619,13 @@ struct BwdPlan {
   int n_ktiles, n_slots, nq, n_splits, split_chunk;
   size_t off_acc;
   size_t cap_pairs;          // selection: pairs the CSR may hold
-  size_t off_delta, off_part, off_csr_ws, off_qob, off_off, off_pbh, off_pos, total;
+  size_t off_delta, off_part, off_csr_ws, off_qob, off_off, off_pbh, off_pos, off_work, total;
 };
+
+size_t sel_work_max_items(size_t units, int n_ktiles, size_t cap_pairs, int nq);   // tc_fwdpair.cu
+size_t sel_work_bytes(size_t units, int n_ktiles, size_t cap_pairs, int nq);
+int sel_build_worklist(const int32_t* offsets, int n_ktiles, size_t units, size_t cap_pairs, int nq,
+                       void* work, cudaStream_t st);
 
 static BwdPlan plan_bwd(const AttnArgs& a) {
   BwdPlan pl;
@@ -618,6 +653,7 @@ static BwdPlan plan_bwd(const AttnArgs& a) {
     pl.off_pbh = off; off += align_up(pl.cap_pairs * 4, 256);
     pl.off_off = off; off += align_up(units * (pl.n_ktiles + 1) * 4, 256);
     pl.off_pos = off; off += align_up(pl.cap_pairs * 4, 256);
+    pl.off_work = off; off += align_up(sel_work_bytes(units, pl.n_ktiles, pl.cap_pairs, pl.nq), 256);
   }
   // compression: a few key tiles are attended by (almost) every query; split their row tiles
   pl.n_splits = 1;
@@ -630,6 +666,8 @@ static BwdPlan plan_bwd(const AttnArgs& a) {
     if (pl.n_splits > 1) off += 2 * align_up((size_t)a.B * a.Hkv * a.Lk * a.D * sizeof(float), 256);
     else pl.n_splits = 1;
   }
+  // selection: blocks split over several work items use the same accumulators
+  if (a.kind == 2) off += 2 * align_up((size_t)a.B * a.Hkv * a.Lk * a.D * sizeof(float), 256);
   pl.total = off;
   return pl;
 }
@@ -663,6 +701,7 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.dk = (__nv_bfloat16*)a.dk_acc;     // the API passes the dk / dv outputs through these fields
   p.dv = (__nv_bfloat16*)a.dv_acc;
   p.dq_part = (__nv_bfloat16*)(base + pl.off_part);
+  p.work = nullptr;
   p.status = device_status_ptr();
   if (!p.status) { set_error("device status word unavailable"); return NSA_ERR_CUDA; }
   p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.T = a.T; p.Lk = a.Lk; p.G = G; p.nq = pl.nq;
@@ -694,6 +733,12 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
                                 (int32_t*)(base + pl.off_pbh), pair_of_slot, base + pl.off_csr_ws,
                                 pl.off_qob - pl.off_csr_ws, st);
     if (rc != NSA_OK) return rc;
+    rc = sel_build_worklist(p.offsets, pl.n_ktiles, (size_t)a.B * a.Hkv, pl.cap_pairs, pl.nq, base + pl.off_work, st);
+    if (rc != NSA_OK) return rc;
+    p.work = (const SelWorkHeader*)(base + pl.off_work);
+    KernelScope ks("sel_split_blocks_kernel", st);
+    sel_split_blocks_kernel<<<dim3(pl.n_ktiles, a.B * a.Hkv), 256, 0, st>>>(p.offsets, p.dk_acc, p.dv_acc, p.dk, p.dv,
+                                                                        pl.n_ktiles, pl.nq, a.Lk, a.D, 0);
   }
   CUtensorMap tm_k, tm_v, tm_q, tm_do;
   int rc = make_map(&tm_k, a.k, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
@@ -710,6 +755,8 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (rc != NSA_OK) return rc;
   const size_t smem = bwd_smem_bytes(a.D);
   dim3 grid(pl.n_ktiles, a.B * a.Hkv, pl.n_splits);
+  if (a.kind == 2)
+    grid = dim3((unsigned)sel_work_max_items((size_t)a.B * a.Hkv, pl.n_ktiles, pl.cap_pairs, pl.nq));
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
@@ -720,6 +767,12 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
     tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, p);
   }
   NSA_LAUNCH_OK("tc_bwd_kernel");
+  if (a.kind == 2) {
+    KernelScope ks("sel_split_blocks_kernel", st);
+    sel_split_blocks_kernel<<<dim3(pl.n_ktiles, a.B * a.Hkv), 256, 0, st>>>(p.offsets, p.dk_acc, p.dv_acc, p.dk, p.dv,
+                                                                        pl.n_ktiles, pl.nq, a.Lk, a.D, 1);
+    NSA_LAUNCH_OK("sel_split_blocks_kernel");
+  }
   if (pl.n_splits > 1) {
     int rc2 = cast_f32_to(p.dk_acc, p.dk, n_kv, NSA_DTYPE_BF16, st);
     if (rc2 == NSA_OK) rc2 = cast_f32_to(p.dv_acc, p.dv, n_kv, NSA_DTYPE_BF16, st);

@@ -70,6 +70,14 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* s
   }
 }
 
+// ---- selection work list -----------------------------------------------------------------------
+// The block-outer selection kernels take one work item per CTA: a 64-token block of one
+// (batch, kv head) and a chunk of at most kSelChunkTiles of its row tiles.  A block that many
+// queries list (an attention-sink block, a forced initial block) becomes several items, so no
+// single CTA walks its whole query list.
+constexpr int kSelChunkTiles = 128;
+struct SelWorkHeader { int n_items; int pad[63]; };   // 256 bytes in front of the int4 items
+
 // ---- TMA -------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0,
                                             int c1, int c2) {

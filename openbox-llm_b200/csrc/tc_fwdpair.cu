@@ -23,6 +23,7 @@ struct PairArgs {
   __nv_bfloat16* o_part;         // [pairs, G, D]
   float* ml;                     // [pairs, G, 3]: m, sum of p over columns 0..31, over 32..63
   const unsigned long long* stats;
+  const SelWorkHeader* work;     // n_items, then int4 items {bh, block, first row tile, chunks of the block}
   int* status;
   int force;                     // 0: device-side choice, 1: query-outer kernel, 2: this kernel
   int B, Hq, Hkv, T, G, nq, n_ktiles, nq_union;
@@ -87,17 +88,19 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   uint32_t* s_prow = s_prow_all + grp * 128;
   float* s_max = s_max_all + grp * 256;
 
-  const int j = blockIdx.x, bh = blockIdx.y;
+  if (!prefer_pairs(p.stats, p.offsets, p.B * p.Hkv, p.n_ktiles, p.nq_union, p.force)) return;
+  if ((int)blockIdx.x >= p.work->n_items) return;
+  const int4 item = reinterpret_cast<const int4*>(p.work + 1)[blockIdx.x];
+  const int bh = item.x, j = item.y;
   const int b = bh / p.Hkv, hkv = bh % p.Hkv;
   const int key0 = j * kKeys;
   const int ql = row / p.G, g = row % p.G;
   const bool row_slot_ok = ql < p.nq;
 
-  if (!prefer_pairs(p.stats, p.offsets, p.B * p.Hkv, p.n_ktiles, p.nq_union, p.force)) return;
   const int pair_base = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j);
   const int n_q = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j + 1) - pair_base;
-  const int n_rt = (n_q + p.nq - 1) / p.nq;
-  if (n_rt <= 0) return;
+  const int n_rt = min((n_q + p.nq - 1) / p.nq, item.z + kSelChunkTiles);   // end of this item's chunk
+  if (n_rt <= item.z) return;
 
   if (tid == 0) {
     *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
@@ -157,7 +160,7 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
   };
 
-  int i = grp;
+  int i = item.z + grp;
   int t_cur = i < n_rt ? row_query(i) : -1;
   int t_nxt = i + 2 < n_rt ? row_query(i + 2) : -1;
   int buf = 0;
@@ -395,10 +398,47 @@ __global__ void sel_stats_kernel(const int32_t* __restrict__ block_idx, unsigned
   if (lane == 0 && cnt) atomicAdd(stats, (unsigned long long)cnt);
 }
 
+// one thread per (batch, kv head, block): its row tiles in chunks of kSelChunkTiles, one work
+// item each (at least one, so that a block nobody lists still gets its zero gradients)
+__global__ void sel_worklist_kernel(const int32_t* __restrict__ offsets, int n_ktiles, int units, int nq,
+                                    SelWorkHeader* __restrict__ work, int max_items) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= units * n_ktiles) return;
+  const int bh = idx / n_ktiles, j = idx % n_ktiles;
+  const int n_q = offsets[(size_t)bh * (n_ktiles + 1) + j + 1] - offsets[(size_t)bh * (n_ktiles + 1) + j];
+  const int n_rt = (n_q + nq - 1) / nq;
+  const int n_chunks = max(1, (n_rt + kSelChunkTiles - 1) / kSelChunkTiles);
+  const int base = atomicAdd(&work->n_items, n_chunks);
+  int4* items = reinterpret_cast<int4*>(work + 1);
+  for (int c = 0; c < n_chunks && base + c < max_items; ++c)
+    items[base + c] = make_int4(bh, j, c * kSelChunkTiles, n_chunks);
+}
+
+size_t sel_work_max_items(size_t units, int n_ktiles, size_t cap_pairs, int nq) {
+  // sum over blocks of max(1, ceil(ceil(n_q / nq) / chunk)) <= blocks * (1 + 1/chunk) + pairs / (chunk * nq)
+  const size_t blocks = units * n_ktiles;
+  return blocks + blocks / kSelChunkTiles + cap_pairs / ((size_t)kSelChunkTiles * nq) + 2;
+}
+size_t sel_work_bytes(size_t units, int n_ktiles, size_t cap_pairs, int nq) {
+  return sizeof(SelWorkHeader) + sel_work_max_items(units, n_ktiles, cap_pairs, nq) * sizeof(int4);
+}
+int sel_build_worklist(const int32_t* offsets, int n_ktiles, size_t units, size_t cap_pairs, int nq,
+                       void* work, cudaStream_t st) {
+  NSA_CUDA_OK(cudaMemsetAsync(work, 0, sizeof(SelWorkHeader), st));
+  const size_t n = units * n_ktiles;
+  if (n == 0) return NSA_OK;
+  KernelScope ks("sel_worklist_kernel", st);
+  sel_worklist_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+      offsets, n_ktiles, (int)units, nq, (SelWorkHeader*)work,
+      (int)sel_work_max_items(units, n_ktiles, cap_pairs, nq));
+  NSA_LAUNCH_OK("sel_worklist_kernel");
+  return NSA_OK;
+}
+
 struct PairPlan {
   int n_ktiles, nq;
   size_t cap_pairs;
-  size_t off_stats, off_part, off_ml, off_csr_ws, off_qob, off_off, off_pbh, off_pos, total;
+  size_t off_stats, off_part, off_ml, off_csr_ws, off_qob, off_off, off_pbh, off_pos, off_work, total;
 };
 
 static PairPlan plan_pairs(const AttnArgs& a) {
@@ -417,6 +457,7 @@ static PairPlan plan_pairs(const AttnArgs& a) {
   pl.off_pbh = off; off += align_up(pl.cap_pairs * 4, 256);
   pl.off_off = off; off += align_up(units * (pl.n_ktiles + 1) * 4, 256);
   pl.off_pos = off; off += align_up(pl.cap_pairs * 4, 256);
+  pl.off_work = off; off += align_up(sel_work_bytes(units, pl.n_ktiles, pl.cap_pairs, pl.nq), 256);
   pl.total = off;
   return pl;
 }
@@ -461,6 +502,8 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
                               (int32_t*)(base + pl.off_qob), offsets, (int32_t*)(base + pl.off_pbh),
                               pair_of_slot, base + pl.off_csr_ws, pl.off_qob - pl.off_csr_ws, st);
   if (rc != NSA_OK) return rc;
+  rc = sel_build_worklist(offsets, pl.n_ktiles, (size_t)a.B * a.Hkv, pl.cap_pairs, pl.nq, base + pl.off_work, st);
+  if (rc != NSA_OK) return rc;
   const int force = get_option_sel_fwd();
   rc = tc_fwd_union_launch(a, stats, offsets, force, st);
   if (rc != NSA_OK) return rc;
@@ -472,6 +515,7 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.o_part = (__nv_bfloat16*)(base + pl.off_part);
   p.ml = (float*)(base + pl.off_ml);
   p.stats = stats;
+  p.work = (const SelWorkHeader*)(base + pl.off_work);
   p.status = device_status_ptr();
   if (!p.status) { set_error("device status word unavailable"); return NSA_ERR_CUDA; }
   p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.T = a.T; p.G = G; p.nq = pl.nq;
@@ -485,7 +529,7 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (rc == NSA_OK) rc = make_map_partial(&tm_o, p.o_part, a.D, G, 1, pl.cap_pairs ? pl.cap_pairs : 1, 1, pl.nq);
   if (rc != NSA_OK) return rc;
   const size_t smem = pair_smem_bytes(a.D);
-  dim3 grid(pl.n_ktiles, a.B * a.Hkv);
+  const dim3 grid((unsigned)sel_work_max_items((size_t)a.B * a.Hkv, pl.n_ktiles, pl.cap_pairs, pl.nq));
   const size_t nthreads = (size_t)a.B * a.Hkv * a.T * G * (a.D / 8);
   const unsigned cgrid = (unsigned)((nthreads + 255) / 256);
   if (a.D == 128) {

@@ -484,6 +484,30 @@ def make_block_idx_recent(B, Hkv, T, block_size, S):
     return blk[None, None].expand(B, Hkv, T, S).contiguous().to(torch.int32)
 
 
+def make_block_idx_forced(B, Hkv, T, block_size, S, n_init=1, n_local=2, seed=0):
+    """Block lists of the published NSA recipe's shape: the first n_init blocks and the n_local
+    most recent blocks (the one holding t and the ones before it) in every query's list, the
+    remaining slots random causally valid blocks; no duplicates, -1 padded.  Not a reference
+    generator (the reference has no forced blocks): it makes block 0 a block that every
+    query lists, the case the work-list split of the block-outer kernels exists for."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    n_blk = (T + block_size - 1) // block_size
+    t = torch.arange(T)
+    cur = t // block_size
+    j = torch.arange(n_blk)
+    score = torch.rand(B, Hkv, T, n_blk, generator=g)
+    forced = (j[None, :] < n_init) | ((j[None, :] <= cur[:, None]) & (j[None, :] > cur[:, None] - n_local))
+    valid = j[None, :] <= cur[:, None]
+    score = torch.where(forced[None, None], score + 2.0, score)
+    score = score.masked_fill(~valid[None, None], -1.0)
+    k = min(S, n_blk)
+    topv, topi = score.topk(k, dim=-1)
+    sel = torch.where(topv >= 0, topi.to(torch.int32), torch.full_like(topi, -1, dtype=torch.int32))
+    idx = torch.full((B, Hkv, T, S), -1, dtype=torch.int32)
+    idx[..., :k] = sel
+    return idx
+
+
 def attended_keys(block_idx, T, block_size, window, n_cmp_keys=None):
     """Exact count of (query, key) pairs each branch attends, per kv head summed
     over batch: used for the algorithmic FLOP figure 4*D*N (forward) and

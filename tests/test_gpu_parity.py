@@ -104,6 +104,39 @@ def test_selection_forward_variants(c):
     assert nsa.lib().nsa_device_status(None) == 0
 
 
+def test_selection_block_listed_by_every_query():
+    """Block 0 and the two local blocks sit in every query's list (the published NSA recipe):
+    block 0 collects one pair per query, more than one work item holds, so its row tiles are
+    split over several CTAs and its dK / dV meet in the fp32 accumulators."""
+    nsa = pkg()
+    dtype = torch.bfloat16
+    B, Hq, Hkv, T, D, bs, S = 1, 8, 1, 4608, 64, 64, 8
+    if not nsa.tc_supported(B, Hq, Hkv, T, D, dtype, bs):
+        pytest.skip("no tcgen05 path for this shape")
+    g = torch.Generator().manual_seed(21)
+    q, do = (torch.randn(B, Hq, T, D, generator=g).to(dtype).float() for _ in range(2))
+    k, v = (torch.randn(B, Hkv, T, D, generator=g).to(dtype).float() for _ in range(2))
+    idx = O.make_block_idx_forced(B, Hkv, T, bs, S, seed=4)
+    assert (idx == 0).any(-1).all()                       # every query lists block 0
+    keep_fn = O.selection_keep_fn(idx, T, bs)
+    o_ref, lse_ref = O.stream_attn_forward(q, k, v, keep_fn)
+    dq_ref, dk_ref, dv_ref = O.stream_attn_backward(q, k, v, o_ref, lse_ref, do, keep_fn)
+    nsa.set_impl("tc")
+    q_d, k_d, v_d, do_d = (dev(x, dtype) for x in (q, k, v, do))
+    for variant in (2, 0):
+        nsa.set_option("sel_fwd_variant", variant)
+        o, lse = nsa.selection_forward_triton(q_d, k_d, v_d, idx.cuda(), bs, return_lse=True)
+        check(o, o_ref, dtype, f"variant{variant} o")
+        assert (lse.cpu() - lse_ref).abs().max().item() <= 2e-2
+    nsa.set_option("sel_fwd_variant", 0)
+    dq, dk, dv = nsa.ops._selection_backward(q_d, k_d, v_d, idx.cuda(), bs, do_d, o, lse)
+    check(dq, dq_ref, dtype, "dq")
+    check(dk, dk_ref, dtype, "dk")
+    check(dv, dv_ref, dtype, "dv")
+    assert nsa.lib().nsa_device_status(None) == 0
+    nsa.set_impl("auto")
+
+
 @pytest.mark.parametrize("c,dtype", ALL, ids=IDS)
 def test_fused_three_branch(c, dtype):
     """nsa_fused_forward and all its input gradients (test_kernel_fused.py)."""
