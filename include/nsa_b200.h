@@ -152,6 +152,16 @@ int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp, int3
                     float* importance_out, const NsaDims* dims, int n_blk, int block_size,
                     int n_sel, int impl, void* stream);
 
+/* The same with forced blocks, as in the published NSA recipe ("always the initial block and the
+ * local blocks"); no counterpart in the reference, whose scorer has none (nsa_model.py:257-258
+ * takes a plain topk).  For query t, cur = t / block_size: the blocks j < n_init (with j <= cur)
+ * come first in ascending order, then the n_local most recent blocks cur, cur-1, ... (the block
+ * holding t is attended causally by the selection kernels), then the remaining slots by
+ * importance as above.  n_init = n_local = 0 is nsa_topn_blocks. */
+int nsa_topn_blocks_forced(const void* q, const void* k_cmp, const float* lse_cmp, int32_t* block_idx,
+                           float* importance_out, const NsaDims* dims, int n_blk, int block_size,
+                           int n_sel, int n_init, int n_local, int impl, void* stream);
+
 /* ---- gate combine ---------------------------------------------------------------------------
  * Replaces the sigmoid blend nsa_model.py:366-368 / nsa_fused_kernel.py:572-573 and its
  * autograd backward: out = sum_i sigmoid(gate[...,i]) * o_i; d_gate is float32-accumulated

@@ -398,11 +398,12 @@ __global__ void __launch_bounds__(128) topn_kernel(const T* __restrict__ q, cons
                                                    const float* __restrict__ lse,
                                                    int32_t* __restrict__ block_idx,
                                                    float* __restrict__ imp_out, int B, int Hq, int Hkv,
-                                                   int T_, int n_blk, int bs, int n_sel, float scale) {
+                                                   int T_, int n_blk, int bs, int n_sel, int n_init,
+                                                   int n_local, float scale) {
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* qs = sm + (size_t)warp * (D + n_blk);   // [D]
-  float* imp = qs + D;                           // [n_blk]
+  float* qs = sm + (size_t)warp * (D + n_blk + 1);   // [D]
+  float* imp = qs + D;                               // [n_blk + 1]: a ragged tail block can be forced
   const size_t total = (size_t)B * Hkv * T_;
   const size_t unit = (size_t)blockIdx.x * 4 + warp;
   if (unit >= total) return;
@@ -451,10 +452,24 @@ __global__ void __launch_bounds__(128) topn_kernel(const T* __restrict__ q, cons
     for (int j = lane; j < n_blk; j += 32) dst[j] = j < n_valid ? imp[j] : 0.f;
   }
   int32_t* out = block_idx + unit * n_sel;
+  // forced blocks: the first n_init blocks and the n_local most recent ones (the block holding
+  // t included) rank ahead of every importance (<= G); other incomplete blocks do not compete
+  int n_cand = n_valid;
+  if (n_init > 0 || n_local > 0) {
+    const int cur = t / bs;
+    __syncwarp();
+    for (int j = lane; j <= cur; j += 32) {
+      if (j < n_init) imp[j] = kForcedInit - (float)j;
+      else if (j > cur - n_local) imp[j] = kForcedLocal - (float)(cur - j);
+      else if (j >= n_valid) imp[j] = -1.f;
+    }
+    n_cand = cur + 1;
+    __syncwarp();
+  }
   for (int s = 0; s < n_sel; ++s) {
     float best = -1.f;
     int bj = 0x7fffffff;
-    for (int j = lane; j < n_valid; j += 32) {
+    for (int j = lane; j < n_cand; j += 32) {
       const float v = imp[j];
       if (v > best) { best = v; bj = j; }        // ascending j: first maximum wins
     }
@@ -875,13 +890,22 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
 namespace nsa {
 bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel);
 int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_idx, float* imp_out,
-            const NsaDims& d, int n_blk, int block_size, int n_sel, cudaStream_t st);
+            const NsaDims& d, int n_blk, int block_size, int n_sel, int n_init, int n_local, cudaStream_t st);
 }
 
 extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp,
                                int32_t* block_idx, float* importance_out, const NsaDims* dims,
                                int n_blk, int block_size, int n_sel, int impl, void* stream) {
+  return nsa_topn_blocks_forced(q, k_cmp, lse_cmp, block_idx, importance_out, dims, n_blk, block_size,
+                                n_sel, 0, 0, impl, stream);
+}
+
+extern "C" int nsa_topn_blocks_forced(const void* q, const void* k_cmp, const float* lse_cmp,
+                                      int32_t* block_idx, float* importance_out, const NsaDims* dims,
+                                      int n_blk, int block_size, int n_sel, int n_init, int n_local,
+                                      int impl, void* stream) {
   NSA_CHECK_ARG(dims && q && lse_cmp && block_idx && (k_cmp || n_blk == 0), "null argument");
+  NSA_CHECK_ARG(n_init >= 0 && n_local >= 0 && n_init < (1 << 18) && n_local < (1 << 18), "bad forced block counts");
   NSA_CHECK_ARG(dims->Hkv > 0 && dims->Hq % dims->Hkv == 0, "Hq must be a multiple of Hkv");
   NSA_CHECK_ARG(block_size > 0 && n_sel > 0 && n_blk >= 0, "bad block_size/n_sel/n_blk");
   const int D = dims->D;
@@ -890,13 +914,14 @@ extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* ls
   if (units == 0) return NSA_OK;
   if (impl != NSA_IMPL_SIMT) {
     if (tc_topn_ok(*dims, n_blk, n_sel))
-      return tc_topn(q, k_cmp, lse_cmp, block_idx, importance_out, *dims, n_blk, block_size, n_sel, st);
+      return tc_topn(q, k_cmp, lse_cmp, block_idx, importance_out, *dims, n_blk, block_size, n_sel, n_init,
+                     n_local, st);
     if (impl == NSA_IMPL_TC) {
       set_error("scoring shape not served by the tcgen05 kernel");
       return NSA_ERR_UNSUPPORTED;
     }
   }
-  const size_t sm = (size_t)4 * (D + n_blk) * sizeof(float);
+  const size_t sm = (size_t)4 * (D + n_blk + 1) * sizeof(float);
   NSA_CHECK_ARG(sm <= 200 * 1024, "n_blk %d too large for the scoring kernel", n_blk);
   const float scale = 1.0f / sqrtf((float)D);
   const unsigned grid = blocks_for(units, 4);
@@ -908,7 +933,7 @@ extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* ls
     KernelScope ks("topn_kernel", st);                                                          \
     topn_kernel<TT, DD><<<grid, 128, sm, st>>>((const TT*)q, (const TT*)k_cmp, lse_cmp,         \
         block_idx, importance_out, dims->B, dims->Hq, dims->Hkv, dims->T, n_blk, block_size,    \
-        n_sel, scale);                                                                          \
+        n_sel, n_init, n_local, scale);                                                         \
   } while (0)
   if (dims->dtype == NSA_DTYPE_BF16) {
     switch (D) {

@@ -9,6 +9,10 @@
 #include "../../include/nsa_b200.h"
 
 namespace nsa {
+// Rank keys of forced selection blocks: above every importance (a sum of at most G <= 128
+// probabilities), initial blocks ahead of local ones, exact in fp32 for counts below 2^18.
+constexpr float kForcedInit = 1048576.f;    // - block index
+constexpr float kForcedLocal = 524288.f;    // - distance from the block holding the query
 
 void set_error(const char* fmt, ...);
 

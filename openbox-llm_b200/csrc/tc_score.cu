@@ -20,7 +20,7 @@ struct ScoreArgs {
   int32_t* block_idx;
   float* imp_out;
   int* status;
-  int B, Hq, Hkv, T, n_blk, G, Gp, nq, block_size, n_sel, n_qtiles;
+  int B, Hq, Hkv, T, n_blk, G, Gp, nq, block_size, n_sel, n_qtiles, n_init, n_local;
   float scale_log2;
 #ifdef NSA_TRACE
   long long* trace;
@@ -87,7 +87,11 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (*s_abort) return;
 
   const int hi_last = min(p.n_blk, (t_last + 1) / p.block_size) - 1;
-  const int n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
+  int n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
+  // forced blocks (the first n_init, the n_local most recent including the block holding t)
+  // are candidates even when incomplete: the tiles reach the block holding the last query
+  const bool forcing = p.n_init > 0 || p.n_local > 0;
+  if (forcing) n_tiles = max(n_tiles, (t_last / p.block_size) / kKeys + 1);
 
   // Running top-16 lists: the 128 threads are dealt out Lq = 128 / nq per query; each keeps, in
   // registers, the best 16 of the candidates it has scanned (64 / Lq per tile), ordered by
@@ -204,12 +208,18 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // top-16 update: this thread scans its share of the query's 64 candidates
       {
         const int hq = my_t < p.T ? min(kKeys - 1, min(p.n_blk, (my_t + 1) / p.block_size) - 1 - key0) : -1;
+        const int my_cur = my_t / p.block_size;
+        const int hf = (forcing && my_t < p.T) ? min(kKeys - 1, my_cur - key0) : -1;
         for (int k = 0; k < per_lane; ++k) {
           const int c = my_sub * per_lane + k;
-          if (c > hq) break;
-          const float cv = sImp[my_q * kKeys + c];
+          if (c > max(hq, hf)) break;
+          const int cj = key0 + c;
+          float cv = c <= hq ? sImp[my_q * kKeys + c] : -1.f;
+          if (forcing) {                     // cj <= my_cur here
+            if (cj < p.n_init) cv = kForcedInit - (float)cj;
+            else if (cj > my_cur - p.n_local) cv = kForcedLocal - (float)(my_cur - cj);
+          }
           if (cv > lv[kList - 1]) {          // beats the list's last entry (empty slots hold -1)
-            const int cj = key0 + c;
 #pragma unroll
             for (int r = kList - 1; r >= 1; --r) {   // strict '>' keeps earlier (lower) indices ahead
               const bool up = cv > lv[r - 1];
@@ -264,7 +274,7 @@ bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel) {
 }
 
 int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_idx, float* imp_out,
-            const NsaDims& d, int n_blk, int block_size, int n_sel, cudaStream_t st) {
+            const NsaDims& d, int n_blk, int block_size, int n_sel, int n_init, int n_local, cudaStream_t st) {
   using namespace tc;
   ScoreArgs p;
   p.lse = lse; p.block_idx = block_idx; p.imp_out = imp_out;
@@ -272,7 +282,7 @@ int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_i
   if (!p.status) { set_error("device status word unavailable"); return NSA_ERR_CUDA; }
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.T = d.T; p.n_blk = n_blk;
   p.G = d.Hq / d.Hkv; p.Gp = group_pad(p.G); p.nq = kRows / p.Gp;
-  p.block_size = block_size; p.n_sel = n_sel;
+  p.block_size = block_size; p.n_sel = n_sel; p.n_init = n_init; p.n_local = n_local;
   p.n_qtiles = (d.T + p.nq - 1) / p.nq;
   p.scale_log2 = kLog2e / sqrtf((float)d.D);
 #ifdef NSA_TRACE

@@ -24,12 +24,14 @@ class _Compressor(nn.Module):
 
 class NSAAttentionB200(nn.Module):
     def __init__(self, d_model, n_q_heads, n_kv_heads, block_size=16, n_selected_blocks=4,
-                 window=32):
+                 window=32, n_init_blocks=0, n_local_blocks=0):
         super().__init__()
         assert n_q_heads % n_kv_heads == 0, "GQA needs n_q_heads divisible by n_kv_heads"
         self.d_model, self.Hq, self.Hkv = d_model, n_q_heads, n_kv_heads
         self.dh = d_model // n_q_heads
         self.block_size, self.n_sel, self.window = block_size, n_selected_blocks, window
+        # forced selection blocks (not in the reference module; 0, 0 reproduces it)
+        self.n_init_blocks, self.n_local_blocks = n_init_blocks, n_local_blocks
         kv_dim = self.Hkv * self.dh
         self.q_proj = nn.Linear(d_model, self.Hq * self.dh, bias=False)
         self.k_cmp = nn.Linear(d_model, kv_dim, bias=False)
@@ -58,6 +60,7 @@ class NSAAttentionB200(nn.Module):
                     k_proj=self.comp_k.proj.weight, v_intra=self.comp_v.intra_pos,
                     v_logits=self.comp_v.pool_logits, v_proj=self.comp_v.proj.weight)
         out = nsa_attention(q, *kv, gate.to(q.dtype), self.block_size, self.n_sel, self.window,
-                            block_idx=block_idx, compressor=comp)
+                            block_idx=block_idx, compressor=comp, n_init_blocks=self.n_init_blocks,
+                            n_local_blocks=self.n_local_blocks)
         out = out.transpose(1, 2).contiguous().view(B, T, self.Hq * self.dh)
         return self.out_proj(out)

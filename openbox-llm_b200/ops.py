@@ -195,18 +195,22 @@ def _compress_bwd(x, intra, logits, proj, d_out, block_size):
 
 
 @torch.no_grad()
-def topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, return_importance=False):
+def topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, return_importance=False, n_init_blocks=0,
+                n_local_blocks=0):
     """Block scoring + top-n (nsa_model.py:343-355): block_idx [B,Hkv,T,n_sel] int32, ordered by
     (importance descending, index ascending), -1 where fewer than n_sel blocks are causally
-    valid.  lse_cmp is the LSE of the compression branch for the same q, k_cmp."""
+    valid.  lse_cmp is the LSE of the compression branch for the same q, k_cmp.
+    n_init_blocks / n_local_blocks (not in the reference) put the first blocks and the most
+    recent blocks, the one holding t included, ahead of the scored ones."""
     B, Hq, T, D = q.shape
     Hkv, n_blk = k_cmp.shape[1], k_cmp.shape[2]
     q, k_cmp, lse_cmp = q.contiguous(), k_cmp.contiguous(), lse_cmp.contiguous()
     idx = torch.empty(B, Hkv, T, n_sel, device=q.device, dtype=torch.int32)
     imp = torch.empty(B, Hkv, T, n_blk, device=q.device, dtype=torch.float32) if return_importance else None
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
-    L.check(L.lib().nsa_topn_blocks(L.ptr(q), L.ptr(k_cmp), L.ptr(lse_cmp), L.ptr(idx), L.ptr(imp),
-                                    d, n_blk, int(block_size), int(n_sel), L.IMPL[_impl], L.stream()))
+    L.check(L.lib().nsa_topn_blocks_forced(L.ptr(q), L.ptr(k_cmp), L.ptr(lse_cmp), L.ptr(idx), L.ptr(imp),
+                                           d, n_blk, int(block_size), int(n_sel), int(n_init_blocks),
+                                           int(n_local_blocks), L.IMPL[_impl], L.stream()))
     return (idx, imp) if return_importance else idx
 
 
@@ -355,7 +359,7 @@ class _NSAAttention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
-                block_idx, k_intra, k_logits, k_proj, v_intra, v_logits, v_proj):
+                block_idx, forced, k_intra, k_logits, k_proj, v_intra, v_logits, v_proj):
         learned = k_intra is not None
         if learned:
             cp = [t.detach().float().contiguous() for t in
@@ -368,7 +372,8 @@ class _NSAAttention(torch.autograd.Function):
             v_cmp = _mean_pool_fwd(vc, block_size)
         o_cmp, lse_cmp = range_attn_forward(q, k_cmp, v_cmp, MODE_COMPRESS, 0, block_size)
         if block_idx is None:
-            block_idx = topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel)
+            block_idx = topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel,
+                                    n_init_blocks=forced[0], n_local_blocks=forced[1])
         else:
             block_idx = block_idx.to(torch.int32).contiguous()
         o_slc, lse_slc = selection_forward_triton(q, ks, vs, block_idx, block_size, return_lse=True)
@@ -416,21 +421,24 @@ class _NSAAttention(torch.autograd.Function):
         else:
             dkc = _mean_pool_bwd(dk_cmp, T, block_size)
             dvc = _mean_pool_bwd(dv_cmp, T, block_size)
-        return (dq, dkc, dvc, dks, dvs, dkw, dvw, d_gate.to(gate_dtype), None, None, None, None,
+        return (dq, dkc, dvc, dks, dvs, dkw, dvw, d_gate.to(gate_dtype), None, None, None, None, None,
                 *pgrads)
 
 
 def nsa_attention(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
-                  block_idx=None, compressor=None, return_block_idx=False):
+                  block_idx=None, compressor=None, return_block_idx=False, n_init_blocks=0,
+                  n_local_blocks=0):
     """Full NSA attention (pre out_proj) as one differentiable op.
 
     q [B,Hq,T,D]; kc..vw [B,Hkv,T,D]; gate_logits [B,Hq,T,3].  `compressor` is None for mean
     pooling or a dict k_intra,k_logits,k_proj,v_intra,v_logits,v_proj holding the parameters
     of the two BlockCompressor modules (nsa_model.py:180-181).  With block_idx=None the blocks
-    are picked by the scorer (nsa_model.py:343-355 semantics, deterministic tie order)."""
+    are picked by the scorer (nsa_model.py:343-355 semantics, deterministic tie order);
+    n_init_blocks / n_local_blocks force the first blocks and the most recent blocks into every
+    list ahead of the scored ones (the published NSA recipe; the reference has no such option)."""
     cp = [None] * 6
     if compressor is not None:
         cp = [compressor[n] for n in ("k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj")]
     out, idx = _NSAAttention.apply(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel,
-                                   window, block_idx, *cp)
+                                   window, block_idx, (int(n_init_blocks), int(n_local_blocks)), *cp)
     return (out, idx) if return_block_idx else out

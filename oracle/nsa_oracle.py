@@ -219,6 +219,40 @@ def canonical_topn(imp: torch.Tensor, valid: torch.Tensor, n_sel: int) -> torch.
     return out
 
 
+FORCED_INIT_KEY = float(1 << 20)     # rank keys of forced blocks: above every importance (<= G)
+FORCED_LOCAL_KEY = float(1 << 19)
+
+
+def forced_topn(imp: torch.Tensor, valid: torch.Tensor, n_sel: int, T: int, block_size: int,
+                n_init: int, n_local: int) -> torch.Tensor:
+    """canonical_topn with forced blocks, the selection rule of the published NSA recipe
+    ("always the initial block and the local blocks").  PARITY UNPINNED: the reference's
+    scorer has no forced blocks (nsa_model.py:257-258 is a plain topk), so nothing of the
+    reference checks this function; with n_init = n_local = 0 it equals canonical_topn,
+    which is pinned.  For query t with cur = t // block_size the list holds, in this order:
+    blocks j < n_init (j <= cur) ascending; blocks cur, cur-1, ... (n_local of them) not
+    already listed; then causally complete blocks by (importance descending, index
+    ascending); -1 in unused slots."""
+    B, Hkv, _, n_blk = imp.shape
+    n_all = (T + block_size - 1) // block_size
+    key = torch.full((B, Hkv, T, n_all), -1.0)
+    if n_blk:
+        key[..., :n_blk] = imp.masked_fill(~valid[None, None], -1.0)
+    cur = (torch.arange(T) // block_size)[:, None]
+    j = torch.arange(n_all)[None, :]
+    is_init = (j < n_init) & (j <= cur)
+    is_local = (j <= cur) & (j > cur - n_local) & ~is_init
+    key = torch.where(is_init[None, None], FORCED_INIT_KEY - j.float(), key)
+    key = torch.where(is_local[None, None], FORCED_LOCAL_KEY - (cur - j).float(), key)
+    k_top = min(n_sel, n_all)
+    order = torch.sort(-key, dim=-1, stable=True).indices[..., :k_top]
+    picked = torch.gather(key, -1, order)
+    out = torch.where(picked >= 0, order, torch.full_like(order, -1)).to(torch.int32)
+    if k_top < n_sel:
+        out = torch.cat([out, torch.full((B, Hkv, T, n_sel - k_top), -1, dtype=torch.int32)], dim=-1)
+    return out
+
+
 def build_block_to_query_csr(block_idx, block_size):
     """nsa_fsa.py:14-64.  Pairs (query i, block j) with j >= 0 and j*Bsz <= i,
     grouped by (b, hkv, j), queries ascending inside a group.  Returns int32

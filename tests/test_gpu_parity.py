@@ -189,6 +189,43 @@ def test_whole_op_with_scorer(c, dtype):
             assert rl <= lim or ma <= lim, f"{impl} d{k}: abs {ma:.3e} rel {rl:.3e}"
 
 
+@pytest.mark.parametrize("c", REF_CONFIGS[:4] + TC_CONFIGS[:4], ids=cfg_id)
+@pytest.mark.parametrize("forced", [(1, 2), (2, 1), (0, 3)], ids=lambda f: f"init{f[0]}local{f[1]}")
+def test_topn_blocks_forced(c, forced):
+    """Scoring with forced initial and local blocks: exactly the oracle's rule applied to the
+    kernel's own importance; with no forcing the entry point equals nsa_topn_blocks.  The
+    selection kernels then attend the forced lists (the block holding t is partly future)."""
+    nsa = pkg()
+    n_init, n_local = forced
+    for dtype in DTYPES:
+        t = make_inputs(c, dtype, seed=7, scale_qkv=False)
+        bs, S, T = c["block_size"], c["S"], c["T"]
+        n_blk = T // bs
+        k_cmp = O.ref_block_mean_pool(t["kc"], bs).to(dtype).float()
+        q_d, k_d = dev(t["q"], dtype), dev(k_cmp, dtype)
+        for impl in _impls_for(c, dtype):
+            nsa.set_impl(impl)
+            _, lse = nsa.range_attn_forward(q_d, k_d, k_d, nsa.MODE_COMPRESS, 0, bs)
+            idx, imp = nsa.topn_blocks(q_d, k_d, lse, bs, S, return_importance=True,
+                                       n_init_blocks=n_init, n_local_blocks=n_local)
+            valid = O.compress_keep(0, T, n_blk, bs)
+            want = O.forced_topn(imp.cpu(), valid, S, T, bs, n_init, n_local)
+            assert (idx.cpu() == want).all(), f"{impl}: forced list differs from the rule"
+            plain = nsa.topn_blocks(q_d, k_d, lse, bs, S)
+            assert (plain.cpu() == O.canonical_topn(imp.cpu(), valid, S)).all()
+            # every query lists block 0 (n_init >= 1) and its own block (n_local >= 1)
+            tt = torch.arange(T).view(1, 1, T, 1)
+            if n_init >= 1 and S >= 1:
+                assert (idx.cpu() == 0).any(-1).all()
+            if n_local >= 1 and S > n_init:
+                assert (idx.cpu() == tt // bs).any(-1).all()
+            o, lse_s = nsa.selection_forward_triton(q_d, dev(t["ks"], dtype), dev(t["vs"], dtype), idx, bs,
+                                                    return_lse=True)
+            o_ref, _ = O.stream_attn_forward(t["q"], t["ks"], t["vs"], O.selection_keep_fn(idx.cpu(), T, bs))
+            check(o, o_ref, dtype, f"{impl} selection on forced lists")
+    nsa.set_impl("auto")
+
+
 @pytest.mark.parametrize("c", REF_CONFIGS + TC_CONFIGS[:3], ids=cfg_id)
 def test_topn_blocks(c):
     """Scoring + top-n: exact against the kernel's own importance (value descending, index
