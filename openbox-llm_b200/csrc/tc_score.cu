@@ -264,6 +264,238 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// The same for GQA groups of 4, 8 or 16 (padded) heads, without the shared-memory round trip:
+// the rows of a tile are ordered query-major (row = query * GP + head, one TMA box from the
+// (D, heads, T) view of q), so the GP heads of a query are GP neighbouring lanes of one warp.
+// They add their probabilities by a recursive-halving exchange (GP/2, ..., 1 lanes apart), after
+// which lane g holds the importance of the tile's blocks [g * 64/GP, (g+1) * 64/GP) and scans
+// exactly those for its top-16 list.  64 KB of shared memory: three CTAs per SM.
+// ------------------------------------------------------------------------------------------
+template <int D, int GP>
+__global__ void __launch_bounds__(128, 3)
+tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const ScoreArgs p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kQBytes = kRows * 128 * kSlabs, kKBytes = kKeys * 128 * kSlabs;
+  constexpr uint32_t kTmemCols = 64;
+  constexpr uint32_t kIdescQK = idesc_bf16(128, kKeys, 0, 0);
+  constexpr int NQ = kRows / GP;       // queries per tile
+  constexpr int PER = kKeys / GP;      // blocks of a tile each lane ends up owning
+  constexpr int kList = 16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kQBytes;                        // 2 stages
+  uint64_t* bars = (uint64_t*)(sK + 2 * kKBytes);
+  uint64_t* bar_q = bars + 0;
+  uint64_t* bar_k = bars + 1;   // [2]
+  uint64_t* bar_s = bars + 3;
+  uint32_t* s_tmem = (uint32_t*)(bars + 4);
+  volatile int* s_abort = (volatile int*)(s_tmem + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int qtile = p.n_qtiles - 1 - (int)blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.Hkv, hkv = bh % p.Hkv;
+  const int t0 = qtile * NQ;
+  const int t_last = min(p.T - 1, t0 + NQ - 1);
+  const int g = tid % GP, ql = tid / GP;
+  const int t = t0 + ql;
+  const bool row_ok = (g < p.G) && (t < p.T);
+
+  if (tid == 0) {
+    *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k + 0, 1); mbar_init(bar_k + 1, 1);
+    mbar_init(bar_s, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k);
+  }
+  __syncthreads();
+  if (*s_abort) return;
+
+  const int hi_last = min(p.n_blk, (t_last + 1) / p.block_size) - 1;
+  int n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
+  const bool forcing = p.n_init > 0 || p.n_local > 0;
+  if (forcing) n_tiles = max(n_tiles, (t_last / p.block_size) / kKeys + 1);
+
+  float lv[kList];
+  int li[kList];
+#pragma unroll
+  for (int k = 0; k < kList; ++k) { lv[k] = -1.f; li[k] = -1; }
+
+  if (n_tiles > 0) {
+    if (warp == 0) {
+      tmem_alloc(s_tmem, kTmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const float lse2 = row_ok ? __ldg(p.lse + (size_t)(b * p.Hq + hkv * p.G + g) * p.T + t) * kLog2e : 0.f;
+    const int n_vis = t < p.T ? min(p.n_blk, (t + 1) / p.block_size) : 0;   // complete blocks query t sees
+    const int my_cur = t / p.block_size;
+
+    auto load_k = [&](int i) {
+      uint64_t* bar = bar_k + (i & 1);
+      mbar_expect_tx(bar, kKBytes);
+#pragma unroll
+      for (int sl = 0; sl < kSlabs; ++sl)
+        tma_load_3d(sK + (i & 1) * kKBytes + sl * (kKeys * 128), &tm_k, bar, sl * 64, i * kKeys, bh);
+    };
+    auto issue_s = [&](int i) {
+      const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), ka = desc_lo_kmajor(smem_u32(sK + (i & 1) * kKBytes));
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+        mma_ss(tmem, desc_at(qa, slab * (kRows * 128) + in), desc_at(ka, slab * (kKeys * 128) + in),
+               kIdescQK, kk > 0);
+      }
+      tc_commit(bar_s);
+    };
+    if (tid == 0) {
+      mbar_expect_tx(bar_q, kQBytes);
+#pragma unroll
+      for (int sl = 0; sl < kSlabs; ++sl)     // box: 64 columns x GP heads x NQ tokens
+        tma_load_3d(sQ + sl * (kRows * 128), &tm_q, bar_q, sl * 64, b * p.Hq + hkv * p.G, t0);
+      load_k(0);
+      if (n_tiles > 1) load_k(1);
+      mbar_wait(bar_q, 0, p.status, s_abort, 1);
+      mbar_wait(bar_k, 0, p.status, s_abort, 2);
+      tc_fence_after();
+      issue_s(0);
+    }
+
+    for (int i = 0; i < n_tiles; ++i) {
+      const int key0 = i * kKeys;
+      mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
+      tc_fence_after();
+      __syncwarp();
+      float v[64];
+      {
+        uint32_t r[64];
+        tmem_ld32(lane_base, r);
+        tmem_ld32(lane_base + 32, r + 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        const int hi = row_ok ? min(kKeys - 1, n_vis - 1 - key0) : -1;
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          v[c] = (c <= hi) ? ex2(__uint_as_float(r[c]) * p.scale_log2 - lse2) : 0.f;
+      }
+      __syncthreads();                         // every thread has read S: the next MMA may overwrite it
+      if (tid == 0) {
+        if (i + 2 < n_tiles) load_k(i + 2);    // stage i & 1 was read by the MMA that just completed
+        if (i + 1 < n_tiles) {
+          tc_fence_after();
+          mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
+          issue_s(i + 1);
+        }
+      }
+      __syncwarp();
+      // sum over the heads of the query: recursive halving, the lane with the bit set keeps the
+      // upper half of the columns
+      {
+        int width = 64;
+#pragma unroll
+        for (int o = GP / 2; o >= 1; o >>= 1) {
+          width >>= 1;
+          const bool upper = (g & o) != 0;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if (c < width) {
+              const float send = upper ? v[c] : v[c + width];
+              const float keep = upper ? v[c + width] : v[c];
+              v[c] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+          }
+        }
+      }
+      // lane g now holds blocks key0 + g * PER + k in v[k]
+      const int hq = min(kKeys - 1, n_vis - 1 - key0);                       // last complete block, tile-relative
+      const int hf = (forcing && t < p.T) ? min(kKeys - 1, my_cur - key0) : -1;
+      if (p.imp_out && t < p.T) {
+        float* out = p.imp_out + ((size_t)bh * p.T + t) * p.n_blk + key0 + g * PER;
+#pragma unroll
+        for (int k = 0; k < PER; ++k)
+          if (key0 + g * PER + k < p.n_blk) out[k] = (g * PER + k <= hq) ? v[k] : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < PER; ++k) {
+        const int c = g * PER + k;
+        const int cj = key0 + c;
+        float cv = c <= hq ? v[k] : -1.f;
+        if (forcing && c <= hf) {              // cj <= my_cur
+          if (cj < p.n_init) cv = kForcedInit - (float)cj;
+          else if (cj > my_cur - p.n_local) cv = kForcedLocal - (float)(my_cur - cj);
+        }
+        if (cv > lv[kList - 1]) {              // beats the list's last entry (empty slots hold -1)
+#pragma unroll
+          for (int r = kList - 1; r >= 1; --r) {   // strict '>' keeps earlier (lower) indices ahead
+            const bool up = cv > lv[r - 1];
+            const bool here = cv > lv[r];
+            li[r] = up ? li[r - 1] : (here ? cj : li[r]);
+            lv[r] = up ? lv[r - 1] : (here ? cv : lv[r]);
+          }
+          if (cv > lv[0]) { lv[0] = cv; li[0] = cj; }
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+  }
+
+  // ---- merge the GP lists of each query: n_sel rounds, each takes the best head ------------------
+  for (int r = 0; r < p.n_sel; ++r) {
+    float bv = lv[0];
+    int bj = li[0];
+#pragma unroll
+    for (int o = 1; o < GP; o <<= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
+      if (ov > bv || (ov == bv && oj >= 0 && (bj < 0 || oj < bj))) { bv = ov; bj = oj; }
+    }
+    if (bj >= 0 && li[0] == bj) {            // this list gave the winner: pop its head
+#pragma unroll
+      for (int k = 0; k < kList - 1; ++k) { lv[k] = lv[k + 1]; li[k] = li[k + 1]; }
+      lv[kList - 1] = -1.f;
+      li[kList - 1] = -1;
+    }
+    if (g == 0 && t < p.T) p.block_idx[((size_t)bh * p.T + t) * p.n_sel + r] = bj;
+  }
+  // importance columns no tile covered are zero
+  if (p.imp_out && t < p.T) {
+    float* out = p.imp_out + ((size_t)bh * p.T + t) * p.n_blk;
+    for (int c = n_tiles * kKeys + g; c < p.n_blk; c += GP) out[c] = 0.f;
+  }
+}
+
+__host__ inline size_t score_lanes_smem_bytes(int D) {
+  return (size_t)(kRows * 128 + 2 * kKeys * 128) * (D / 64) + 256 + 1024;
+}
+
+template <int D, int GP>
+static int launch_score_lanes(const void* q, const void* k_cmp, const NsaDims& d, int n_blk, ScoreArgs p,
+                              cudaStream_t st) {
+  p.nq = kRows / GP;
+  p.n_qtiles = (d.T + p.nq - 1) / p.nq;
+  CUtensorMap tm_q, tm_k;
+  int rc = make_map_query_rows(&tm_q, q, d.D, d.T, d.B * d.Hq, GP, p.nq);
+  if (rc == NSA_OK) rc = make_map(&tm_k, k_cmp, d.D, n_blk, d.B * d.Hkv, kKeys, 1);
+  if (rc != NSA_OK) return rc;
+  const size_t smem = score_lanes_smem_bytes(d.D);
+  NSA_CUDA_OK(cudaFuncSetAttribute(tc_score_lanes_kernel<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  KernelScope ks("tc_score_topn", st);
+  tc_score_lanes_kernel<D, GP><<<dim3(p.n_qtiles, d.B * d.Hkv), 128, smem, st>>>(tm_q, tm_k, p);
+  return NSA_OK;
+}
+
 }  // namespace tc
 
 bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel) {
@@ -288,6 +520,18 @@ int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_i
 #ifdef NSA_TRACE
   p.trace = nsa_trace_buffer();
 #endif
+  if (p.Gp == 4 || p.Gp == 8 || p.Gp == 16) {
+    int rc = NSA_ERR_UNSUPPORTED;
+    if (d.D == 128) rc = p.Gp == 4 ? launch_score_lanes<128, 4>(q, k_cmp, d, n_blk, p, st)
+                       : p.Gp == 8 ? launch_score_lanes<128, 8>(q, k_cmp, d, n_blk, p, st)
+                                   : launch_score_lanes<128, 16>(q, k_cmp, d, n_blk, p, st);
+    else rc = p.Gp == 4 ? launch_score_lanes<64, 4>(q, k_cmp, d, n_blk, p, st)
+            : p.Gp == 8 ? launch_score_lanes<64, 8>(q, k_cmp, d, n_blk, p, st)
+                        : launch_score_lanes<64, 16>(q, k_cmp, d, n_blk, p, st);
+    if (rc != NSA_OK) return rc;
+    NSA_LAUNCH_OK("tc_score_lanes_kernel");
+    return NSA_OK;
+  }
   CUtensorMap tm_q, tm_k;
   int rc = make_map(&tm_q, q, d.D, d.T, d.B * d.Hq, p.nq, p.Gp);
   if (rc == NSA_OK) rc = make_map(&tm_k, k_cmp, d.D, n_blk, d.B * d.Hkv, kKeys, 1);
