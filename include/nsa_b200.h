@@ -93,6 +93,15 @@ int nsa_selection_bwd(const void* q, const void* k, const void* v, const int32_t
                       const float* row_scale, const float* row_dot,
                       void* workspace, size_t workspace_bytes, int impl, void* stream);
 
+/* dq of the whole op in one pass (no counterpart in the reference, which adds the three branch
+ * gradients with torch).  When the tcgen05 kernels serve a backward call (nsa_tc_supported) its
+ * `dq` argument may be NULL: the branch's bf16 dQ partials then stay in the call's workspace, and
+ * this entry point adds the partials of the compression, selection and window branches of every
+ * query in fp32 and writes dq [B,Hq,T,D] once.  ws_* are the workspaces of the three backward
+ * calls (same dims; Lk_cmp, block_size, S, window as given to them); NULL = branch absent. */
+int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int block_size, int S, int window,
+                   const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq, void* stream);
+
 /* ---- block -> query CSR ---------------------------------------------------------------------
  * Replaces build_block_to_query_csr (nsa_fsa.py:14-64): pairs (query i, block j) with j >= 0
  * and j*block_size <= i, grouped by (b, hkv, j), queries ascending.  block_offsets is

@@ -55,6 +55,7 @@ SIGNATURES = {
     "nsa_topn_blocks_forced": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_gate_combine_bwd_rows": (_i, [_vp] * 8 + [_dp, _vp]),
     "nsa_sum3": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "nsa_dq_reduce3": (_i, [_dp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "nsa_gate_combine_fwd": (_i, [_vp] * 5 + [_dp, _vp]),
     "nsa_gate_combine_bwd": (_i, [_vp] * 9 + [_dp, _vp]),
 }

@@ -84,7 +84,7 @@ static bool use_tc(const NsaDims* d, int block_size, int impl, int* err) {
   if (impl == NSA_IMPL_SIMT) return false;
   const bool ok = tc_shape_ok(*d, block_size);
   if (impl == NSA_IMPL_TC && !ok) {
-    set_error("shape not served by the tcgen05 kernels (bf16, D in {64,128}, group in {1,2,4,8,16})");
+    set_error("shape not served by the tcgen05 kernels (bf16, D in {64,128}, 64-token blocks, 2 to 128 query heads per kv head)");
     *err = NSA_ERR_UNSUPPORTED;
   }
   return ok;
@@ -242,14 +242,14 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
   const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
   const size_t nkv = (size_t)dims->B * dims->Hkv * Lk * dims->D;
   if (rows == 0 || Lk == 0) {
-    if (rows) NSA_CUDA_OK(cudaMemsetAsync(dq, 0, rows * dims->D * elem_size(dims->dtype), st));
+    if (rows && dq) NSA_CUDA_OK(cudaMemsetAsync(dq, 0, rows * dims->D * elem_size(dims->dtype), st));
     if (nkv) {
       NSA_CUDA_OK(cudaMemsetAsync(dk, 0, nkv * elem_size(dims->dtype), st));
       NSA_CUDA_OK(cudaMemsetAsync(dv, 0, nkv * elem_size(dims->dtype), st));
     }
     return NSA_OK;
   }
-  NSA_CHECK_ARG(q && k && v && o && lse && d_o && dq && dk && dv, "null tensor");
+  NSA_CHECK_ARG(q && k && v && o && lse && d_o && dk && dv, "null tensor");
   AttnArgs a = base_args(dims, Lk);
   a.q = q; a.k = k; a.v = v; a.o = (void*)o; a.lse = (float*)lse; a.d_o = d_o; a.dq = dq;
   a.kind = mode; a.window = window; a.block_size = block_size;
@@ -261,6 +261,7 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
     return tc_attn_bwd(a, workspace, workspace_bytes, st);
   }
   if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(dq, "dq may be null only when the tcgen05 kernels serve the call");
   return simt_bwd(a, dims, dk, dv, workspace, workspace_bytes, st);
 }
 
@@ -324,7 +325,7 @@ extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
   cudaStream_t st = (cudaStream_t)stream;
   const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
   if (rows == 0) return NSA_OK;
-  NSA_CHECK_ARG(q && k && v && o && lse && d_o && dq && dk && dv && (S == 0 || block_idx),
+  NSA_CHECK_ARG(q && k && v && o && lse && d_o && dk && dv && (S == 0 || block_idx),
                 "null tensor");
   AttnArgs a = base_args(dims, dims->T);
   a.q = q; a.k = k; a.v = v; a.o = (void*)o; a.lse = (float*)lse; a.d_o = d_o; a.dq = dq;
@@ -337,5 +338,20 @@ extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
     return tc_attn_bwd(a, workspace, workspace_bytes, st);
   }
   if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(dq, "dq may be null only when the tcgen05 kernels serve the call");
   return simt_bwd(a, dims, dk, dv, workspace, workspace_bytes, st);
+}
+
+extern "C" int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int block_size, int S, int window,
+                              const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
+                              void* stream) {
+  int rc = check_dims(dims);
+  if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(dq, "null dq");
+  NSA_CHECK_ARG(use_tc(dims, block_size, NSA_IMPL_AUTO, &rc), "nsa_dq_reduce3 needs a shape the tcgen05 kernels serve");
+  NSA_CHECK_ARG(!ws_cmp || (Lk_cmp > 0 && block_size > 0), "bad compression geometry");
+  NSA_CHECK_ARG(!ws_slc || S > 0, "bad S");
+  NSA_CHECK_ARG(!ws_win || window >= 1, "bad window");
+  const AttnArgs a = base_args(dims, dims->T);
+  return tc_dq_reduce3(a, Lk_cmp, block_size, S, window, ws_cmp, ws_slc, ws_win, dq, (cudaStream_t)stream);
 }

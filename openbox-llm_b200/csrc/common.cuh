@@ -106,5 +106,7 @@ size_t tc_sel_fwd_workspace(const AttnArgs& a);
 int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t tc_attn_bwd_workspace(const AttnArgs& a);
 int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int block_size, int S, int window, const void* ws_cmp,
+                  const void* ws_slc, const void* ws_win, void* dq, cudaStream_t st);
 
 }  // namespace nsa

@@ -576,6 +576,83 @@ __global__ void dq_reduce_kernel(const __nv_bfloat16* __restrict__ part, const i
   *reinterpret_cast<uint4*>(dq + (((size_t)b * Hq + hkv * G + g) * T + t) * D + v * 8) = u;
 }
 
+// dq of the whole op in one pass: the partials of the compression, selection and window branches
+// of query (bh, t) are added in fp32 and rounded once.  A branch whose buffer is null is absent.
+struct Reduce3Args {
+  const __nv_bfloat16* part_cmp; int slots_cmp, Lk_cmp, block_size;
+  const __nv_bfloat16* part_slc; const int32_t* pair_of_slot; int S;
+  const __nv_bfloat16* part_win; int slots_win, window;
+  __nv_bfloat16* dq;
+  int B, Hq, Hkv, T, G;
+};
+
+template <int D>
+__global__ void dq_reduce3_kernel(const Reduce3Args a) {
+  constexpr int kVec = D / 8;
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)a.B * a.Hkv * a.T * a.G * kVec;
+  if (gid >= total) return;
+  const int v = (int)(gid % kVec);
+  const int g = (int)((gid / kVec) % a.G);
+  const int t = (int)((gid / ((size_t)kVec * a.G)) % a.T);
+  const size_t bh = gid / ((size_t)kVec * a.G * a.T);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  // four partial rows per trip: their loads are issued before the first is added
+  auto add4 = [&](const __nv_bfloat16* part, const long long (&rows)[4]) {
+    uint4 u[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      u[k] = rows[k] >= 0 ? __ldg(reinterpret_cast<const uint4*>(part + ((size_t)rows[k] * a.G + g) * D + v * 8))
+                          : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+  };
+  const long long qrow = (long long)(bh * a.T + t);
+  if (a.part_slc) {
+    const int32_t* ps = a.pair_of_slot + (size_t)qrow * a.S;
+    for (int s0 = 0; s0 < a.S; s0 += 4) {
+      long long rows[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) rows[k] = s0 + k < a.S ? (long long)__ldg(ps + s0 + k) : -1;
+      add4(a.part_slc, rows);
+    }
+  }
+  if (a.part_win) {
+    const int first = max(0, t - a.window + 1) >> 6, last = t >> 6;
+    for (int j0 = first; j0 <= last; j0 += 4) {
+      long long rows[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) rows[k] = j0 + k <= last ? qrow * a.slots_win + (j0 + k) % a.slots_win : -1;
+      add4(a.part_win, rows);
+    }
+  }
+  if (a.part_cmp) {
+    const int n_vis = min(a.Lk_cmp, (t + 1) / a.block_size);
+    const int last = n_vis > 0 ? (n_vis - 1) >> 6 : -1;
+    for (int j0 = 0; j0 <= last; j0 += 4) {
+      long long rows[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) rows[k] = j0 + k <= last ? qrow * a.slots_cmp + j0 + k : -1;
+      add4(a.part_cmp, rows);
+    }
+  }
+  const int b = (int)(bh / a.Hkv), hkv = (int)(bh % a.Hkv);
+  uint4 u;
+  u.x = pack_bf16(acc[0], acc[1]); u.y = pack_bf16(acc[2], acc[3]);
+  u.z = pack_bf16(acc[4], acc[5]); u.w = pack_bf16(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(a.dq + (((size_t)b * a.Hq + hkv * a.G + g) * a.T + t) * D + v * 8) = u;
+}
+
 #ifdef NSA_TRACE
 }  // namespace tc
 }  // namespace nsa
@@ -778,6 +855,7 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
     if (rc2 == NSA_OK) rc2 = cast_f32_to(p.dv_acc, p.dv, n_kv, NSA_DTYPE_BF16, st);
     if (rc2 != NSA_OK) return rc2;
   }
+  if (!a.dq) return NSA_OK;   // the partials stay in the workspace for tc_dq_reduce3
   const size_t nthreads = (size_t)a.B * a.Hkv * a.T * G * (a.D / 8);
   const unsigned rgrid = (unsigned)((nthreads + 255) / 256);
   {
@@ -792,6 +870,47 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
                                                  pl.n_slots, a.S);
   }
   NSA_LAUNCH_OK("dq_reduce_kernel");
+  return NSA_OK;
+}
+
+
+// dq of the whole op from the three branch workspaces (each written by tc_attn_bwd with a null
+// dq): `base` carries B, Hq, Hkv, T, D; a null workspace means the branch is absent.
+int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int block_size, int S, int window, const void* ws_cmp,
+                  const void* ws_slc, const void* ws_win, void* dq, cudaStream_t st) {
+  using namespace tc;
+  Reduce3Args r;
+  r.part_cmp = r.part_slc = r.part_win = nullptr;
+  r.pair_of_slot = nullptr;
+  r.slots_cmp = r.slots_win = 1;
+  r.Lk_cmp = Lk_cmp; r.block_size = block_size; r.S = S; r.window = window;
+  r.dq = (__nv_bfloat16*)dq;
+  r.B = base.B; r.Hq = base.Hq; r.Hkv = base.Hkv; r.T = base.T; r.G = base.Hq / base.Hkv;
+  if (ws_cmp) {
+    AttnArgs a = base; a.kind = 1; a.Lk = Lk_cmp; a.block_size = block_size;
+    const BwdPlan pl = plan_bwd(a);
+    r.part_cmp = (const __nv_bfloat16*)((const char*)ws_cmp + pl.off_part);
+    r.slots_cmp = pl.n_slots;
+  }
+  if (ws_slc) {
+    AttnArgs a = base; a.kind = 2; a.Lk = base.T; a.S = S; a.block_size = block_size;
+    const BwdPlan pl = plan_bwd(a);
+    r.part_slc = (const __nv_bfloat16*)((const char*)ws_slc + pl.off_part);
+    r.pair_of_slot = (const int32_t*)((const char*)ws_slc + pl.off_pos);
+  }
+  if (ws_win) {
+    AttnArgs a = base; a.kind = 0; a.Lk = base.T; a.window = window;
+    const BwdPlan pl = plan_bwd(a);
+    r.part_win = (const __nv_bfloat16*)((const char*)ws_win + pl.off_part);
+    r.slots_win = pl.n_slots;
+  }
+  const size_t nthreads = (size_t)r.B * r.Hkv * r.T * r.G * (base.D / 8);
+  if (nthreads == 0) return NSA_OK;
+  const unsigned grid = (unsigned)((nthreads + 255) / 256);
+  KernelScope ks("dq_reduce3", st);
+  if (base.D == 128) dq_reduce3_kernel<128><<<grid, 256, 0, st>>>(r);
+  else dq_reduce3_kernel<64><<<grid, 256, 0, st>>>(r);
+  NSA_LAUNCH_OK("dq_reduce3_kernel");
   return NSA_OK;
 }
 

@@ -68,12 +68,16 @@ def range_attn_forward(q, k, v, mode, window, block_size):
     return o, lse
 
 
-def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size, row_scale=None, row_dot=None):
+def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size, row_scale=None, row_dot=None,
+                        defer_dq=False):
     """dq, dk, dv of a range branch.  With row_scale / row_dot (see nsa_gate_combine_bwd_rows) `do`
-    is the whole op's upstream gradient and the gate factor is applied inside the kernel."""
+    is the whole op's upstream gradient and the gate factor is applied inside the kernel.
+    defer_dq (tcgen05 shapes only): returns (workspace, dk, dv), the dQ partials staying in the
+    workspace for nsa_dq_reduce3."""
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     q, k, v, o, do = (t.contiguous() for t in (q, k, v, o, do))
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq = None if defer_dq else torch.empty_like(q)
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
     nws = L.lib().nsa_range_attn_bwd_workspace_bytes(d, k.shape[2], mode, int(window), L.IMPL[_impl])
     ws = L.workspace(nws, q.device)
@@ -81,7 +85,7 @@ def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size, row_scale
                                        L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, k.shape[2],
                                        mode, int(window), int(block_size), L.ptr(row_scale),
                                        L.ptr(row_dot), L.ptr(ws), nws, L.IMPL[_impl], L.stream()))
-    return dq, dk, dv
+    return (ws if defer_dq else dq), dk, dv
 
 
 def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False):
@@ -103,13 +107,15 @@ def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False):
     return (o, lse) if return_lse else o
 
 
-def _selection_backward(q, k, v, block_idx, block_size, do, o, lse, row_scale=None, row_dot=None):
+def _selection_backward(q, k, v, block_idx, block_size, do, o, lse, row_scale=None, row_dot=None,
+                        defer_dq=False):
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     S = block_idx.shape[-1]
     assert block_size >= 16
     q, k, v, o, do = (t.contiguous() for t in (q, k, v, o, do))
     idx = block_idx.to(torch.int32).contiguous()
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq = None if defer_dq else torch.empty_like(q)
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
     nws = L.lib().nsa_selection_bwd_workspace_bytes(d, S, block_size, L.IMPL[_impl])
     ws = L.workspace(nws, q.device)
@@ -117,7 +123,7 @@ def _selection_backward(q, k, v, block_idx, block_size, do, o, lse, row_scale=No
                                       L.ptr(lse), L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, S,
                                       int(block_size), L.ptr(row_scale), L.ptr(row_dot), L.ptr(ws),
                                       nws, L.IMPL[_impl], L.stream()))
-    return dq, dk, dv
+    return (ws if defer_dq else dq), dk, dv
 
 
 def selection_backward_triton(q, k, v, block_idx, block_size, do, o):
@@ -403,15 +409,28 @@ class _NSAAttention(torch.autograd.Function):
         L.check(L.lib().nsa_gate_combine_bwd_rows(
             L.ptr(o_cmp), L.ptr(o_slc), L.ptr(o_win), L.ptr(gate), L.ptr(d_out), L.ptr(rs), L.ptr(rd),
             L.ptr(d_gate), L.dims(B, Hq, 1, T, q.shape[3], L.dtype_code(q)), L.stream()))
+        S = block_idx.shape[-1]
+        # tcgen05 shapes: the three branches leave their dQ partials in their workspaces and one
+        # kernel adds them all; otherwise three dq tensors and a sum
+        fused = (_impl != "simt" and S > 0 and q.dtype == torch.bfloat16 and
+                 tc_supported(B, Hq, ks.shape[1], T, q.shape[3], q.dtype, block_size))
         dq, dk_cmp, dv_cmp = range_attn_backward(q, k_cmp, v_cmp, o_cmp, lse_cmp, d_out,
-                                                 MODE_COMPRESS, 0, block_size, rs[0], rd[0])
+                                                 MODE_COMPRESS, 0, block_size, rs[0], rd[0],
+                                                 defer_dq=fused)
         dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
-                                            rs[1], rd[1])
+                                            rs[1], rd[1], defer_dq=fused)
         dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, d_out, MODE_WINDOW, window, 0,
-                                            rs[2], rd[2])
-        dq_sum = torch.empty_like(dq)
-        L.check(L.lib().nsa_sum3(L.ptr(dq), L.ptr(dq2), L.ptr(dq3), L.ptr(dq_sum), dq.numel(),
-                                 L.dtype_code(dq), L.stream()))
+                                            rs[2], rd[2], defer_dq=fused)
+        dq_sum = torch.empty_like(q)
+        if fused:
+            n_cmp = k_cmp.shape[2]
+            d = L.dims(B, Hq, ks.shape[1], T, q.shape[3], L.dtype_code(q))
+            L.check(L.lib().nsa_dq_reduce3(d, n_cmp, int(block_size), S, int(window),
+                                           L.ptr(dq) if n_cmp > 0 else None, L.ptr(dq2), L.ptr(dq3),
+                                           L.ptr(dq_sum), L.stream()))
+        else:
+            L.check(L.lib().nsa_sum3(L.ptr(dq), L.ptr(dq2), L.ptr(dq3), L.ptr(dq_sum), dq.numel(),
+                                     L.dtype_code(dq), L.stream()))
         dq = dq_sum
         pgrads = [None] * 6
         if learned:
