@@ -437,3 +437,29 @@ def test_headline_shape_properties():
     assert abs(lhs - rhs) <= 2e-2 * max(1.0, abs(rhs)), (lhs, rhs)
     for n in names:
         assert torch.isfinite(g[n]).all()
+
+
+def test_module_under_activation_checkpointing():
+    """The attention layer inside torch.utils.checkpoint(use_reentrant=False), as the reference's
+    blocks run it (nsa_model.py:494-497): the forward is replayed inside backward and must give
+    the same output and parameter gradients as the plain run."""
+    import importlib
+    from torch.utils.checkpoint import checkpoint
+    mod = importlib.import_module("openbox-llm_b200.module")
+    torch.manual_seed(3)
+    layer = mod.NSAAttentionB200(d_model=256, n_q_heads=4, n_kv_heads=2, block_size=64,
+                                 n_selected_blocks=4, window=128).cuda().to(torch.bfloat16)
+    x = torch.randn(2, 512, 256, device="cuda", dtype=torch.bfloat16)
+    grads = []
+    outs = []
+    for use_ckpt in (False, True):
+        layer.zero_grad(set_to_none=True)
+        xi = x.clone().requires_grad_(True)
+        y = checkpoint(layer, xi, use_reentrant=False) if use_ckpt else layer(xi)
+        y.float().square().mean().backward()
+        outs.append(y.detach().float())
+        grads.append([xi.grad.float()] + [p.grad.float() for p in layer.parameters()])
+    assert torch.equal(outs[0], outs[1])
+    for a, b in zip(*grads):
+        assert torch.allclose(a, b, rtol=0, atol=1e-6 + 1e-2 * a.abs().max().item()), (a - b).abs().max()
+    assert pkg().lib().nsa_device_status(None) == 0
