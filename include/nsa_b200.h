@@ -150,6 +150,22 @@ int nsa_block_compress_bwd(const void* x, const float* intra_pos, const float* p
                            int block_size, int dtype, void* workspace, size_t workspace_bytes,
                            void* stream);
 
+/* The same learned pooling over windows of block_size tokens every `stride` tokens
+ * (stride <= block_size; (T - block_size) / stride + 1 summaries): the compression geometry of the
+ * published NSA recipe (length 32, stride 16).  No counterpart in the reference, whose
+ * BlockCompressor is applied to a non-overlapping block view (nsa_model.py:217-220);
+ * stride == block_size is exactly nsa_block_compress_fwd / _bwd. */
+int nsa_block_compress_strided_fwd(const void* x, const float* intra_pos, const float* pool_logits,
+                                   const float* proj_w, void* out, int B, int Hkv, int T, int D,
+                                   int block_size, int stride, int dtype, void* stream);
+size_t nsa_block_compress_strided_bwd_workspace_bytes(int B, int Hkv, int T, int D, int block_size,
+                                                      int stride);
+int nsa_block_compress_strided_bwd(const void* x, const float* intra_pos, const float* pool_logits,
+                                   const float* proj_w, const void* d_out, void* dx,
+                                   float* d_intra_pos, float* d_pool_logits, float* d_proj_w, int B,
+                                   int Hkv, int T, int D, int block_size, int stride, int dtype,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- block scoring and top-n ----------------------------------------------------------------
  * Replaces the dense scoring pass of nsa_model.py:343-355: importance of block j for
  * (b, hkv, t) is the sum over the group's query heads of the compression-branch softmax

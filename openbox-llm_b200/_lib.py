@@ -51,6 +51,9 @@ SIGNATURES = {
     "nsa_block_compress_fwd": (_i, [_vp] * 5 + [_i] * 6 + [_vp]),
     "nsa_block_compress_bwd_workspace_bytes": (_sz, [_i] * 5),
     "nsa_block_compress_bwd": (_i, [_vp] * 9 + [_i] * 6 + [_vp, _sz, _vp]),
+    "nsa_block_compress_strided_fwd": (_i, [_vp] * 5 + [_i] * 7 + [_vp]),
+    "nsa_block_compress_strided_bwd_workspace_bytes": (_sz, [_i] * 6),
+    "nsa_block_compress_strided_bwd": (_i, [_vp] * 9 + [_i] * 7 + [_vp, _sz, _vp]),
     "nsa_topn_blocks": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _i, _vp]),
     "nsa_topn_blocks_forced": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_gate_combine_bwd_rows": (_i, [_vp] * 8 + [_dp, _vp]),

@@ -43,7 +43,7 @@ template <typename T>
 __global__ void compress_fwd_kernel(const T* __restrict__ x, const float* __restrict__ intra,
                                     const float* __restrict__ logits, const float* __restrict__ proj,
                                     T* __restrict__ out, float* __restrict__ pooled_out, int T_,
-                                    int D, int bs, int n_blk) {
+                                    int D, int bs, int stride, int n_blk) {
   extern __shared__ float sm[];
   float* w = sm;            // [bs]
   float* pooled = sm + bs;  // [D]
@@ -58,7 +58,7 @@ __global__ void compress_fwd_kernel(const T* __restrict__ x, const float* __rest
   for (int r = d; r < bs; r += blockDim.x) w[r] = expf(logits[r] - mx) / den;
   __syncthreads();
   const bool act = d < D;   // the CTA is padded to whole warps
-  const T* p = x + (bh * T_ + (size_t)j * bs) * D + d;
+  const T* p = x + (bh * T_ + (size_t)j * stride) * D + d;
   float s = 0.f;
   if (act) {
     for (int r = 0; r < bs; ++r) s = fmaf(w[r], to_float(p[(size_t)r * D]) + intra[r * D + d], s);
@@ -83,7 +83,7 @@ __global__ void compress_bwd_block_kernel(const T* __restrict__ x, const float* 
                                           const T* __restrict__ d_out, T* __restrict__ dx,
                                           float* __restrict__ d_pooled_out,
                                           float* __restrict__ sum_dpooled, float* __restrict__ d_w,
-                                          int T_, int D, int bs, int n_blk) {
+                                          int T_, int D, int bs, int stride, int n_blk) {
   extern __shared__ float sm[];
   float* w = sm;           // [bs]
   float* go = sm + bs;     // [D] d_out row
@@ -105,12 +105,12 @@ __global__ void compress_bwd_block_kernel(const T* __restrict__ x, const float* 
     d_pooled_out[(bh * n_blk + j) * D + d] = dp;
     atomicAdd(sum_dpooled + d, dp);
   }
-  const size_t xo = (bh * T_ + (size_t)j * bs) * D + d;
+  const size_t xo = (bh * T_ + (size_t)j * stride) * D + d;
   for (int r = 0; r < bs; ++r) {
     float xv = 0.f;
     if (act) {
       xv = to_float(x[xo + (size_t)r * D]) + intra[r * D + d];
-      dx[xo + (size_t)r * D] = from_float<T>(w[r] * dp);
+      if (stride == bs) dx[xo + (size_t)r * D] = from_float<T>(w[r] * dp);   // else: compress_dx_kernel
     }
     // reduce dp * xv over d for position r
     float part = warp_sum(dp * xv);
@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(kCompThreads)
 compress_fast_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ intra,
                          const float* __restrict__ logits, const float* __restrict__ proj,
                          __nv_bfloat16* __restrict__ out, float* __restrict__ pooled_out, int T_, int D,
-                         int bs, int n_blk, size_t rows) {
+                         int bs, int stride, int n_blk, size_t rows) {
   extern __shared__ float sm[];
   float* w = sm;
   float* cvec = w + bs;
@@ -207,7 +207,7 @@ compress_fast_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
     if (row < rows) {
       const size_t bh = row / n_blk;
       const int j = (int)(row % n_blk);
-      const __nv_bfloat16* xb = x + (bh * T_ + (size_t)j * bs) * D + vl * 8;
+      const __nv_bfloat16* xb = x + (bh * T_ + (size_t)j * stride) * D + vl * 8;
       for (int r = rg; r < bs; r += RG) {
         const uint4 u = __ldg(reinterpret_cast<const uint4*>(xb + (size_t)r * D));
         float f[8];
@@ -258,7 +258,7 @@ compress_fast_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
                          const float* __restrict__ proj, const __nv_bfloat16* __restrict__ d_out,
                          __nv_bfloat16* __restrict__ dx, float* __restrict__ d_pooled_out,
                          float* __restrict__ sum_dpooled, float* __restrict__ d_w, int T_, int D, int bs,
-                         int n_blk, size_t rows) {
+                         int stride, int n_blk, size_t rows) {
   extern __shared__ float sm[];
   float* w = sm;
   float* dw = w + bs;
@@ -302,7 +302,8 @@ compress_fast_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
     if (row >= rows) break;
     const size_t bh = row / n_blk;
     const int j = (int)(row % n_blk);
-    const size_t base = (bh * T_ + (size_t)j * bs) * D + vl * 8;
+    const size_t base = (bh * T_ + (size_t)j * stride) * D + vl * 8;
+    const bool write_dx = stride == bs;               // overlapping windows: compress_dx_kernel
     float g[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) g[e] = dp[b * D + vl * 8 + e];
@@ -317,7 +318,7 @@ compress_fast_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
         uint4 o;
         o.x = pack2(wr * g[0], wr * g[1]); o.y = pack2(wr * g[2], wr * g[3]);
         o.z = pack2(wr * g[4], wr * g[5]); o.w = pack2(wr * g[6], wr * g[7]);
-        *reinterpret_cast<uint4*>(dx + base + (size_t)r * D) = o;
+        if (write_dx) *reinterpret_cast<uint4*>(dx + base + (size_t)r * D) = o;
 #pragma unroll
         for (int e = 0; e < 8; ++e) dot = fmaf(g[e], f[e], dot);
       }
@@ -337,6 +338,27 @@ size_t compress_fast_fwd_smem(int D, int bs, bool with_proj) {
 }
 size_t compress_fast_bwd_smem(int D, int bs) {
   return (2 * (size_t)bs + 2 * kCompRows * D + (size_t)D * D) * sizeof(float);
+}
+
+// dx for overlapping windows (stride < length): token pos of (b, hkv) collects
+// w[pos - j*stride] * d_pooled[j] from every window j that holds it; tokens in no window get 0
+template <typename T>
+__global__ void compress_dx_kernel(const float* __restrict__ d_pooled, const float* __restrict__ logits,
+                                   T* __restrict__ dx, int T_, int D, int bs, int stride, int n_blk,
+                                   size_t n_elems) {
+  extern __shared__ float w[];
+  pool_weights(logits, w, bs);
+  __syncthreads();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_elems) return;
+  const int d = (int)(i % D);
+  const int pos = (int)((i / D) % T_);
+  const size_t bh = i / ((size_t)D * T_);
+  const int j_hi = min(n_blk - 1, pos / stride);
+  const int j_lo = max(0, (pos - bs + stride) / stride);   // ceil((pos - bs + 1) / stride) for pos >= bs - 1
+  float acc = 0.f;
+  for (int j = j_lo; j <= j_hi; ++j) acc = fmaf(w[pos - j * stride], d_pooled[(bh * n_blk + j) * D + d], acc);
+  dx[i] = from_float<T>(acc);
 }
 
 // tail tokens past the last complete block get zero gradient
@@ -795,11 +817,22 @@ extern "C" int nsa_block_mean_pool_bwd(const void* d_out, void* dx, int B, int H
   return NSA_OK;
 }
 
+static int n_windows(int T, int len, int stride) { return T >= len ? (T - len) / stride + 1 : 0; }
+
 extern "C" int nsa_block_compress_fwd(const void* x, const float* intra_pos, const float* pool_logits,
                                       const float* proj_w, void* out, int B, int Hkv, int T, int D,
                                       int block_size, int dtype, void* stream) {
+  return nsa_block_compress_strided_fwd(x, intra_pos, pool_logits, proj_w, out, B, Hkv, T, D, block_size,
+                                        block_size, dtype, stream);
+}
+
+extern "C" int nsa_block_compress_strided_fwd(const void* x, const float* intra_pos,
+                                              const float* pool_logits, const float* proj_w, void* out,
+                                              int B, int Hkv, int T, int D, int block_size, int stride,
+                                              int dtype, void* stream) {
   NSA_CHECK_ARG(block_size > 0 && D > 0 && D <= 1024, "bad block_size/D");
-  const int n_blk = T / block_size;
+  NSA_CHECK_ARG(stride > 0 && stride <= block_size, "stride must be in [1, block_size]");
+  const int n_blk = n_windows(T, block_size, stride);
   const size_t ctas = (size_t)B * Hkv * n_blk;
   if (ctas == 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -810,17 +843,22 @@ extern "C" int nsa_block_compress_fwd(const void* x, const float* intra_pos, con
     KernelScope ks("compress_fast_fwd_kernel", st);
     compress_fast_fwd_kernel<<<(unsigned)((ctas + kCompRows - 1) / kCompRows), kCompThreads, fsm, st>>>(
         (const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D,
-        block_size, n_blk, ctas);
+        block_size, stride, n_blk, ctas);
   } else if (dtype == NSA_DTYPE_BF16)
-    { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D, block_size, n_blk); }
+    { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)out, (float*)nullptr, T, D, block_size, stride, n_blk); }
   else
-    { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)out, (float*)nullptr, T, D, block_size, n_blk); }
+    { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)ctas, (D + 31) / 32 * 32, sm, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)out, (float*)nullptr, T, D, block_size, stride, n_blk); }
   NSA_LAUNCH_OK("compress_fwd_kernel");
   return NSA_OK;
 }
 
 extern "C" size_t nsa_block_compress_bwd_workspace_bytes(int B, int Hkv, int T, int D, int block_size) {
-  const size_t rows = (size_t)B * Hkv * (block_size > 0 ? T / block_size : 0);
+  return nsa_block_compress_strided_bwd_workspace_bytes(B, Hkv, T, D, block_size, block_size);
+}
+
+extern "C" size_t nsa_block_compress_strided_bwd_workspace_bytes(int B, int Hkv, int T, int D,
+                                                                 int block_size, int stride) {
+  const size_t rows = (size_t)B * Hkv * (block_size > 0 && stride > 0 ? n_windows(T, block_size, stride) : 0);
   // pooled[rows,D] + d_pooled[rows,D] + sum_dpooled[D] + d_w[block_size]
   return align_up((2 * rows * D + D + block_size) * sizeof(float), 256);
 }
@@ -830,11 +868,23 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
                                       float* d_intra_pos, float* d_pool_logits, float* d_proj_w,
                                       int B, int Hkv, int T, int D, int block_size, int dtype,
                                       void* workspace, size_t workspace_bytes, void* stream) {
+  return nsa_block_compress_strided_bwd(x, intra_pos, pool_logits, proj_w, d_out, dx, d_intra_pos,
+                                        d_pool_logits, d_proj_w, B, Hkv, T, D, block_size, block_size,
+                                        dtype, workspace, workspace_bytes, stream);
+}
+
+extern "C" int nsa_block_compress_strided_bwd(const void* x, const float* intra_pos,
+                                              const float* pool_logits, const float* proj_w,
+                                              const void* d_out, void* dx, float* d_intra_pos,
+                                              float* d_pool_logits, float* d_proj_w, int B, int Hkv,
+                                              int T, int D, int block_size, int stride, int dtype,
+                                              void* workspace, size_t workspace_bytes, void* stream) {
   NSA_CHECK_ARG(block_size > 0 && D > 0 && D <= 1024, "bad block_size/D");
-  const int n_blk = T / block_size;
+  NSA_CHECK_ARG(stride > 0 && stride <= block_size, "stride must be in [1, block_size]");
+  const int n_blk = n_windows(T, block_size, stride);
   const size_t rows = (size_t)B * Hkv * n_blk;
   cudaStream_t st = (cudaStream_t)stream;
-  if (workspace_bytes < nsa_block_compress_bwd_workspace_bytes(B, Hkv, T, D, block_size) || !workspace) {
+  if (workspace_bytes < nsa_block_compress_strided_bwd_workspace_bytes(B, Hkv, T, D, block_size, stride) || !workspace) {
     set_error("compress bwd workspace too small");
     return NSA_ERR_WORKSPACE;
   }
@@ -845,7 +895,8 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
   NSA_CUDA_OK(cudaMemsetAsync(sum_dp, 0, (size_t)(D + block_size) * sizeof(float), st));
   const size_t sm_f = (size_t)(block_size + D) * sizeof(float);
   const size_t sm_b = (size_t)(block_size + D + 32) * sizeof(float);
-  const size_t tail = (size_t)(T - n_blk * block_size) * D * B * Hkv;
+  const bool overlap = stride < block_size;
+  const size_t tail = overlap ? 0 : (size_t)(T - n_blk * block_size) * D * B * Hkv;
   NSA_CUDA_OK(cudaMemsetAsync(d_proj_w, 0, (size_t)D * D * sizeof(float), st));
   const dim3 pgrid(D, (unsigned)(rows >= 4096 ? 64 : (rows >= 64 ? rows / 64 : 1)));
   const bool fast = compress_fast_ok(D, block_size, dtype);
@@ -858,22 +909,34 @@ extern "C" int nsa_block_compress_bwd(const void* x, const float* intra_pos, con
       const unsigned grid = (unsigned)((rows + kCompRows - 1) / kCompRows);
       { KernelScope ks("compress_fast_fwd_kernel", st);
         compress_fast_fwd_kernel<<<grid, kCompThreads, fsm, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w,
-                                                                 (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk, rows); }
+                                                                 (__nv_bfloat16*)nullptr, pooled, T, D, block_size, stride, n_blk, rows); }
       { KernelScope ks("compress_fast_bwd_kernel", st);
         compress_fast_bwd_kernel<<<grid, kCompThreads, bsm, st>>>((const __nv_bfloat16*)x, pool_logits, proj_w,
                                                                  (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled,
-                                                                 sum_dp, d_w, T, D, block_size, n_blk, rows); }
+                                                                 sum_dp, d_w, T, D, block_size, stride, n_blk, rows); }
       { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<pgrid, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D); }
     } else if (dtype == NSA_DTYPE_BF16) {
-      { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)nullptr, pooled, T, D, block_size, n_blk); }
-      { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk); }
+      { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (__nv_bfloat16*)nullptr, pooled, T, D, block_size, stride, n_blk); }
+      { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const __nv_bfloat16*)x, intra_pos, pool_logits, proj_w, (const __nv_bfloat16*)d_out, (__nv_bfloat16*)dx, d_pooled, sum_dp, d_w, T, D, block_size, stride, n_blk); }
       { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<pgrid, (D + 31) / 32 * 32, 0, st>>>((const __nv_bfloat16*)d_out, pooled, d_proj_w, rows, D); }
     } else {
-      { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)nullptr, pooled, T, D, block_size, n_blk); }
-      { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (const float*)d_out, (float*)dx, d_pooled, sum_dp, d_w, T, D, block_size, n_blk); }
+      { KernelScope ks("compress_fwd_kernel", st); compress_fwd_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_f, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (float*)nullptr, pooled, T, D, block_size, stride, n_blk); }
+      { KernelScope ks("compress_bwd_block_kernel", st); compress_bwd_block_kernel<<<(unsigned)rows, (D + 31) / 32 * 32, sm_b, st>>>((const float*)x, intra_pos, pool_logits, proj_w, (const float*)d_out, (float*)dx, d_pooled, sum_dp, d_w, T, D, block_size, stride, n_blk); }
       { KernelScope ks("compress_bwd_proj_kernel", st); compress_bwd_proj_kernel<<<pgrid, (D + 31) / 32 * 32, 0, st>>>((const float*)d_out, pooled, d_proj_w, rows, D); }
     }
     NSA_LAUNCH_OK("compress_bwd kernels");
+  }
+  if (overlap) {   // every token of dx is written here (tokens in no window: 0)
+    const size_t n = (size_t)B * Hkv * T * D;
+    if (n && rows == 0) NSA_CUDA_OK(cudaMemsetAsync(dx, 0, n * (dtype == NSA_DTYPE_BF16 ? 2 : 4), st));
+    if (n && rows) {
+      KernelScope ks("compress_dx_kernel", st);
+      if (dtype == NSA_DTYPE_BF16)
+        compress_dx_kernel<<<blocks_for(n, 256), 256, block_size * sizeof(float), st>>>(d_pooled, pool_logits, (__nv_bfloat16*)dx, T, D, block_size, stride, n_blk, n);
+      else
+        compress_dx_kernel<<<blocks_for(n, 256), 256, block_size * sizeof(float), st>>>(d_pooled, pool_logits, (float*)dx, T, D, block_size, stride, n_blk, n);
+      NSA_LAUNCH_OK("compress_dx_kernel");
+    }
   }
   if (tail > 0) {
     if (dtype == NSA_DTYPE_BF16)

@@ -176,27 +176,34 @@ def _mean_pool_bwd(d_out, T, block_size):
     return dx
 
 
-def _compress_fwd(x, intra, logits, proj, block_size):
-    B, H, T, D, n_blk = _pool_dims(x, block_size)
+def n_summaries(T, cmp_len, cmp_stride):
+    """Complete windows of cmp_len tokens every cmp_stride tokens inside T tokens."""
+    return (T - cmp_len) // cmp_stride + 1 if T >= cmp_len else 0
+
+
+def _compress_fwd(x, intra, logits, proj, block_size, stride=None):
+    stride = block_size if stride is None else stride
+    B, H, T, D = x.shape
     x = x.contiguous()
-    out = torch.empty(B, H, n_blk, D, device=x.device, dtype=x.dtype)
-    L.check(L.lib().nsa_block_compress_fwd(L.ptr(x), L.ptr(intra), L.ptr(logits), L.ptr(proj),
-                                           L.ptr(out), B, H, T, D, int(block_size),
-                                           L.dtype_code(x), L.stream()))
+    out = torch.empty(B, H, n_summaries(T, block_size, stride), D, device=x.device, dtype=x.dtype)
+    L.check(L.lib().nsa_block_compress_strided_fwd(L.ptr(x), L.ptr(intra), L.ptr(logits), L.ptr(proj),
+                                                   L.ptr(out), B, H, T, D, int(block_size), int(stride),
+                                                   L.dtype_code(x), L.stream()))
     return out
 
 
-def _compress_bwd(x, intra, logits, proj, d_out, block_size):
-    B, H, T, D, n_blk = _pool_dims(x, block_size)
+def _compress_bwd(x, intra, logits, proj, d_out, block_size, stride=None):
+    stride = block_size if stride is None else stride
+    B, H, T, D = x.shape
     x, d_out = x.contiguous(), d_out.contiguous()
     dx = torch.empty_like(x)
     d_intra, d_logits, d_proj = (torch.empty_like(t) for t in (intra, logits, proj))
-    nws = L.lib().nsa_block_compress_bwd_workspace_bytes(B, H, T, D, int(block_size))
+    nws = L.lib().nsa_block_compress_strided_bwd_workspace_bytes(B, H, T, D, int(block_size), int(stride))
     ws = L.workspace(nws, x.device)
-    L.check(L.lib().nsa_block_compress_bwd(L.ptr(x), L.ptr(intra), L.ptr(logits), L.ptr(proj),
-                                           L.ptr(d_out), L.ptr(dx), L.ptr(d_intra), L.ptr(d_logits),
-                                           L.ptr(d_proj), B, H, T, D, int(block_size),
-                                           L.dtype_code(x), L.ptr(ws), nws, L.stream()))
+    L.check(L.lib().nsa_block_compress_strided_bwd(
+        L.ptr(x), L.ptr(intra), L.ptr(logits), L.ptr(proj), L.ptr(d_out), L.ptr(dx), L.ptr(d_intra),
+        L.ptr(d_logits), L.ptr(d_proj), B, H, T, D, int(block_size), int(stride), L.dtype_code(x),
+        L.ptr(ws), nws, L.stream()))
     return dx, d_intra, d_logits, d_proj
 
 
@@ -308,24 +315,25 @@ def block_mean_pool(x, block_size):
 
 class _BlockCompress(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, intra_pos, pool_logits, proj_weight, block_size):
+    def forward(ctx, x, intra_pos, pool_logits, proj_weight, block_size, stride):
         intra, logits, proj = (t.detach().float().contiguous() for t in (intra_pos, pool_logits, proj_weight))
         ctx.save_for_backward(x, intra, logits, proj)
-        ctx.block_size = block_size
+        ctx.block_size, ctx.stride = block_size, stride
         ctx.param_dtypes = (intra_pos.dtype, pool_logits.dtype, proj_weight.dtype)
-        return _compress_fwd(x, intra, logits, proj, block_size)
+        return _compress_fwd(x, intra, logits, proj, block_size, stride)
 
     @staticmethod
     def backward(ctx, d_out):
         x, intra, logits, proj = ctx.saved_tensors
-        dx, di, dl, dp = _compress_bwd(x, intra, logits, proj, d_out, ctx.block_size)
+        dx, di, dl, dp = _compress_bwd(x, intra, logits, proj, d_out, ctx.block_size, ctx.stride)
         a, b, c = ctx.param_dtypes
-        return dx, di.to(a), dl.to(b), dp.to(c), None
+        return dx, di.to(a), dl.to(b), dp.to(c), None, None
 
 
-def block_compress(x, intra_pos, pool_logits, proj_weight, block_size):
-    """BlockCompressor.forward (nsa_model.py:118-123) on the block view of x [B,Hkv,T,D]."""
-    return _BlockCompress.apply(x, intra_pos, pool_logits, proj_weight, block_size)
+def block_compress(x, intra_pos, pool_logits, proj_weight, block_size, stride=None):
+    """BlockCompressor.forward (nsa_model.py:118-123) on the block view of x [B,Hkv,T,D];
+    with stride < block_size on overlapping windows (not in the reference)."""
+    return _BlockCompress.apply(x, intra_pos, pool_logits, proj_weight, block_size, stride)
 
 
 class _GateCombine(torch.autograd.Function):

@@ -62,12 +62,19 @@ def window_keep(t0: int, t1: int, Lk: int, window: int) -> torch.Tensor:
     return (jj <= tt) & (tt - jj < window)
 
 
-def compress_keep(t0: int, t1: int, Lk: int, block_size: int) -> torch.Tensor:
+def compress_keep(t0: int, t1: int, Lk: int, block_size: int, stride: int = None) -> torch.Tensor:
     """[t1-t0, Lk] bool: summary j visible iff its last token (j+1)*Bsz-1 <= t
-    (nsa_fused_kernel.py:590-592, nsa_model.py:233-235)."""
+    (nsa_fused_kernel.py:590-592, nsa_model.py:233-235).  With a stride (summaries of length
+    block_size every `stride` tokens, not in the reference): last token j*stride+Bsz-1 <= t."""
+    stride = block_size if stride is None else stride
     tt = torch.arange(t0, t1)[:, None]
     jj = torch.arange(Lk)[None, :]
-    return ((jj + 1) * block_size - 1) <= tt
+    return (jj * stride + block_size - 1) <= tt
+
+
+def n_summaries(T: int, cmp_len: int, cmp_stride: int) -> int:
+    """Number of complete summary windows [j*stride, j*stride+len) inside T tokens."""
+    return (T - cmp_len) // cmp_stride + 1 if T >= cmp_len else 0
 
 
 def selection_keep(block_idx: torch.Tensor, t0: int, t1: int, T: int,
@@ -145,13 +152,22 @@ def ref_block_mean_pool(x, block_size):
     return x.mean(dim=3)
 
 
-def ref_block_compressor(x, intra_pos, pool_logits, proj_weight, block_size):
+def _windows(x, block_size, stride):
+    """[B,H,T,D] -> [B,H,n,block_size,D]: the complete windows of block_size tokens every
+    `stride` tokens (a view of the blocks when stride == block_size)."""
+    B, H, T, D = x.shape
+    n = n_summaries(T, block_size, stride)
+    if n == 0:
+        return x.new_zeros(B, H, 0, block_size, D)
+    return x.unfold(2, block_size, stride)[:, :, :n].permute(0, 1, 2, 4, 3)
+
+
+def ref_block_compressor(x, intra_pos, pool_logits, proj_weight, block_size, stride=None):
     """nsa_model.py:118-123 (BlockCompressor.forward) applied to the block view
     of x [B,Hkv,T,D] taken at nsa_model.py:217-220: softmax-weighted sum over the
-    positions of each block of (x + intra_pos), then a bias-free D x D linear."""
-    B, H, T, D = x.shape
-    n_blk = T // block_size
-    xb = x[:, :, :n_blk * block_size].reshape(B, H, n_blk, block_size, D)
+    positions of each block of (x + intra_pos), then a bias-free D x D linear.
+    stride < block_size (overlapping windows) is not expressible in the reference."""
+    xb = _windows(x, block_size, block_size if stride is None else stride)
     xb = xb + intra_pos
     w = torch.softmax(pool_logits, dim=0)
     pooled = (xb * w[:, None]).sum(dim=-2)
@@ -355,15 +371,15 @@ def window_keep_fn(Lk, window) -> KeepFn:
     return lambda t0, t1: window_keep(t0, t1, Lk, window)
 
 
-def compress_keep_fn(Lk, block_size) -> KeepFn:
-    return lambda t0, t1: compress_keep(t0, t1, Lk, block_size)
+def compress_keep_fn(Lk, block_size, stride=None) -> KeepFn:
+    return lambda t0, t1: compress_keep(t0, t1, Lk, block_size, stride)
 
 
 def selection_keep_fn(block_idx, T, block_size) -> KeepFn:
     return lambda t0, t1: selection_keep(block_idx, t0, t1, T, block_size)
 
 
-def stream_importance(q, k_cmp, block_size, chunk: int = 512):
+def stream_importance(q, k_cmp, block_size, chunk: int = 512, stride=None):
     """Row-chunked form of ref_importance: imp [B,Hkv,T,n_blk] fp32, valid [T,n_blk]."""
     B, Hq, T, D = q.shape
     Hkv, n_blk = k_cmp.shape[1], k_cmp.shape[2]
@@ -374,11 +390,35 @@ def stream_importance(q, k_cmp, block_size, chunk: int = 512):
     imp = torch.zeros(B, Hkv, T, n_blk)
     for t0 in range(0, T if n_blk > 0 else 0, chunk):
         t1 = min(T, t0 + chunk)
-        keep = compress_keep(t0, t1, n_blk, block_size)[None, None, None].expand(
+        keep = compress_keep(t0, t1, n_blk, block_size, stride)[None, None, None].expand(
             B, Hkv, G, t1 - t0, n_blk)
         s = torch.einsum("bhgtd,bhjd->bhgtj", qf[:, :, :, t0:t1], kf) * scale
         imp[:, :, t0:t1] = _masked_softmax(s, keep).sum(dim=2)
-    return imp, compress_keep(0, T, n_blk, block_size)
+    return imp, compress_keep(0, T, n_blk, block_size, stride)
+
+
+def block_importance(imp_cmp, T, cmp_len, cmp_stride, sel_block):
+    """Importance of selection blocks from the importance of summaries when the summary grid
+    (length cmp_len every cmp_stride tokens) differs from the selection grid (sel_block
+    tokens): a block takes the sum over the summaries that overlap it, and is a candidate
+    for query t as soon as the first of them is visible.  PARITY UNPINNED (the reference
+    only has cmp_len = cmp_stride = sel_block, where this is the identity on the complete
+    blocks).  cmp_len and sel_block must be multiples of cmp_stride.
+    Returns (imp_blk [B,Hkv,T,n_sblk], valid [T,n_sblk]) with n_sblk = ceil(T / sel_block)."""
+    assert cmp_len % cmp_stride == 0 and sel_block % cmp_stride == 0
+    B, Hkv, _, n_cmp = imp_cmp.shape
+    r, o = sel_block // cmp_stride, cmp_len // cmp_stride
+    n_sblk = (T + sel_block - 1) // sel_block
+    imp_blk = torch.zeros(B, Hkv, T, n_sblk)
+    valid = torch.zeros(T, n_sblk, dtype=torch.bool)
+    tt = torch.arange(T)
+    for b in range(n_sblk):
+        j0, j1 = max(0, r * b - o + 1), min(n_cmp - 1, r * b + r - 1)
+        if j0 > j1:
+            continue
+        imp_blk[..., b] = imp_cmp[..., j0:j1 + 1].sum(-1)
+        valid[:, b] = tt >= j0 * cmp_stride + cmp_len - 1
+    return imp_blk, valid
 
 
 # ---------------------------------------------------------------------------
@@ -394,12 +434,13 @@ def mean_pool_backward(d_pooled, T, block_size):
     return dx
 
 
-def compressor_backward(x, intra_pos, pool_logits, proj_weight, block_size, d_out):
+def compressor_backward(x, intra_pos, pool_logits, proj_weight, block_size, d_out, stride=None):
     """Analytic backward of ref_block_compressor.  Returns
     (dx [B,H,T,D], d_intra_pos [Bsz,D], d_pool_logits [Bsz], d_proj_weight [D,D])."""
     B, H, T, D = x.shape
-    n_blk = T // block_size
-    xb = x.float()[:, :, :n_blk * block_size].reshape(B, H, n_blk, block_size, D) + intra_pos.float()
+    stride = block_size if stride is None else stride
+    n_blk = n_summaries(T, block_size, stride)
+    xb = _windows(x.float(), block_size, stride) + intra_pos.float()
     w = torch.softmax(pool_logits.float(), dim=0)
     pooled = (xb * w[:, None]).sum(dim=-2)                         # [B,H,n,D]
     d_out = d_out.float()
@@ -410,7 +451,8 @@ def compressor_backward(x, intra_pos, pool_logits, proj_weight, block_size, d_ou
     d_w = (d_pooled[:, :, :, None, :] * xb).sum(dim=(0, 1, 2, 4))  # [Bsz]
     d_logits = w * (d_w - (d_w * w).sum())
     dx = torch.zeros(B, H, T, D)
-    dx[:, :, :n_blk * block_size] = d_xb.reshape(B, H, n_blk * block_size, D)
+    for r in range(block_size if n_blk else 0):     # position r of window j is token j*stride + r
+        dx[:, :, r:r + (n_blk - 1) * stride + 1:stride] += d_xb[:, :, :, r]
     return dx, d_intra, d_logits, d_proj
 
 
@@ -429,31 +471,45 @@ def gate_combine_backward(o_cmp, o_slc, o_win, gate_logits, d_out):
 # the whole op (pooling -> compression -> top-n -> selection -> window -> gate)
 # ---------------------------------------------------------------------------
 def stream_nsa_forward(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
-                       block_idx=None, compressor=None, chunk: int = 512):
+                       block_idx=None, compressor=None, chunk: int = 512, cmp_len=None,
+                       cmp_stride=None, n_init=0, n_local=0):
     """Forward of the full op in fp32.  `compressor` is None for mean pooling
     (nsa_fused_kernel.py:560-573) or a dict with keys k_intra,k_logits,k_proj,
     v_intra,v_logits,v_proj for the learned pooling of the model
     (nsa_model.py:336-337).  When block_idx is None it is chosen by
     canonical_topn over the compression probabilities (nsa_model.py:343-355).
     Returns a dict with out, the three branch outputs and LSEs, k_cmp, v_cmp,
-    block_idx and (when computed) importance."""
+    block_idx and (when computed) importance.
+    cmp_len / cmp_stride (default block_size: the reference's geometry) give summaries of
+    cmp_len tokens every cmp_stride tokens, selection blocks staying block_size tokens;
+    n_init / n_local force blocks into every list (see forced_topn).  Both generalisations
+    are parity-unpinned restatements of the published NSA recipe."""
     T = q.shape[2]
+    cl = block_size if cmp_len is None else cmp_len
+    cs = cl if cmp_stride is None else cmp_stride
+    general = (cl, cs) != (block_size, block_size)
     if compressor is None:
+        assert not general, "mean pooling is defined on the aligned grid only"
         k_cmp = ref_block_mean_pool(kc.float(), block_size)
         v_cmp = ref_block_mean_pool(vc.float(), block_size)
     else:
         k_cmp = ref_block_compressor(kc.float(), compressor["k_intra"].float(),
                                      compressor["k_logits"].float(),
-                                     compressor["k_proj"].float(), block_size)
+                                     compressor["k_proj"].float(), cl, cs)
         v_cmp = ref_block_compressor(vc.float(), compressor["v_intra"].float(),
                                      compressor["v_logits"].float(),
-                                     compressor["v_proj"].float(), block_size)
+                                     compressor["v_proj"].float(), cl, cs)
     n_blk = k_cmp.shape[2]
     res = {"k_cmp": k_cmp, "v_cmp": v_cmp}
-    o_cmp, lse_cmp = stream_attn_forward(q, k_cmp, v_cmp, compress_keep_fn(n_blk, block_size), chunk)
+    o_cmp, lse_cmp = stream_attn_forward(q, k_cmp, v_cmp, compress_keep_fn(n_blk, cl, cs), chunk)
     if block_idx is None:
-        imp, valid = stream_importance(q, k_cmp, block_size, chunk)
-        block_idx = canonical_topn(imp, valid, n_sel)
+        imp, valid = stream_importance(q, k_cmp, cl, chunk, cs)
+        if general:
+            imp, valid = block_importance(imp, T, cl, cs, block_size)
+        if general or n_init or n_local:
+            block_idx = forced_topn(imp, valid, n_sel, T, block_size, n_init, n_local)
+        else:
+            block_idx = canonical_topn(imp, valid, n_sel)
         res["importance"] = imp
     o_slc, lse_slc = stream_attn_forward(q, ks, vs, selection_keep_fn(block_idx, T, block_size), chunk)
     o_win, lse_win = stream_attn_forward(q, kw, vw, window_keep_fn(T, window), chunk)
@@ -464,17 +520,19 @@ def stream_nsa_forward(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel
 
 
 def stream_nsa_backward(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, window, fwd, d_out,
-                        compressor=None, chunk: int = 512):
+                        compressor=None, chunk: int = 512, cmp_len=None, cmp_stride=None):
     """Analytic backward of stream_nsa_forward given its result dict `fwd`.
     Returns a dict of gradients: q, kc, vc, ks, vs, kw, vw, gate and, for the
     learned compressor, k_intra,k_logits,k_proj,v_intra,v_logits,v_proj."""
     T = q.shape[2]
+    cl = block_size if cmp_len is None else cmp_len
+    cs = cl if cmp_stride is None else cmp_stride
     n_blk = fwd["k_cmp"].shape[2]
     do_cmp, do_slc, do_win, d_gate = gate_combine_backward(
         fwd["o_cmp"], fwd["o_slc"], fwd["o_win"], gate_logits, d_out)
     dq1, dk_cmp, dv_cmp = stream_attn_backward(q, fwd["k_cmp"], fwd["v_cmp"], fwd["o_cmp"],
                                                fwd["lse_cmp"], do_cmp,
-                                               compress_keep_fn(n_blk, block_size), chunk)
+                                               compress_keep_fn(n_blk, cl, cs), chunk)
     dq2, dks, dvs = stream_attn_backward(q, ks, vs, fwd["o_slc"], fwd["lse_slc"], do_slc,
                                          selection_keep_fn(fwd["block_idx"], T, block_size), chunk)
     dq3, dkw, dvw = stream_attn_backward(q, kw, vw, fwd["o_win"], fwd["lse_win"], do_win,
@@ -486,10 +544,10 @@ def stream_nsa_backward(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, wind
     else:
         g["kc"], g["k_intra"], g["k_logits"], g["k_proj"] = compressor_backward(
             kc, compressor["k_intra"], compressor["k_logits"], compressor["k_proj"],
-            block_size, dk_cmp)
+            cl, dk_cmp, cs)
         g["vc"], g["v_intra"], g["v_logits"], g["v_proj"] = compressor_backward(
             vc, compressor["v_intra"], compressor["v_logits"], compressor["v_proj"],
-            block_size, dv_cmp)
+            cl, dv_cmp, cs)
     return g
 
 

@@ -463,3 +463,32 @@ def test_module_under_activation_checkpointing():
     for a, b in zip(*grads):
         assert torch.allclose(a, b, rtol=0, atol=1e-6 + 1e-2 * a.abs().max().item()), (a - b).abs().max()
     assert pkg().lib().nsa_device_status(None) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("geom", [(32, 16, 64), (32, 8, 16), (64, 64, 128), (16, 16, 32), (48, 16, 40)],
+                         ids=lambda g: f"len{g[0]}stride{g[1]}D{g[2]}")
+def test_strided_compressor(geom, dtype):
+    """Learned pooling over overlapping windows (length != stride) and its backward against the
+    oracle, whose strided form is checked against autograd; stride == length is the pinned case."""
+    nsa = pkg()
+    l, d, D = geom
+    B, H, T = 2, 2, 333
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(B, H, T, D, generator=g).to(dtype).float()
+    ip, pl = 0.1 * torch.randn(l, D, generator=g), 0.5 * torch.randn(l, generator=g)
+    W = torch.randn(D, D, generator=g) * D ** -0.5
+    y_ref = O.ref_block_compressor(x, ip, pl, W, l, d)
+    do = torch.randn(y_ref.shape, generator=g).to(dtype).float()
+    ref = O.compressor_backward(x, ip, pl, W, l, do, d)
+    xd = dev(x, dtype).requires_grad_(True)
+    ps = [t.cuda().requires_grad_(True) for t in (ip, pl, W)]
+    y = nsa.block_compress(xd, *ps, l, d)
+    assert y.shape == y_ref.shape
+    y.backward(dev(do, dtype))
+    check(y, y_ref, dtype, "pooled", abs32=1e-4)
+    check(xd.grad, ref[0], dtype, "dx", abs32=1e-4)
+    for got, want, name in zip(ps, ref[1:], ("d_intra", "d_logits", "d_proj")):
+        ma, rl = err(got.grad, want)
+        lim = 2e-3 if dtype == torch.float32 else 5e-2
+        assert rl <= lim or ma <= lim, f"{name}: abs {ma:.3e} rel {rl:.3e}"
