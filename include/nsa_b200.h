@@ -33,6 +33,7 @@ extern "C" {
 
 #define NSA_MODE_WINDOW   0   /* nsa_fused_kernel.py:46 */
 #define NSA_MODE_COMPRESS 1   /* nsa_fused_kernel.py:47 */
+#define NSA_MODE_COMPRESS_STRIDED 3   /* no counterpart in the reference: `window` is the summary stride */
 
 /* which kernel family serves a call */
 #define NSA_IMPL_AUTO 0   /* tcgen05 kernels when the shape allows, else the SIMT kernels */
@@ -60,7 +61,11 @@ int nsa_tc_supported(const NsaDims* dims, int block_size);
  * Replaces _range_attn_forward / _range_attn_backward and the kernels under them
  * (nsa_fused_kernel.py:442-518, kernels :61-426) behind _RangeAttn (:521-534).
  * mode WINDOW: query t attends keys [max(0,t-window+1), t]; Lk = T.
- * mode COMPRESS: query t attends summaries j with (j+1)*block_size-1 <= t; Lk = n_blk.
+ * mode COMPRESS: query t attends summaries j with (j+1)*block_size-1 <= t; Lk = n_blk (`window`
+ *   is ignored, as in the reference).
+ * mode COMPRESS_STRIDED: `window` is a summary stride d <= block_size: summary j covers tokens
+ *   [j*d, j*d + block_size) and is attended when j*d + block_size - 1 <= t; d = block_size is
+ *   mode COMPRESS.
  * The forward also writes lse (the reference recomputes it in backward). */
 /* Backward of a gated branch: when row_scale / row_dot [B,Hq,T] float32 are given (both or
  * neither), d_o is the upstream gradient of the whole op, the branch's own gradient is
@@ -98,9 +103,11 @@ int nsa_selection_bwd(const void* q, const void* k, const void* v, const int32_t
  * `dq` argument may be NULL: the branch's bf16 dQ partials then stay in the call's workspace, and
  * this entry point adds the partials of the compression, selection and window branches of every
  * query in fp32 and writes dq [B,Hq,T,D] once.  ws_* are the workspaces of the three backward
- * calls (same dims; Lk_cmp, block_size, S, window as given to them); NULL = branch absent. */
-int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int block_size, int S, int window,
-                   const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq, void* stream);
+ * calls (same dims; Lk_cmp, the summary length and stride, S, the selection block size and the
+ * window as given to them); NULL = branch absent. */
+int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int cmp_len, int cmp_stride, int S, int block_size,
+                   int window, const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
+                   void* stream);
 
 /* ---- block -> query CSR ---------------------------------------------------------------------
  * Replaces build_block_to_query_csr (nsa_fsa.py:14-64): pairs (query i, block j) with j >= 0

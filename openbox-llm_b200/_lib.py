@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libnsa_b200.so")
 
 DTYPE_BF16, DTYPE_F32 = 0, 1
 MODE_WINDOW, MODE_COMPRESS = 0, 1
+MODE_COMPRESS_STRIDED = 3   # the `window` argument is the stride of the summaries
 IMPL = {"auto": 0, "simt": 1, "tc": 2}
 
 
@@ -58,7 +59,7 @@ SIGNATURES = {
     "nsa_topn_blocks_forced": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_gate_combine_bwd_rows": (_i, [_vp] * 8 + [_dp, _vp]),
     "nsa_sum3": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp]),
-    "nsa_dq_reduce3": (_i, [_dp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "nsa_dq_reduce3": (_i, [_dp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "nsa_gate_combine_fwd": (_i, [_vp] * 5 + [_dp, _vp]),
     "nsa_gate_combine_bwd": (_i, [_vp] * 9 + [_dp, _vp]),
 }

@@ -200,16 +200,22 @@ extern "C" int nsa_range_attn_fwd(const void* q, const void* k, const void* v, v
                                   int impl, void* stream) {
   int rc = check_dims(dims);
   if (rc != NSA_OK) return rc;
-  NSA_CHECK_ARG(mode == NSA_MODE_WINDOW || mode == NSA_MODE_COMPRESS, "bad mode %d", mode);
+  NSA_CHECK_ARG(mode == NSA_MODE_WINDOW || mode == NSA_MODE_COMPRESS || mode == NSA_MODE_COMPRESS_STRIDED,
+                "bad mode %d", mode);
   NSA_CHECK_ARG(Lk >= 0, "bad Lk");
   if (mode == NSA_MODE_WINDOW) NSA_CHECK_ARG(window >= 1, "window must be >= 1");
-  if (mode == NSA_MODE_COMPRESS) NSA_CHECK_ARG(block_size >= 1, "block_size must be >= 1");
+  if (mode != NSA_MODE_WINDOW) NSA_CHECK_ARG(block_size >= 1, "block_size must be >= 1");
   const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
   if (rows == 0) return NSA_OK;
   NSA_CHECK_ARG(q && o && lse && (Lk == 0 || (k && v)), "null tensor");
   AttnArgs a = base_args(dims, Lk);
   a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse;
   a.kind = mode; a.window = window; a.block_size = block_size;
+  if (mode == NSA_MODE_COMPRESS) a.window = block_size;   // internally `window` holds the summary stride
+  if (mode == NSA_MODE_COMPRESS_STRIDED) {
+    NSA_CHECK_ARG(window >= 1 && window <= block_size, "summary stride must be in [1, block_size]");
+    a.kind = NSA_MODE_COMPRESS;
+  }
   if (use_tc(dims, 64, impl, &rc) && Lk > 0) return tc_attn_fwd(a, (cudaStream_t)stream);
   if (rc != NSA_OK) return rc;
   return simt_attn_fwd(a, dims->dtype, (cudaStream_t)stream);
@@ -222,7 +228,8 @@ extern "C" size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk
   size_t need = simt_bwd_ws(dims, Lk);
   if (use_tc(dims, 64, impl, &rc)) {
     AttnArgs a = base_args(dims, Lk);
-    a.kind = mode; a.window = window > 0 ? window : 1;
+    a.kind = mode == NSA_MODE_COMPRESS_STRIDED ? NSA_MODE_COMPRESS : mode;
+    a.window = window > 0 ? window : 1;
     need = need > tc_attn_bwd_workspace(a) ? need : tc_attn_bwd_workspace(a);
   }
   return need;
@@ -235,9 +242,10 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
                                   void* workspace, size_t workspace_bytes, int impl, void* stream) {
   int rc = check_dims(dims);
   if (rc != NSA_OK) return rc;
-  NSA_CHECK_ARG(mode == NSA_MODE_WINDOW || mode == NSA_MODE_COMPRESS, "bad mode %d", mode);
+  NSA_CHECK_ARG(mode == NSA_MODE_WINDOW || mode == NSA_MODE_COMPRESS || mode == NSA_MODE_COMPRESS_STRIDED,
+                "bad mode %d", mode);
   if (mode == NSA_MODE_WINDOW) NSA_CHECK_ARG(window >= 1, "window must be >= 1");
-  if (mode == NSA_MODE_COMPRESS) NSA_CHECK_ARG(block_size >= 1, "block_size must be >= 1");
+  if (mode != NSA_MODE_WINDOW) NSA_CHECK_ARG(block_size >= 1, "block_size must be >= 1");
   cudaStream_t st = (cudaStream_t)stream;
   const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
   const size_t nkv = (size_t)dims->B * dims->Hkv * Lk * dims->D;
@@ -253,6 +261,11 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
   AttnArgs a = base_args(dims, Lk);
   a.q = q; a.k = k; a.v = v; a.o = (void*)o; a.lse = (float*)lse; a.d_o = d_o; a.dq = dq;
   a.kind = mode; a.window = window; a.block_size = block_size;
+  if (mode == NSA_MODE_COMPRESS) a.window = block_size;   // internally `window` holds the summary stride
+  if (mode == NSA_MODE_COMPRESS_STRIDED) {
+    NSA_CHECK_ARG(window >= 1 && window <= block_size, "summary stride must be in [1, block_size]");
+    a.kind = NSA_MODE_COMPRESS;
+  }
   a.row_scale = row_scale; a.row_dot = row_dot;
   NSA_CHECK_ARG((row_scale == nullptr) == (row_dot == nullptr), "row_scale and row_dot go together");
   if (use_tc(dims, 64, impl, &rc)) {
@@ -342,16 +355,18 @@ extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
   return simt_bwd(a, dims, dk, dv, workspace, workspace_bytes, st);
 }
 
-extern "C" int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int block_size, int S, int window,
-                              const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
-                              void* stream) {
+extern "C" int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int cmp_len, int cmp_stride, int S,
+                              int block_size, int window, const void* ws_cmp, const void* ws_slc,
+                              const void* ws_win, void* dq, void* stream) {
   int rc = check_dims(dims);
   if (rc != NSA_OK) return rc;
   NSA_CHECK_ARG(dq, "null dq");
   NSA_CHECK_ARG(use_tc(dims, block_size, NSA_IMPL_AUTO, &rc), "nsa_dq_reduce3 needs a shape the tcgen05 kernels serve");
-  NSA_CHECK_ARG(!ws_cmp || (Lk_cmp > 0 && block_size > 0), "bad compression geometry");
+  if (cmp_stride <= 0) cmp_stride = cmp_len;
+  NSA_CHECK_ARG(!ws_cmp || (Lk_cmp > 0 && cmp_len > 0 && cmp_stride <= cmp_len), "bad compression geometry");
   NSA_CHECK_ARG(!ws_slc || S > 0, "bad S");
   NSA_CHECK_ARG(!ws_win || window >= 1, "bad window");
   const AttnArgs a = base_args(dims, dims->T);
-  return tc_dq_reduce3(a, Lk_cmp, block_size, S, window, ws_cmp, ws_slc, ws_win, dq, (cudaStream_t)stream);
+  return tc_dq_reduce3(a, Lk_cmp, cmp_len, cmp_stride, S, block_size, window, ws_cmp, ws_slc, ws_win, dq,
+                       (cudaStream_t)stream);
 }

@@ -9,6 +9,14 @@
 #include "../../include/nsa_b200.h"
 
 namespace nsa {
+// Compression summaries: summary j covers tokens [j * stride, j * stride + len); query t sees
+// the summaries that end at or before t (nsa_model.py:233-235 for stride == len).
+__host__ __device__ __forceinline__ int cmp_visible(int t, int len, int stride, int n_summaries) {
+  if (t + 1 < len) return 0;
+  const int n = (t + 1 - len) / stride + 1;
+  return n < n_summaries ? n : n_summaries;
+}
+
 // Rank keys of forced selection blocks: above every importance (a sum of at most G <= 128
 // probabilities), initial blocks ahead of local ones, exact in fp32 for counts below 2^18.
 constexpr float kForcedInit = 1048576.f;    // - block index
@@ -106,7 +114,8 @@ size_t tc_sel_fwd_workspace(const AttnArgs& a);
 int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t tc_attn_bwd_workspace(const AttnArgs& a);
 int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
-int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int block_size, int S, int window, const void* ws_cmp,
-                  const void* ws_slc, const void* ws_win, void* dq, cudaStream_t st);
+int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int cmp_len, int cmp_stride, int S, int block_size,
+                  int window, const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
+                  cudaStream_t st);
 
 }  // namespace nsa

@@ -73,7 +73,7 @@ __device__ __forceinline__ bool key_range(const AttnArgs& a, int b, int hkv, int
     hi = min(t, a.Lk - 1);
   } else if (a.kind == 1) {
     lo = 0;
-    hi = min((t + 1) / a.block_size - 1, a.Lk - 1);
+    hi = cmp_visible(t, a.block_size, a.window, a.Lk) - 1;   // compression: window holds the stride
   } else {
     int blk = __ldg(a.block_idx + ((size_t)(b * a.Hkv + hkv) * a.T + t) * a.S + r);
     if (blk < 0) return false;

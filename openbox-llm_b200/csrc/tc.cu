@@ -111,7 +111,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     first_key = max(0, t0 - p.window + 1) & ~(kKeys - 1);
     n_tiles = (min(t_last, p.Lk - 1) - first_key) / kKeys + 1;
   } else if (p.kind == 1) {
-    const int hi_last = min(p.Lk, (t_last + 1) / p.block_size) - 1;
+    const int hi_last = cmp_visible(t_last, p.block_size, p.window, p.Lk) - 1;   // window: the stride
     n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
   } else {
     const int nmem = p.nb_sel * p.nw;
@@ -238,7 +238,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           lo = max(0, t - p.window + 1 - key0);
           hi = min(kKeys - 1, t - key0);
         } else if (p.kind == 1) {
-          hi = min(kKeys - 1, min(p.Lk, (t + 1) / p.block_size) - 1 - key0);
+          hi = min(kKeys - 1, cmp_visible(t, p.block_size, p.window, p.Lk) - 1 - key0);
         } else {
           const uint32_t w = s_member[(key0 / kKeys) * p.nw + (ql >> 5)];
           if ((w >> (ql & 31)) & 1u) hi = min(kKeys - 1, t - key0);

@@ -157,7 +157,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     t_lo = key0;
     n_q = min(p.T - 1, key0 + kKeys - 1 + p.window - 1) - t_lo + 1;
   } else if (p.kind == 1) {
-    t_lo = (key0 + 1) * p.block_size - 1;
+    t_lo = key0 * p.window + p.block_size - 1;       // first query that sees summary key0 (window: the stride)
     n_q = p.T - t_lo;
   } else {
     pair_base = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j);
@@ -346,7 +346,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         lo = max(0, t_cur - p.window + 1 - key0);
         hi = min(kKeys - 1, t_cur - key0);
       } else if (p.kind == 1) {
-        hi = min(kKeys - 1, min(p.Lk, (t_cur + 1) / p.block_size) - 1 - key0);
+        hi = min(kKeys - 1, cmp_visible(t_cur, p.block_size, p.window, p.Lk) - 1 - key0);
       } else {
         hi = min(kKeys - 1, min(t_cur, p.T - 1) - key0);
       }
@@ -563,7 +563,7 @@ __global__ void dq_reduce_kernel(const __nv_bfloat16* __restrict__ part, const i
   } else {
     int first, last;   // key tiles this query attends
     if (kind == 0) { first = max(0, t - window + 1) >> 6; last = t >> 6; }
-    else { first = 0; last = (min(Lk, (t + 1) / block_size) - 1); last = last < 0 ? -1 : last >> 6; }
+    else { first = 0; last = cmp_visible(t, block_size, window, Lk) - 1; last = last < 0 ? -1 : last >> 6; }
     for (int jt = first; jt <= last; ++jt) {
       const int slot = kind == 0 ? jt % n_slots : jt;
       add((bh * T + t) * n_slots + slot);
@@ -579,7 +579,7 @@ __global__ void dq_reduce_kernel(const __nv_bfloat16* __restrict__ part, const i
 // dq of the whole op in one pass: the partials of the compression, selection and window branches
 // of query (bh, t) are added in fp32 and rounded once.  A branch whose buffer is null is absent.
 struct Reduce3Args {
-  const __nv_bfloat16* part_cmp; int slots_cmp, Lk_cmp, block_size;
+  const __nv_bfloat16* part_cmp; int slots_cmp, Lk_cmp, cmp_len, cmp_stride;
   const __nv_bfloat16* part_slc; const int32_t* pair_of_slot; int S;
   const __nv_bfloat16* part_win; int slots_win, window;
   __nv_bfloat16* dq;
@@ -637,7 +637,7 @@ __global__ void dq_reduce3_kernel(const Reduce3Args a) {
     }
   }
   if (a.part_cmp) {
-    const int n_vis = min(a.Lk_cmp, (t + 1) / a.block_size);
+    const int n_vis = cmp_visible(t, a.cmp_len, a.cmp_stride, a.Lk_cmp);
     const int last = n_vis > 0 ? (n_vis - 1) >> 6 : -1;
     for (int j0 = 0; j0 <= last; j0 += 4) {
       long long rows[4];
@@ -876,18 +876,19 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
 
 // dq of the whole op from the three branch workspaces (each written by tc_attn_bwd with a null
 // dq): `base` carries B, Hq, Hkv, T, D; a null workspace means the branch is absent.
-int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int block_size, int S, int window, const void* ws_cmp,
-                  const void* ws_slc, const void* ws_win, void* dq, cudaStream_t st) {
+int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int cmp_len, int cmp_stride, int S, int block_size,
+                  int window, const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
+                  cudaStream_t st) {
   using namespace tc;
   Reduce3Args r;
   r.part_cmp = r.part_slc = r.part_win = nullptr;
   r.pair_of_slot = nullptr;
   r.slots_cmp = r.slots_win = 1;
-  r.Lk_cmp = Lk_cmp; r.block_size = block_size; r.S = S; r.window = window;
+  r.Lk_cmp = Lk_cmp; r.cmp_len = cmp_len; r.cmp_stride = cmp_stride; r.S = S; r.window = window;
   r.dq = (__nv_bfloat16*)dq;
   r.B = base.B; r.Hq = base.Hq; r.Hkv = base.Hkv; r.T = base.T; r.G = base.Hq / base.Hkv;
   if (ws_cmp) {
-    AttnArgs a = base; a.kind = 1; a.Lk = Lk_cmp; a.block_size = block_size;
+    AttnArgs a = base; a.kind = 1; a.Lk = Lk_cmp; a.block_size = cmp_len; a.window = cmp_stride;
     const BwdPlan pl = plan_bwd(a);
     r.part_cmp = (const __nv_bfloat16*)((const char*)ws_cmp + pl.off_part);
     r.slots_cmp = pl.n_slots;

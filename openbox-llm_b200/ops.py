@@ -17,6 +17,7 @@ from . import _lib as L
 
 MODE_WINDOW = L.MODE_WINDOW
 MODE_COMPRESS = L.MODE_COMPRESS
+MODE_COMPRESS_STRIDED = L.MODE_COMPRESS_STRIDED
 
 _impl = "auto"
 
@@ -272,7 +273,11 @@ def window_attn_triton(q, k, v, window):
     return _RangeAttn.apply(q, k, v, MODE_WINDOW, window, 0)
 
 
-def compression_attn_triton(q, k_cmp, v_cmp, block_size):
+def compression_attn_triton(q, k_cmp, v_cmp, block_size, stride=0):
+    """nsa_fused_kernel.py:541-543.  stride (not in the reference): the summaries are windows of
+    block_size tokens every `stride` tokens; 0 = block_size."""
+    if stride:
+        return _RangeAttn.apply(q, k_cmp, v_cmp, MODE_COMPRESS_STRIDED, stride, block_size)
     return _RangeAttn.apply(q, k_cmp, v_cmp, MODE_COMPRESS, 0, block_size)
 
 
@@ -433,7 +438,7 @@ class _NSAAttention(torch.autograd.Function):
         if fused:
             n_cmp = k_cmp.shape[2]
             d = L.dims(B, Hq, ks.shape[1], T, q.shape[3], L.dtype_code(q))
-            L.check(L.lib().nsa_dq_reduce3(d, n_cmp, int(block_size), S, int(window),
+            L.check(L.lib().nsa_dq_reduce3(d, n_cmp, int(block_size), int(block_size), S, int(block_size), int(window),
                                            L.ptr(dq) if n_cmp > 0 else None, L.ptr(dq2), L.ptr(dq3),
                                            L.ptr(dq_sum), L.stream()))
         else:

@@ -492,3 +492,34 @@ def test_strided_compressor(geom, dtype):
         ma, rl = err(got.grad, want)
         lim = 2e-3 if dtype == torch.float32 else 5e-2
         assert rl <= lim or ma <= lim, f"{name}: abs {ma:.3e} rel {rl:.3e}"
+
+
+@pytest.mark.parametrize("geom", [(32, 16), (64, 16), (64, 32)], ids=lambda g: f"len{g[0]}stride{g[1]}")
+@pytest.mark.parametrize("c", [REF_CONFIGS[1], TC_CONFIGS[0], TC_CONFIGS[2]], ids=cfg_id)
+def test_strided_compression_attention(c, geom):
+    """Compression attention over summaries of `len` tokens every `stride` tokens (visible when
+    j*stride + len - 1 <= t), forward and backward, CUDA-core and tcgen05 kernels."""
+    nsa = pkg()
+    l, d = geom
+    T = c["T"]
+    n_cmp = O.n_summaries(T, l, d)
+    for dtype in DTYPES:
+        t = make_inputs(c, dtype, seed=11)
+        g = torch.Generator().manual_seed(12)
+        k = torch.randn(c["B"], c["Hkv"], n_cmp, c["D"], generator=g).to(dtype).float()
+        v = torch.randn(c["B"], c["Hkv"], n_cmp, c["D"], generator=g).to(dtype).float()
+        keep_fn = O.compress_keep_fn(n_cmp, l, d)
+        o_ref, lse_ref = O.stream_attn_forward(t["q"], k, v, keep_fn)
+        dq_ref, dk_ref, dv_ref = O.stream_attn_backward(t["q"], k, v, o_ref, lse_ref, t["do"], keep_fn)
+        for impl in _impls_for(c, dtype):
+            nsa.set_impl(impl)
+            q_d, k_d, v_d, do_d = (dev(x, dtype) for x in (t["q"], k, v, t["do"]))
+            o, lse = nsa.range_attn_forward(q_d, k_d, v_d, nsa.MODE_COMPRESS_STRIDED, d, l)
+            check(o, o_ref, dtype, impl + " o")
+            empty = lse_ref == O.LSE_EMPTY
+            assert (o.float().cpu()[empty] == 0).all()
+            dq, dk, dv = nsa.range_attn_backward(q_d, k_d, v_d, o, lse, do_d, nsa.MODE_COMPRESS_STRIDED, d, l)
+            check(dq, dq_ref, dtype, impl + " dq", abs32=4e-3)
+            check(dk, dk_ref, dtype, impl + " dk", abs32=4e-3)
+            check(dv, dv_ref, dtype, impl + " dv", abs32=4e-3)
+    nsa.set_impl("auto")
