@@ -194,6 +194,20 @@ int nsa_topn_blocks_forced(const void* q, const void* k_cmp, const float* lse_cm
                            float* importance_out, const NsaDims* dims, int n_blk, int block_size,
                            int n_sel, int n_init, int n_local, int impl, void* stream);
 
+/* The same when the compression summaries and the selection blocks sit on different grids (the
+ * published NSA recipe: summaries of 32 tokens every 16, selection blocks of 64); no counterpart in
+ * the reference, where the three sizes are one number.  k_cmp holds n_cmp summaries of cmp_len
+ * tokens every cmp_stride tokens (lse_cmp from mode COMPRESS_STRIDED); cmp_len and sel_block are
+ * multiples of cmp_stride.  The importance of selection block b is the sum of the importances of
+ * the summaries that overlap it, and b is a candidate for query t once the first of them is
+ * visible; forced blocks as above with cur = t / sel_block.  importance_out (optional) receives
+ * the block importance [B,Hkv,T,ceil(T/sel_block)] (with the three sizes equal: [B,Hkv,T,n_cmp],
+ * which is nsa_topn_blocks_forced). */
+int nsa_topn_blocks_general(const void* q, const void* k_cmp, const float* lse_cmp, int32_t* block_idx,
+                            float* importance_out, const NsaDims* dims, int n_cmp, int cmp_len,
+                            int cmp_stride, int sel_block, int n_sel, int n_init, int n_local, int impl,
+                            void* stream);
+
 /* ---- gate combine ---------------------------------------------------------------------------
  * Replaces the sigmoid blend nsa_model.py:366-368 / nsa_fused_kernel.py:572-573 and its
  * autograd backward: out = sum_i sigmoid(gate[...,i]) * o_i; d_gate is float32-accumulated

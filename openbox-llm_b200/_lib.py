@@ -57,6 +57,7 @@ SIGNATURES = {
     "nsa_block_compress_strided_bwd": (_i, [_vp] * 9 + [_i] * 7 + [_vp, _sz, _vp]),
     "nsa_topn_blocks": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _i, _vp]),
     "nsa_topn_blocks_forced": (_i, [_vp] * 5 + [_dp, _i, _i, _i, _i, _i, _i, _vp]),
+    "nsa_topn_blocks_general": (_i, [_vp] * 5 + [_dp] + [_i] * 8 + [_vp]),
     "nsa_gate_combine_bwd_rows": (_i, [_vp] * 8 + [_dp, _vp]),
     "nsa_sum3": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "nsa_dq_reduce3": (_i, [_dp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

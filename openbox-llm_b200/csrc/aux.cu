@@ -421,11 +421,16 @@ __global__ void __launch_bounds__(128) topn_kernel(const T* __restrict__ q, cons
                                                    int32_t* __restrict__ block_idx,
                                                    float* __restrict__ imp_out, int B, int Hq, int Hkv,
                                                    int T_, int n_blk, int bs, int n_sel, int n_init,
-                                                   int n_local, float scale) {
+                                                   int n_local, float scale, int stride, int sel_block,
+                                                   int n_sblk, int imp_cols) {
+  // n_blk summaries of bs tokens every `stride` tokens; n_sblk selection blocks of sel_block
+  // tokens.  A selection block takes the sum of the summaries that overlap it and is a candidate
+  // once the first of them is visible; with bs == stride == sel_block blocks and summaries coincide.
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* qs = sm + (size_t)warp * (D + n_blk + 1);   // [D]
-  float* imp = qs + D;                               // [n_blk + 1]: a ragged tail block can be forced
+  float* qs = sm + (size_t)warp * (D + n_blk + n_sblk + 1);   // [D]
+  float* sums = qs + D;                                       // [n_blk] importance of the summaries
+  float* imp = sums + n_blk;                                  // [n_sblk + 1] importance of the blocks
   const size_t total = (size_t)B * Hkv * T_;
   const size_t unit = (size_t)blockIdx.x * 4 + warp;
   if (unit >= total) return;
@@ -433,8 +438,8 @@ __global__ void __launch_bounds__(128) topn_kernel(const T* __restrict__ q, cons
   const int hkv = (int)((unit / T_) % Hkv);
   const int b = (int)(unit / ((size_t)T_ * Hkv));
   const int G = Hq / Hkv;
-  const int n_valid = min((t + 1) / bs, n_blk);
-  for (int j = lane; j < n_blk; j += 32) imp[j] = 0.f;
+  const int n_valid = cmp_visible(t, bs, stride, n_blk);
+  for (int j = lane; j < n_blk; j += 32) sums[j] = 0.f;
   const T* kbase = kc + (size_t)(b * Hkv + hkv) * n_blk * D;
   for (int g = 0; g < G; ++g) {
     const size_t row = ((size_t)(b * Hq + hkv * G + g)) * T_ + t;
@@ -465,27 +470,37 @@ __global__ void __launch_bounds__(128) topn_kernel(const T* __restrict__ q, cons
         for (int i = 0; i < D; ++i) acc = fmaf(kr[i], qs[i], acc);
         s = acc;
       }
-      imp[j] += expf(s - l);
+      sums[j] += expf(s - l);
     }
   }
   __syncwarp();
+  // selection blocks up to the one holding t: importance, -1 when no overlapping summary is visible
+  const int r_ = sel_block / stride, o_ = bs / stride;
+  const int cur = t / sel_block;
+  for (int bb = lane; bb <= cur; bb += 32) {
+    const int j0 = max(0, r_ * bb - o_ + 1), j1 = min(n_valid - 1, r_ * bb + r_ - 1);
+    float v = -1.f;
+    if (j0 < n_valid) {
+      v = 0.f;
+      for (int j = j0; j <= j1; ++j) v += sums[j];
+    }
+    imp[bb] = v;
+  }
+  __syncwarp();
   if (imp_out) {
-    float* dst = imp_out + unit * n_blk;
-    for (int j = lane; j < n_blk; j += 32) dst[j] = j < n_valid ? imp[j] : 0.f;
+    float* dst = imp_out + unit * imp_cols;
+    for (int j = lane; j < imp_cols; j += 32) dst[j] = (j <= cur && imp[j] >= 0.f) ? imp[j] : 0.f;
   }
   int32_t* out = block_idx + unit * n_sel;
   // forced blocks: the first n_init blocks and the n_local most recent ones (the block holding
-  // t included) rank ahead of every importance (<= G); other incomplete blocks do not compete
-  int n_cand = n_valid;
+  // t included) rank ahead of every importance (<= G); other invisible blocks do not compete
+  const int n_cand = cur + 1;
   if (n_init > 0 || n_local > 0) {
-    const int cur = t / bs;
     __syncwarp();
     for (int j = lane; j <= cur; j += 32) {
       if (j < n_init) imp[j] = kForcedInit - (float)j;
       else if (j > cur - n_local) imp[j] = kForcedLocal - (float)(cur - j);
-      else if (j >= n_valid) imp[j] = -1.f;
     }
-    n_cand = cur + 1;
     __syncwarp();
   }
   for (int s = 0; s < n_sel; ++s) {
@@ -951,9 +966,10 @@ extern "C" int nsa_block_compress_strided_bwd(const void* x, const float* intra_
 }
 
 namespace nsa {
-bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel);
+bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel, int cmp_len, int stride, int sel_block);
 int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_idx, float* imp_out,
-            const NsaDims& d, int n_blk, int block_size, int n_sel, int n_init, int n_local, cudaStream_t st);
+            const NsaDims& d, int n_blk, int block_size, int n_sel, int n_init, int n_local, int stride,
+            int sel_block, int imp_cols, cudaStream_t st);
 }
 
 extern "C" int nsa_topn_blocks(const void* q, const void* k_cmp, const float* lse_cmp,
@@ -967,24 +983,38 @@ extern "C" int nsa_topn_blocks_forced(const void* q, const void* k_cmp, const fl
                                       int32_t* block_idx, float* importance_out, const NsaDims* dims,
                                       int n_blk, int block_size, int n_sel, int n_init, int n_local,
                                       int impl, void* stream) {
+  return nsa_topn_blocks_general(q, k_cmp, lse_cmp, block_idx, importance_out, dims, n_blk, block_size,
+                                 block_size, block_size, n_sel, n_init, n_local, impl, stream);
+}
+
+extern "C" int nsa_topn_blocks_general(const void* q, const void* k_cmp, const float* lse_cmp,
+                                       int32_t* block_idx, float* importance_out, const NsaDims* dims,
+                                       int n_cmp, int cmp_len, int cmp_stride, int sel_block, int n_sel,
+                                       int n_init, int n_local, int impl, void* stream) {
+  const int n_blk = n_cmp, block_size = cmp_len;
   NSA_CHECK_ARG(dims && q && lse_cmp && block_idx && (k_cmp || n_blk == 0), "null argument");
   NSA_CHECK_ARG(n_init >= 0 && n_local >= 0 && n_init < (1 << 18) && n_local < (1 << 18), "bad forced block counts");
   NSA_CHECK_ARG(dims->Hkv > 0 && dims->Hq % dims->Hkv == 0, "Hq must be a multiple of Hkv");
   NSA_CHECK_ARG(block_size > 0 && n_sel > 0 && n_blk >= 0, "bad block_size/n_sel/n_blk");
+  NSA_CHECK_ARG(cmp_stride > 0 && cmp_stride <= cmp_len && cmp_len % cmp_stride == 0 && sel_block > 0 &&
+                sel_block % cmp_stride == 0, "summary length and selection block must be multiples of the stride");
+  const bool aligned = cmp_len == cmp_stride && cmp_stride == sel_block;
+  const int n_sblk = (dims->T + sel_block - 1) / sel_block;
+  const int imp_cols = aligned ? n_blk : n_sblk;     // the aligned call keeps its [.., n_blk] layout
   const int D = dims->D;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t units = (size_t)dims->B * dims->Hkv * dims->T;
   if (units == 0) return NSA_OK;
   if (impl != NSA_IMPL_SIMT) {
-    if (tc_topn_ok(*dims, n_blk, n_sel))
+    if (tc_topn_ok(*dims, n_blk, n_sel, cmp_len, cmp_stride, sel_block))
       return tc_topn(q, k_cmp, lse_cmp, block_idx, importance_out, *dims, n_blk, block_size, n_sel, n_init,
-                     n_local, st);
+                     n_local, cmp_stride, sel_block, imp_cols, st);
     if (impl == NSA_IMPL_TC) {
       set_error("scoring shape not served by the tcgen05 kernel");
       return NSA_ERR_UNSUPPORTED;
     }
   }
-  const size_t sm = (size_t)4 * (D + n_blk + 1) * sizeof(float);
+  const size_t sm = (size_t)4 * (D + n_blk + n_sblk + 1) * sizeof(float);
   NSA_CHECK_ARG(sm <= 200 * 1024, "n_blk %d too large for the scoring kernel", n_blk);
   const float scale = 1.0f / sqrtf((float)D);
   const unsigned grid = blocks_for(units, 4);
@@ -996,7 +1026,7 @@ extern "C" int nsa_topn_blocks_forced(const void* q, const void* k_cmp, const fl
     KernelScope ks("topn_kernel", st);                                                          \
     topn_kernel<TT, DD><<<grid, 128, sm, st>>>((const TT*)q, (const TT*)k_cmp, lse_cmp,         \
         block_idx, importance_out, dims->B, dims->Hq, dims->Hkv, dims->T, n_blk, block_size,    \
-        n_sel, n_init, n_local, scale);                                                         \
+        n_sel, n_init, n_local, scale, cmp_stride, sel_block, n_sblk, imp_cols);                \
   } while (0)
   if (dims->dtype == NSA_DTYPE_BF16) {
     switch (D) {

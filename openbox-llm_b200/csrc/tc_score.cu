@@ -21,6 +21,9 @@ struct ScoreArgs {
   float* imp_out;
   int* status;
   int B, Hq, Hkv, T, n_blk, G, Gp, nq, block_size, n_sel, n_qtiles, n_init, n_local;
+  // general geometry (lanes kernel): n_blk summaries of block_size tokens every `stride`; selection
+  // blocks of sel_block = r * stride tokens; overlap: block_size == 2 * stride; imp_out has imp_cols columns
+  int stride, sel_block, r, overlap, imp_cols;
   float scale_log2;
 #ifdef NSA_TRACE
   long long* trace;
@@ -317,10 +320,12 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   __syncthreads();
   if (*s_abort) return;
 
-  const int hi_last = min(p.n_blk, (t_last + 1) / p.block_size) - 1;
+  const int hi_last = cmp_visible(t_last, p.block_size, p.stride, p.n_blk) - 1;
   int n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
   const bool forcing = p.n_init > 0 || p.n_local > 0;
-  if (forcing) n_tiles = max(n_tiles, (t_last / p.block_size) / kKeys + 1);
+  // forced blocks are candidates whatever their importance: reach the tile whose lanes own the
+  // block that holds the last query
+  if (forcing) n_tiles = max(n_tiles, (p.r * (t_last / p.sel_block)) / kKeys + 1);
 
   float lv[kList];
   int li[kList];
@@ -338,8 +343,9 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t tmem = *s_tmem;
     const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
     const float lse2 = row_ok ? __ldg(p.lse + (size_t)(b * p.Hq + hkv * p.G + g) * p.T + t) * kLog2e : 0.f;
-    const int n_vis = t < p.T ? min(p.n_blk, (t + 1) / p.block_size) : 0;   // complete blocks query t sees
-    const int my_cur = t / p.block_size;
+    const int n_vis = t < p.T ? cmp_visible(t, p.block_size, p.stride, p.n_blk) : 0;   // summaries query t sees
+    const int my_cur = t / p.sel_block;              // selection block that holds t
+    float carry = 0.f;                               // last summary of the previous tile (overlap)
 
     auto load_k = [&](int i) {
       uint64_t* bar = bar_k + (i & 1);
@@ -416,21 +422,24 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           }
         }
       }
-      // lane g now holds blocks key0 + g * PER + k in v[k]
-      const int hq = min(kKeys - 1, n_vis - 1 - key0);                       // last complete block, tile-relative
-      const int hf = (forcing && t < p.T) ? min(kKeys - 1, my_cur - key0) : -1;
-      if (p.imp_out && t < p.T) {
-        float* out = p.imp_out + ((size_t)bh * p.T + t) * p.n_blk + key0 + g * PER;
-#pragma unroll
-        for (int k = 0; k < PER; ++k)
-          if (key0 + g * PER + k < p.n_blk) out[k] = (g * PER + k <= hq) ? v[k] : 0.f;
-      }
+      // lane g now holds the summaries key0 + g * PER + k in v[k].  A selection block is r
+      // consecutive summaries (plus, when the summaries overlap, the one before them); it is a
+      // candidate once its first summary is visible.
+      float prev = __shfl_up_sync(0xffffffffu, v[PER - 1], 1);
+      if (g == 0) prev = carry;
+      carry = __shfl_sync(0xffffffffu, v[PER - 1], (threadIdx.x & 31 & ~(GP - 1)) + GP - 1);
+      float* out = (p.imp_out && t < p.T) ? p.imp_out + ((size_t)bh * p.T + t) * p.imp_cols : nullptr;
+      float accb = 0.f;
 #pragma unroll
       for (int k = 0; k < PER; ++k) {
-        const int c = g * PER + k;
-        const int cj = key0 + c;
-        float cv = c <= hq ? v[k] : -1.f;
-        if (forcing && c <= hf) {              // cj <= my_cur
+        if ((k & (p.r - 1)) == 0) accb = p.overlap ? (k == 0 ? prev : v[k > 0 ? k - 1 : 0]) : 0.f;
+        accb += v[k];
+        if (((k + 1) & (p.r - 1)) != 0) continue;
+        const int cj = (key0 + g * PER + k) / p.r;                  // block index
+        const bool visible = max(0, p.r * cj - p.overlap) < n_vis;  // first overlapping summary
+        if (out && cj < p.imp_cols) out[cj] = visible ? accb : 0.f;
+        float cv = visible ? accb : -1.f;
+        if (forcing && cj <= my_cur && t < p.T) {
           if (cj < p.n_init) cv = kForcedInit - (float)cj;
           else if (cj > my_cur - p.n_local) cv = kForcedLocal - (float)(my_cur - cj);
         }
@@ -471,8 +480,8 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
   // importance columns no tile covered are zero
   if (p.imp_out && t < p.T) {
-    float* out = p.imp_out + ((size_t)bh * p.T + t) * p.n_blk;
-    for (int c = n_tiles * kKeys + g; c < p.n_blk; c += GP) out[c] = 0.f;
+    float* out = p.imp_out + ((size_t)bh * p.T + t) * p.imp_cols;
+    for (int c = n_tiles * kKeys / p.r + g; c < p.imp_cols; c += GP) out[c] = 0.f;
   }
 }
 
@@ -498,15 +507,23 @@ static int launch_score_lanes(const void* q, const void* k_cmp, const NsaDims& d
 
 }  // namespace tc
 
-bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel) {
+bool tc_topn_ok(const NsaDims& d, int n_blk, int n_sel, int cmp_len, int stride, int sel_block) {
   if (d.dtype != NSA_DTYPE_BF16 || (d.D != 64 && d.D != 128)) return false;
   if (n_sel < 1 || n_sel > 16 || n_blk < 1) return false;
   const int G = d.Hq / d.Hkv;
-  return G <= 32;   // at least 4 queries per tile, so the lanes of one query sit in one warp
+  if (G > 32) return false;   // at least 4 queries per tile, so the lanes of one query sit in one warp
+  if (cmp_len == stride && stride == sel_block) return true;
+  // summaries and selection blocks on different grids: the lane-exchange kernel only
+  const int gp = tc::group_pad(G);
+  if (gp != 4 && gp != 8 && gp != 16) return false;
+  if (stride <= 0 || sel_block % stride || cmp_len % stride) return false;
+  const int r = sel_block / stride, o = cmp_len / stride;
+  return (r & (r - 1)) == 0 && r <= tc::kKeys / gp && (o == 1 || o == 2);
 }
 
 int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_idx, float* imp_out,
-            const NsaDims& d, int n_blk, int block_size, int n_sel, int n_init, int n_local, cudaStream_t st) {
+            const NsaDims& d, int n_blk, int block_size, int n_sel, int n_init, int n_local, int stride,
+            int sel_block, int imp_cols, cudaStream_t st) {
   using namespace tc;
   ScoreArgs p;
   p.lse = lse; p.block_idx = block_idx; p.imp_out = imp_out;
@@ -515,6 +532,8 @@ int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_i
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.T = d.T; p.n_blk = n_blk;
   p.G = d.Hq / d.Hkv; p.Gp = group_pad(p.G); p.nq = kRows / p.Gp;
   p.block_size = block_size; p.n_sel = n_sel; p.n_init = n_init; p.n_local = n_local;
+  p.stride = stride; p.sel_block = sel_block; p.r = sel_block / stride;
+  p.overlap = block_size / stride - 1; p.imp_cols = imp_cols;
   p.n_qtiles = (d.T + p.nq - 1) / p.nq;
   p.scale_log2 = kLog2e / sqrtf((float)d.D);
 #ifdef NSA_TRACE

@@ -210,21 +210,28 @@ def _compress_bwd(x, intra, logits, proj, d_out, block_size, stride=None):
 
 @torch.no_grad()
 def topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, return_importance=False, n_init_blocks=0,
-                n_local_blocks=0):
+                n_local_blocks=0, cmp_len=None, cmp_stride=None):
     """Block scoring + top-n (nsa_model.py:343-355): block_idx [B,Hkv,T,n_sel] int32, ordered by
     (importance descending, index ascending), -1 where fewer than n_sel blocks are causally
     valid.  lse_cmp is the LSE of the compression branch for the same q, k_cmp.
-    n_init_blocks / n_local_blocks (not in the reference) put the first blocks and the most
-    recent blocks, the one holding t included, ahead of the scored ones."""
+    Not in the reference: n_init_blocks / n_local_blocks put the first blocks and the most
+    recent blocks, the one holding t included, ahead of the scored ones; cmp_len / cmp_stride
+    (default block_size) say that k_cmp are summaries of cmp_len tokens every cmp_stride tokens
+    while the selection blocks stay block_size tokens."""
     B, Hq, T, D = q.shape
-    Hkv, n_blk = k_cmp.shape[1], k_cmp.shape[2]
+    Hkv, n_cmp = k_cmp.shape[1], k_cmp.shape[2]
+    cl = int(block_size if cmp_len is None else cmp_len)
+    cs = int(cl if cmp_stride is None else cmp_stride)
+    aligned = cl == cs == int(block_size)
     q, k_cmp, lse_cmp = q.contiguous(), k_cmp.contiguous(), lse_cmp.contiguous()
     idx = torch.empty(B, Hkv, T, n_sel, device=q.device, dtype=torch.int32)
-    imp = torch.empty(B, Hkv, T, n_blk, device=q.device, dtype=torch.float32) if return_importance else None
+    cols = n_cmp if aligned else (T + int(block_size) - 1) // int(block_size)
+    imp = torch.empty(B, Hkv, T, cols, device=q.device, dtype=torch.float32) if return_importance else None
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
-    L.check(L.lib().nsa_topn_blocks_forced(L.ptr(q), L.ptr(k_cmp), L.ptr(lse_cmp), L.ptr(idx), L.ptr(imp),
-                                           d, n_blk, int(block_size), int(n_sel), int(n_init_blocks),
-                                           int(n_local_blocks), L.IMPL[_impl], L.stream()))
+    L.check(L.lib().nsa_topn_blocks_general(L.ptr(q), L.ptr(k_cmp), L.ptr(lse_cmp), L.ptr(idx), L.ptr(imp),
+                                            d, n_cmp, cl, cs, int(block_size), int(n_sel),
+                                            int(n_init_blocks), int(n_local_blocks), L.IMPL[_impl],
+                                            L.stream()))
     return (idx, imp) if return_importance else idx
 
 

@@ -523,3 +523,44 @@ def test_strided_compression_attention(c, geom):
             check(dk, dk_ref, dtype, impl + " dk", abs32=4e-3)
             check(dv, dv_ref, dtype, impl + " dv", abs32=4e-3)
     nsa.set_impl("auto")
+
+
+@pytest.mark.parametrize("forced", [(0, 0), (1, 2)], ids=lambda f: f"init{f[0]}local{f[1]}")
+@pytest.mark.parametrize("geom", [(32, 16, 64), (64, 32, 64), (16, 16, 64), (32, 32, 64)],
+                         ids=lambda g: f"len{g[0]}stride{g[1]}sel{g[2]}")
+@pytest.mark.parametrize("c", [REF_CONFIGS[2], TC_CONFIGS[0], TC_CONFIGS[1]], ids=cfg_id)
+def test_topn_blocks_general_geometry(c, geom, forced):
+    """Scoring when summaries (len, stride) and selection blocks (sel) sit on different grids:
+    the block importance is the oracle's mapping of the summary importance, the list is the
+    oracle's rule applied to the kernel's own block importance, and the selection kernels attend
+    the resulting lists."""
+    nsa = pkg()
+    l, d, lsel = geom
+    n_init, n_local = forced
+    T, S = c["T"], c["S"]
+    n_cmp = O.n_summaries(T, l, d)
+    for dtype in DTYPES:
+        t = make_inputs(c, dtype, seed=13, scale_qkv=False)
+        g = torch.Generator().manual_seed(14)
+        k_cmp = (torch.randn(c["B"], c["Hkv"], n_cmp, c["D"], generator=g) * 0.5).to(dtype).float()
+        q_d, k_d = dev(t["q"], dtype), dev(k_cmp, dtype)
+        imp_cmp_ref, _ = O.stream_importance(t["q"], k_cmp, l, stride=d)
+        imp_blk_ref, valid = O.block_importance(imp_cmp_ref, T, l, d, lsel)
+        for impl in _impls_for(c, dtype):
+            nsa.set_impl(impl)
+            _, lse = nsa.range_attn_forward(q_d, k_d, k_d, nsa.MODE_COMPRESS_STRIDED, d, l)
+            try:
+                idx, imp = nsa.topn_blocks(q_d, k_d, lse, lsel, S, return_importance=True,
+                                           n_init_blocks=n_init, n_local_blocks=n_local, cmp_len=l, cmp_stride=d)
+            except Exception as e:   # a grid the tcgen05 scorer does not serve when it is forced
+                assert impl == "tc" and "not served" in str(e), e
+                continue
+            imp = imp.cpu()
+            assert imp.shape == imp_blk_ref.shape
+            tol = 1e-5 if dtype == torch.float32 else 2e-3
+            assert (imp - imp_blk_ref * valid[None, None]).abs().max().item() <= tol
+            want = O.forced_topn(imp, valid, S, T, lsel, n_init, n_local)
+            assert (idx.cpu() == want).all(), f"{impl}: list differs from the rule on own importance"
+            o, _ = nsa.selection_forward_triton(q_d, dev(t["ks"], dtype), dev(t["vs"], dtype), idx, lsel,
+                                                return_lse=True) if lsel == c["block_size"] else (None, None)
+    nsa.set_impl("auto")
