@@ -24,7 +24,7 @@ class _Compressor(nn.Module):
 
 class NSAAttentionB200(nn.Module):
     def __init__(self, d_model, n_q_heads, n_kv_heads, block_size=16, n_selected_blocks=4,
-                 window=32, n_init_blocks=0, n_local_blocks=0):
+                 window=32, n_init_blocks=0, n_local_blocks=0, cmp_len=None, cmp_stride=None):
         super().__init__()
         assert n_q_heads % n_kv_heads == 0, "GQA needs n_q_heads divisible by n_kv_heads"
         self.d_model, self.Hq, self.Hkv = d_model, n_q_heads, n_kv_heads
@@ -32,6 +32,9 @@ class NSAAttentionB200(nn.Module):
         self.block_size, self.n_sel, self.window = block_size, n_selected_blocks, window
         # forced selection blocks (not in the reference module; 0, 0 reproduces it)
         self.n_init_blocks, self.n_local_blocks = n_init_blocks, n_local_blocks
+        # summaries of cmp_len tokens every cmp_stride tokens (default: the reference's block grid)
+        self.cmp_len = block_size if cmp_len is None else cmp_len
+        self.cmp_stride = self.cmp_len if cmp_stride is None else cmp_stride
         kv_dim = self.Hkv * self.dh
         self.q_proj = nn.Linear(d_model, self.Hq * self.dh, bias=False)
         self.k_cmp = nn.Linear(d_model, kv_dim, bias=False)
@@ -40,8 +43,8 @@ class NSAAttentionB200(nn.Module):
         self.v_slc = nn.Linear(d_model, kv_dim, bias=False)
         self.k_win = nn.Linear(d_model, kv_dim, bias=False)
         self.v_win = nn.Linear(d_model, kv_dim, bias=False)
-        self.comp_k = _Compressor(block_size, self.dh)
-        self.comp_v = _Compressor(block_size, self.dh)
+        self.comp_k = _Compressor(self.cmp_len, self.dh)
+        self.comp_v = _Compressor(self.cmp_len, self.dh)
         self.gate = nn.Linear(d_model, self.Hq * 3, bias=True)
         self.out_proj = nn.Linear(self.Hq * self.dh, d_model, bias=False)
 
@@ -61,6 +64,7 @@ class NSAAttentionB200(nn.Module):
                     v_logits=self.comp_v.pool_logits, v_proj=self.comp_v.proj.weight)
         out = nsa_attention(q, *kv, gate.to(q.dtype), self.block_size, self.n_sel, self.window,
                             block_idx=block_idx, compressor=comp, n_init_blocks=self.n_init_blocks,
-                            n_local_blocks=self.n_local_blocks)
+                            n_local_blocks=self.n_local_blocks, cmp_len=self.cmp_len,
+                            cmp_stride=self.cmp_stride)
         out = out.transpose(1, 2).contiguous().view(B, T, self.Hq * self.dh)
         return self.out_proj(out)

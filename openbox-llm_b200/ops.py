@@ -387,19 +387,21 @@ class _NSAAttention(torch.autograd.Function):
     def forward(ctx, q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
                 block_idx, forced, k_intra, k_logits, k_proj, v_intra, v_logits, v_proj):
         learned = k_intra is not None
+        n_init, n_local, cl, cs = forced          # cl, cs: length and stride of the summaries
         if learned:
             cp = [t.detach().float().contiguous() for t in
                   (k_intra, k_logits, k_proj, v_intra, v_logits, v_proj)]
-            k_cmp = _compress_fwd(kc, cp[0], cp[1], cp[2], block_size)
-            v_cmp = _compress_fwd(vc, cp[3], cp[4], cp[5], block_size)
+            k_cmp = _compress_fwd(kc, cp[0], cp[1], cp[2], cl, cs)
+            v_cmp = _compress_fwd(vc, cp[3], cp[4], cp[5], cl, cs)
         else:
+            assert cl == cs == block_size, "mean pooling is defined on the aligned grid only"
             cp = []
             k_cmp = _mean_pool_fwd(kc, block_size)
             v_cmp = _mean_pool_fwd(vc, block_size)
-        o_cmp, lse_cmp = range_attn_forward(q, k_cmp, v_cmp, MODE_COMPRESS, 0, block_size)
+        o_cmp, lse_cmp = range_attn_forward(q, k_cmp, v_cmp, MODE_COMPRESS_STRIDED, cs, cl)
         if block_idx is None:
-            block_idx = topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel,
-                                    n_init_blocks=forced[0], n_local_blocks=forced[1])
+            block_idx = topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, n_init_blocks=n_init,
+                                    n_local_blocks=n_local, cmp_len=cl, cmp_stride=cs)
         else:
             block_idx = block_idx.to(torch.int32).contiguous()
         o_slc, lse_slc = selection_forward_triton(q, ks, vs, block_idx, block_size, return_lse=True)
@@ -410,7 +412,7 @@ class _NSAAttention(torch.autograd.Function):
                               lse_cmp, lse_slc, lse_win, block_idx, *cp)
         ctx.cfg = (block_size, window, learned, gate_logits.dtype,
                    tuple(t.dtype for t in (k_intra, k_logits, k_proj, v_intra, v_logits, v_proj))
-                   if learned else None)
+                   if learned else None, cl, cs)
         ctx.mark_non_differentiable(block_idx)
         return out, block_idx
 
@@ -418,7 +420,7 @@ class _NSAAttention(torch.autograd.Function):
     def backward(ctx, d_out, _d_idx):
         (q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o_cmp, o_slc, o_win,
          lse_cmp, lse_slc, lse_win, block_idx, *cp) = ctx.saved_tensors
-        block_size, window, learned, gate_dtype, pdt = ctx.cfg
+        block_size, window, learned, gate_dtype, pdt, cl, cs = ctx.cfg
         T = q.shape[2]
         # gate backward as per-row statistics; the branch kernels apply the gate factor themselves
         B, Hq = q.shape[0], q.shape[1]
@@ -435,7 +437,7 @@ class _NSAAttention(torch.autograd.Function):
         fused = (_impl != "simt" and S > 0 and q.dtype == torch.bfloat16 and
                  tc_supported(B, Hq, ks.shape[1], T, q.shape[3], q.dtype, block_size))
         dq, dk_cmp, dv_cmp = range_attn_backward(q, k_cmp, v_cmp, o_cmp, lse_cmp, d_out,
-                                                 MODE_COMPRESS, 0, block_size, rs[0], rd[0],
+                                                 MODE_COMPRESS_STRIDED, cs, cl, rs[0], rd[0],
                                                  defer_dq=fused)
         dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
                                             rs[1], rd[1], defer_dq=fused)
@@ -445,7 +447,7 @@ class _NSAAttention(torch.autograd.Function):
         if fused:
             n_cmp = k_cmp.shape[2]
             d = L.dims(B, Hq, ks.shape[1], T, q.shape[3], L.dtype_code(q))
-            L.check(L.lib().nsa_dq_reduce3(d, n_cmp, int(block_size), int(block_size), S, int(block_size), int(window),
+            L.check(L.lib().nsa_dq_reduce3(d, n_cmp, int(cl), int(cs), S, int(block_size), int(window),
                                            L.ptr(dq) if n_cmp > 0 else None, L.ptr(dq2), L.ptr(dq3),
                                            L.ptr(dq_sum), L.stream()))
         else:
@@ -454,8 +456,8 @@ class _NSAAttention(torch.autograd.Function):
         dq = dq_sum
         pgrads = [None] * 6
         if learned:
-            dkc, a, b, c = _compress_bwd(kc, cp[0], cp[1], cp[2], dk_cmp, block_size)
-            dvc, d, e, f = _compress_bwd(vc, cp[3], cp[4], cp[5], dv_cmp, block_size)
+            dkc, a, b, c = _compress_bwd(kc, cp[0], cp[1], cp[2], dk_cmp, cl, cs)
+            dvc, d, e, f = _compress_bwd(vc, cp[3], cp[4], cp[5], dv_cmp, cl, cs)
             pgrads = [g.to(t) for g, t in zip((a, b, c, d, e, f), pdt)]
         else:
             dkc = _mean_pool_bwd(dk_cmp, T, block_size)
@@ -466,7 +468,7 @@ class _NSAAttention(torch.autograd.Function):
 
 def nsa_attention(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
                   block_idx=None, compressor=None, return_block_idx=False, n_init_blocks=0,
-                  n_local_blocks=0):
+                  n_local_blocks=0, cmp_len=None, cmp_stride=None):
     """Full NSA attention (pre out_proj) as one differentiable op.
 
     q [B,Hq,T,D]; kc..vw [B,Hkv,T,D]; gate_logits [B,Hq,T,3].  `compressor` is None for mean
@@ -474,10 +476,15 @@ def nsa_attention(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, win
     of the two BlockCompressor modules (nsa_model.py:180-181).  With block_idx=None the blocks
     are picked by the scorer (nsa_model.py:343-355 semantics, deterministic tie order);
     n_init_blocks / n_local_blocks force the first blocks and the most recent blocks into every
-    list ahead of the scored ones (the published NSA recipe; the reference has no such option)."""
+    list ahead of the scored ones (the published NSA recipe; the reference has no such option).
+    cmp_len / cmp_stride (learned pooling only; default block_size, the reference's grid) make
+    the summaries windows of cmp_len tokens every cmp_stride tokens, e.g. 32 / 16 with 64-token
+    selection blocks; the compressor parameters then have cmp_len positions."""
     cp = [None] * 6
     if compressor is not None:
         cp = [compressor[n] for n in ("k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj")]
+    cl = int(block_size if cmp_len is None else cmp_len)
+    cs = int(cl if cmp_stride is None else cmp_stride)
     out, idx = _NSAAttention.apply(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel,
-                                   window, block_idx, (int(n_init_blocks), int(n_local_blocks)), *cp)
+                                   window, block_idx, (int(n_init_blocks), int(n_local_blocks), cl, cs), *cp)
     return (out, idx) if return_block_idx else out

@@ -564,3 +564,43 @@ def test_topn_blocks_general_geometry(c, geom, forced):
             o, _ = nsa.selection_forward_triton(q_d, dev(t["ks"], dtype), dev(t["vs"], dtype), idx, lsel,
                                                 return_lse=True) if lsel == c["block_size"] else (None, None)
     nsa.set_impl("auto")
+
+
+@pytest.mark.parametrize("case", [(TC_CONFIGS[1], (32, 16), (1, 2)), (TC_CONFIGS[0], (32, 16), (0, 0)),
+                                  (TC_CONFIGS[2], (64, 32), (1, 1)), (REF_CONFIGS[1], (16, 8), (1, 2))],
+                         ids=["G8_32_16_forced", "G16_32_16", "G4_64_32_forced", "simt_16_8_forced"])
+def test_whole_op_general_geometry(case):
+    """nsa_attention with summaries of (len, stride) != selection block and forced blocks: the
+    published NSA recipe's geometry (32 / 16 / 64, initial block and local blocks forced).  The
+    list is checked by test_topn_blocks_general_geometry; here the oracle is fed the kernel's
+    list and everything else (output, every gradient) is compared."""
+    nsa = pkg()
+    c, (l, d), (n_init, n_local) = case
+    bs, W, S, D = c["block_size"], window_for(c), c["S"], c["D"]
+    g = torch.Generator().manual_seed(6)
+    comp = {}
+    for p in ("k", "v"):
+        comp[p + "_intra"] = 0.02 * torch.randn(l, D, generator=g)
+        comp[p + "_logits"] = 0.5 * torch.randn(l, generator=g)
+        comp[p + "_proj"] = torch.randn(D, D, generator=g) * D ** -0.5
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+    for dtype in DTYPES:
+        t = make_inputs(c, dtype, seed=15, scale_qkv=True)
+        for impl in _impls_for(c, dtype):
+            nsa.set_impl(impl)
+            ins = [dev(t[n], dtype).requires_grad_(True) for n in names]
+            comp_d = {k: v.cuda().requires_grad_(True) for k, v in comp.items()}
+            out, idx = nsa.nsa_attention(*ins, bs, S, W, compressor=comp_d, return_block_idx=True,
+                                         n_init_blocks=n_init, n_local_blocks=n_local, cmp_len=l, cmp_stride=d)
+            out.backward(dev(t["do"], dtype))
+            kw = dict(compressor=comp, cmp_len=l, cmp_stride=d)
+            fwd = O.stream_nsa_forward(*(t[n] for n in names), bs, S, W, block_idx=idx.cpu(), **kw)
+            g_ref = O.stream_nsa_backward(*(t[n] for n in names), bs, W, fwd, t["do"], **kw)
+            check(out, fwd["out"], dtype, impl + " op out", abs16=3e-2)
+            for n, x in zip(names, ins):
+                check(x.grad, g_ref[n], dtype, impl + " op d" + n, abs32=3e-3, abs16=3e-2)
+            for k in comp:
+                ma, rl = err(comp_d[k].grad, g_ref[k])
+                lim = 5e-3 if dtype == torch.float32 else 5e-2
+                assert rl <= lim or ma <= lim, f"{impl} d{k}: abs {ma:.3e} rel {rl:.3e}"
+    nsa.set_impl("auto")
