@@ -31,6 +31,10 @@ if ROOT not in sys.path:
 WORKLOADS = {
     # BASELINE config 4: the T=32K training shape of the headline metric
     "c4_t32k": dict(B=8, T=32768, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
+    # the same shape with the geometry BASELINE.json words (not expressible in the reference):
+    # summaries of 32 tokens every 16, block 0 and the two local blocks in every list
+    "c4_t32k_l32d16": dict(B=8, T=32768, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512,
+                           cmp_len=32, cmp_stride=16, n_init=1, n_local=2),
     # BASELINE config 2
     "c2_t8k": dict(B=4, T=8192, Hq=16, Hkv=1, D=128, block_size=64, n_sel=16, window=512),
     "tiny": dict(B=1, T=2048, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
@@ -48,7 +52,12 @@ COMP = ["k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj"]
 
 
 def config_of(args, w):
-    return dict(workload=args.workload, **w, compression="learned block pooling, stride = block",
+    cl = w.get("cmp_len") or w["block_size"]
+    cs = w.get("cmp_stride") or cl
+    return dict(workload=args.workload, **w,
+                compression=f"learned pooling, summaries of {cl} tokens every {cs}" +
+                            (" (the reference's grid)" if cl == cs == w["block_size"] else
+                             " (not expressible in the reference)"),
                 kv_tensors="six independent (kc,vc,ks,vs,kw,vw)",
                 l2="inputs (2.9 GB per step at c4_t32k) exceed the 126 MB L2")
 
@@ -76,8 +85,9 @@ def device_inputs(w, seed, device):
     t["do"] = mk(B, Hq, T, D)
     comp = {}
     for p in ("k", "v"):
-        comp[p + "_intra"] = 0.02 * torch.randn(bs, D, generator=g, device=device)
-        comp[p + "_logits"] = 0.02 * torch.randn(bs, generator=g, device=device)
+        cl = w.get("cmp_len") or bs
+        comp[p + "_intra"] = 0.02 * torch.randn(cl, D, generator=g, device=device)
+        comp[p + "_logits"] = 0.02 * torch.randn(cl, generator=g, device=device)
         bound = D ** -0.5                                   # nn.Linear default init range
         comp[p + "_proj"] = (torch.rand(D, D, generator=g, device=device) * 2 - 1) * bound
     return t, comp
@@ -87,7 +97,9 @@ def run_step(nsa, t, comp, w):
     ins = [t[n].detach().requires_grad_(True) for n in NAMES]
     cps = {k: v.detach().requires_grad_(True) for k, v in comp.items()}
     out, idx = nsa.nsa_attention(*ins, w["block_size"], w["n_sel"], w["window"], compressor=cps,
-                                 return_block_idx=True)
+                                 return_block_idx=True, n_init_blocks=w.get("n_init", 0),
+                                 n_local_blocks=w.get("n_local", 0), cmp_len=w.get("cmp_len"),
+                                 cmp_stride=w.get("cmp_stride"))
     grads = torch.autograd.grad(out, ins + [cps[k] for k in COMP], t["do"])
     return out, idx, grads
 
@@ -98,7 +110,10 @@ def attended(idx, w):
     T, bs, W = w["T"], w["block_size"], w["window"]
     tt = torch.arange(T, device=idx.device)
     units = idx.shape[0] * idx.shape[1]
-    n_cmp = int(torch.clamp((tt + 1) // bs, max=T // bs).sum().item()) * units
+    cl = w.get("cmp_len") or bs
+    cs = w.get("cmp_stride") or cl
+    n_sum = (T - cl) // cs + 1 if T >= cl else 0
+    n_cmp = int(torch.clamp((tt + 1 - cl) // cs + 1, min=0, max=n_sum).sum().item()) * units
     n_win = int(torch.clamp(tt + 1, max=W).sum().item()) * units
     i64 = idx.long()
     start = i64 * bs
@@ -164,10 +179,12 @@ def cpu_reference_pass(w, rows, threads, seed=0):
     do = torch.randn(1, G, rows, D, generator=g)
     idx = O.make_block_idx_recent(1, 1, T, bs, w["n_sel"])
     t0 = time.perf_counter()
-    k_cmp = O.ref_block_mean_pool(kv[0], bs)
-    v_cmp = O.ref_block_mean_pool(kv[1], bs)
-    n_blk = T // bs
-    fns = [(k_cmp, v_cmp, lambda a, b: O.compress_keep(r0 + a, r0 + b, n_blk, bs)),
+    cl = w.get("cmp_len") or bs
+    cs = w.get("cmp_stride") or cl
+    k_cmp = O._windows(kv[0], cl, cs).mean(dim=-2)        # uniform pooling over each summary window
+    v_cmp = O._windows(kv[1], cl, cs).mean(dim=-2)
+    n_blk = k_cmp.shape[2]
+    fns = [(k_cmp, v_cmp, lambda a, b: O.compress_keep(r0 + a, r0 + b, n_blk, cl, cs)),
            (kv[2], kv[3], lambda a, b: O.selection_keep(idx, r0 + a, r0 + b, T, bs)),
            (kv[4], kv[5], lambda a, b: O.window_keep(r0 + a, r0 + b, T, w["window"]))]
     outs = [O.stream_attn_forward(q, k, v, fn, chunk=256) for k, v, fn in fns]
@@ -354,7 +371,9 @@ def main():
     row = G * D * 2                                        # the G head rows of one query
     t1 = torch.arange(T_)
     win_slots = int(((t1 >> 6) - (torch.clamp(t1 - w["window"] + 1, min=0) >> 6) + 1).sum().item())
-    cmp_slots = int(((torch.clamp((t1 + 1) // w["block_size"], max=T_ // w["block_size"]) + 63) // 64).sum().item())
+    cl_, cs_ = (w.get("cmp_len") or w["block_size"]), (w.get("cmp_stride") or w.get("cmp_len") or w["block_size"])
+    n_sum_ = (T_ - cl_) // cs_ + 1 if T_ >= cl_ else 0
+    cmp_slots = int(((torch.clamp((t1 + 1 - cl_) // cs_ + 1, min=0, max=n_sum_) + 63) // 64).sum().item())
     bytes_tab = {
         "sel_combine_kernel": n_pairs * (row + G * 12) + B_ * Hkv_ * T_ * S_ * 4 + full + B_ * Hq_ * T_ * 4,
         "dq_reduce_slc": n_pairs * row + B_ * Hkv_ * T_ * S_ * 4 + full,

@@ -361,6 +361,34 @@ __global__ void compress_dx_kernel(const float* __restrict__ d_pooled, const flo
   dx[i] = from_float<T>(acc);
 }
 
+// the same for bf16 rows of D = 8 * k elements: one thread per 8 columns, 16-byte stores
+__global__ void compress_dx_vec_kernel(const float* __restrict__ d_pooled, const float* __restrict__ logits,
+                                       __nv_bfloat16* __restrict__ dx, int T_, int D, int bs, int stride,
+                                       int n_blk, size_t n_vec) {
+  extern __shared__ float w[];
+  pool_weights(logits, w, bs);
+  __syncthreads();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const int VL = D >> 3;
+  const int vl = (int)(i % VL);
+  const int pos = (int)((i / VL) % T_);
+  const size_t bh = i / ((size_t)VL * T_);
+  const int j_hi = min(n_blk - 1, pos / stride);
+  const int j_lo = max(0, (pos - bs + stride) / stride);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = j_lo; j <= j_hi; ++j) {
+    const float wj = w[pos - j * stride];
+    const float4 lo = *reinterpret_cast<const float4*>(d_pooled + (bh * n_blk + j) * D + vl * 8);
+    const float4 hi = *reinterpret_cast<const float4*>(d_pooled + (bh * n_blk + j) * D + vl * 8 + 4);
+    acc[0] = fmaf(wj, lo.x, acc[0]); acc[1] = fmaf(wj, lo.y, acc[1]); acc[2] = fmaf(wj, lo.z, acc[2]); acc[3] = fmaf(wj, lo.w, acc[3]);
+    acc[4] = fmaf(wj, hi.x, acc[4]); acc[5] = fmaf(wj, hi.y, acc[5]); acc[6] = fmaf(wj, hi.z, acc[6]); acc[7] = fmaf(wj, hi.w, acc[7]);
+  }
+  uint4 o;
+  o.x = pack2(acc[0], acc[1]); o.y = pack2(acc[2], acc[3]); o.z = pack2(acc[4], acc[5]); o.w = pack2(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(dx + i * 8) = o;
+}
+
 // tail tokens past the last complete block get zero gradient
 template <typename T>
 __global__ void zero_tail_kernel(T* __restrict__ dx, int T_, int D, int t_first, size_t n_bh) {
@@ -946,7 +974,9 @@ extern "C" int nsa_block_compress_strided_bwd(const void* x, const float* intra_
     if (n && rows == 0) NSA_CUDA_OK(cudaMemsetAsync(dx, 0, n * (dtype == NSA_DTYPE_BF16 ? 2 : 4), st));
     if (n && rows) {
       KernelScope ks("compress_dx_kernel", st);
-      if (dtype == NSA_DTYPE_BF16)
+      if (dtype == NSA_DTYPE_BF16 && D % 8 == 0)
+        compress_dx_vec_kernel<<<blocks_for(n / 8, 256), 256, block_size * sizeof(float), st>>>(d_pooled, pool_logits, (__nv_bfloat16*)dx, T, D, block_size, stride, n_blk, n / 8);
+      else if (dtype == NSA_DTYPE_BF16)
         compress_dx_kernel<<<blocks_for(n, 256), 256, block_size * sizeof(float), st>>>(d_pooled, pool_logits, (__nv_bfloat16*)dx, T, D, block_size, stride, n_blk, n);
       else
         compress_dx_kernel<<<blocks_for(n, 256), 256, block_size * sizeof(float), st>>>(d_pooled, pool_logits, (float*)dx, T, D, block_size, stride, n_blk, n);
