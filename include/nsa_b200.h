@@ -228,6 +228,18 @@ int nsa_gate_combine_bwd_rows(const void* o_cmp, const void* o_slc, const void* 
  * autograd forms when one q feeds three branch Functions (nsa_model.py:330,338,360). */
 int nsa_sum3(const void* a, const void* b, const void* c, void* out, size_t n, int dtype, void* stream);
 
+/* ---- optimizer step of the data-parallel training step ---------------------------------------
+ * Replace torch.nn.utils.clip_grad_norm_ + torch.optim.AdamW of the reference's step
+ * (train.py:148-149, :262-264) on flat fp32 buffers, with no host synchronisation in between.
+ * nsa_sumsq_f32 adds sum(x^2) to *accum (device, zeroed by the caller).  nsa_adamw_step_f32 scales
+ * the gradient by grad_scale (1 / world size after a summing all-reduce) and by the clip factor
+ * min(1, max_norm / (grad_scale * sqrt(*sumsq) + 1e-6)) (sumsq NULL or max_norm <= 0: no clip), then
+ * applies AdamW with decoupled weight decay and bias correction for `step` (counted from 1). */
+int nsa_sumsq_f32(const float* x, size_t n, float* accum, void* stream);
+int nsa_adamw_step_f32(float* p, const float* g, float* m, float* v, size_t n, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, int step, const float* sumsq,
+                       float max_norm, float grad_scale, void* stream);
+
 /* ---- accounting ------------------------------------------------------------------------------
  * nsa_launch_count: kernels launched by this library in this process so far.
  * nsa_profile_enable(1) makes every later kernel launch be bracketed by CUDA events on its own

@@ -23,7 +23,7 @@ class NsaError(RuntimeError):
 
 
 _lib = None
-_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_vp, _i, _sz, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_float
 _dp = ctypes.POINTER(NsaDims)
 
 # every symbol the header declares, with its signature
@@ -60,6 +60,8 @@ SIGNATURES = {
     "nsa_topn_blocks_general": (_i, [_vp] * 5 + [_dp] + [_i] * 8 + [_vp]),
     "nsa_gate_combine_bwd_rows": (_i, [_vp] * 8 + [_dp, _vp]),
     "nsa_sum3": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "nsa_sumsq_f32": (_i, [_vp, _sz, _vp, _vp]),
+    "nsa_adamw_step_f32": (_i, [_vp] * 4 + [_sz] + [_f] * 5 + [_i, _vp, _f, _f, _vp]),
     "nsa_dq_reduce3": (_i, [_dp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "nsa_gate_combine_fwd": (_i, [_vp] * 5 + [_dp, _vp]),
     "nsa_gate_combine_bwd": (_i, [_vp] * 9 + [_dp, _vp]),

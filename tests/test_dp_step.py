@@ -1,0 +1,135 @@
+"""Data-parallel training step: the bucketed gradient all-reduce on two gloo ranks (CPU), and on a
+GPU the clip + AdamW kernels against torch and the whole step against the reference's recipe
+(autocast forward, backward, clip_grad_norm_, torch.optim.AdamW: train.py:148-149, :256-264)."""
+import copy
+import importlib
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+DP = importlib.import_module("openbox-llm_b200.dp_step")
+
+
+def _mlp(seed):
+    torch.manual_seed(seed)
+    return torch.nn.Sequential(torch.nn.Linear(12, 32), torch.nn.Tanh(), torch.nn.Linear(32, 32),
+                               torch.nn.Tanh(), torch.nn.Linear(32, 3))
+
+
+def test_flat_views_and_bucket_layout():
+    m = _mlp(0)
+    before = [p.detach().clone() for p in m.parameters()]
+    flat = DP.FlatParams(m)
+    b = DP.GradBuckets(flat, bucket_bytes=1024)
+    assert all(torch.equal(p.detach(), q) for p, q in zip(m.parameters(), before))
+    # the ranges tile the buffer from the end backwards, every parameter in exactly one bucket
+    assert b.ranges[0][1] == flat.numel and b.ranges[-1][0] == 0
+    assert all(b.ranges[i][0] == b.ranges[i + 1][1] for i in range(len(b.ranges) - 1))
+    assert sum(b.pending0) == len(flat.params)
+    flat.zero_grad(); b.start()
+    m(torch.randn(4, 12)).square().sum().backward()
+    b.finish()
+    assert b.pending == [0] * len(b.ranges)
+    ref = copy.deepcopy(m)
+    for p in ref.parameters():
+        p.grad = None
+    # the flat gradient is what autograd wrote through the views
+    for p, off in zip(flat.params, flat.offsets):
+        assert torch.equal(flat.grad[off:off + p.numel()].view(p.shape), p.grad)
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    m = _mlp(0)                                   # identical replicas
+    flat = DP.FlatParams(m)
+    b = DP.GradBuckets(flat, bucket_bytes=512)    # several buckets
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(6, 12, generator=g)           # each rank its own micro-batch
+    flat.zero_grad(); b.start()
+    m(x).square().mean().backward()
+    b.finish()
+    out.put((rank, x, flat.grad.clone() / world))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_average_their_gradients():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted([out.get(timeout=120) for _ in range(2)], key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # both ranks hold the same averaged gradient = gradient of the mean loss over both micro-batches
+    assert torch.equal(got[0][2], got[1][2])
+    m = _mlp(0)
+    loss = sum(m(x).square().mean() for _, x, _ in got) / 2
+    loss.backward()
+    want = torch.cat([torch.nn.functional.pad(p.grad.reshape(-1), (0, (-p.numel()) % 4)) for p in m.parameters()])
+    assert (got[0][2] - want).abs().max().item() <= 1e-6
+
+
+@pytest.mark.gpu
+def test_fused_clip_adamw_matches_torch():
+    m = _mlp(1).cuda()
+    ref = copy.deepcopy(m)
+    flat = DP.FlatParams(m)
+    opt = DP.FusedAdamW(flat, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, grad_clip=0.5)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for step in range(6):
+        x = torch.randn(16, 12, generator=g, device="cuda") * (3.0 if step % 2 else 0.1)   # clipped and unclipped steps
+        flat.zero_grad()
+        m(x).square().sum().backward()
+        opt.step()
+        ropt.zero_grad(set_to_none=True)
+        ref(x).square().sum().backward()
+        norm = torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        ropt.step()
+        assert abs(opt.grad_norm() - float(norm)) <= 1e-4 * max(1.0, float(norm))
+        for p, q in zip(m.parameters(), ref.parameters()):
+            assert (p - q).abs().max().item() <= 2e-6, step
+
+
+@pytest.mark.gpu
+def test_training_step_matches_the_reference_recipe():
+    M = importlib.import_module("openbox-llm_b200.model")
+    torch.manual_seed(0)
+    kw = dict(vocab_size=512, d_model=128, n_layers=2, n_q_heads=4, n_kv_heads=2, max_seq_len=256,
+              block_size=64, n_selected_blocks=2, window=64)
+    a = M.NSATransformerB200(**kw).cuda()
+    b = copy.deepcopy(a)
+    assert a.lm_head.weight is a.tok_emb.weight and b.lm_head.weight is b.tok_emb.weight
+    step = DP.DataParallelStep(a, lr=1e-3, weight_decay=0.1, grad_clip=1.0)
+    ropt = torch.optim.AdamW(b.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    g = torch.Generator().manual_seed(1)
+    losses = []
+    for _ in range(3):
+        idx = torch.randint(0, 512, (2, 256), generator=g).cuda()
+        tgt = torch.randint(0, 512, (2, 256), generator=g).cuda()
+        la = step.step(idx, tgt)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            _, lb = b(idx, tgt)
+        ropt.zero_grad(set_to_none=True)
+        lb.backward()
+        torch.nn.utils.clip_grad_norm_(b.parameters(), 1.0)
+        ropt.step()
+        losses.append((float(la), float(lb.detach())))
+    for la, lb in losses:
+        assert abs(la - lb) <= 2e-3 * max(1.0, abs(lb)), losses
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert (p - q).abs().max().item() <= 2e-3, n
+    # a snapshot with the reference's key names loads (nsa_model.py:455-478 module tree)
+    keys = set(a.state_dict())
+    assert {"tok_emb.weight", "pos_emb.weight", "blocks.0.ln1.weight", "blocks.0.attn.q_proj.weight",
+            "blocks.0.attn.comp_k.intra_pos", "blocks.0.attn.gate.bias", "blocks.1.ffn.2.weight",
+            "ln_f.bias", "lm_head.weight"} <= keys
