@@ -234,19 +234,121 @@ def reference_arm(args, w, rank):
     print(json.dumps(line))
 
 
+MODEL_C5 = dict(vocab_size=50304, d_model=768, n_layers=12, n_q_heads=12, n_kv_heads=4,
+                max_seq_len=4096, ffn_mult=4, block_size=64, n_selected_blocks=16, window=512)
+
+
+def model_workload(args, rank, world, local_rank):
+    """BASELINE config 5: one optimizer step of the 12-layer model (d_model 768, 12 query / 4 kv
+    heads, head dim 64, T=4096, micro-batch 8 per GPU; the reference's ~150 M configuration),
+    replicas kept in step by the bucketed NCCL gradient all-reduce of dp_step.py.  Token ids and
+    targets are uniform random (no corpus here), uploaded from pinned host memory every step;
+    the loss is read back every step in the end-to-end leg."""
+    assert args.warmup >= 3, "timing rules: at least 3 warm-up steps"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    L = importlib.import_module("openbox-llm_b200._lib")
+    M = importlib.import_module("openbox-llm_b200.model")
+    DP = importlib.import_module("openbox-llm_b200.dp_step")
+    torch.manual_seed(0)                                     # identical replicas
+    model = M.NSATransformerB200(**MODEL_C5).to(dev)
+    step = DP.DataParallelStep(model, lr=3e-4, weight_decay=0.1, grad_clip=1.0)
+    mb, T = 8, MODEL_C5["max_seq_len"]
+    g = torch.Generator().manual_seed(1234 + rank)           # every rank its own micro-batches
+    host = [(torch.randint(0, MODEL_C5["vocab_size"], (mb, T), generator=g).pin_memory(),
+             torch.randint(0, MODEL_C5["vocab_size"], (mb, T), generator=g).pin_memory()) for _ in range(4)]
+    devb = [(a.to(dev), b.to(dev)) for a, b in host]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step.step(*devb[i % 4])
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ
+                           else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    L.lib().nsa_profile_enable(1)
+    launches0 = L.lib().nsa_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        loss = step.step(*devb[i % 4])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = L.lib().nsa_launch_count() - launches0
+    prof = L.profile_summary()
+    L.lib().nsa_profile_enable(0)
+    clocks = sampler.stop()
+    assert L.lib().nsa_device_status(None) == 0, L.lib().nsa_last_error()
+    # end to end: ids and targets from pinned host memory, the loss back to the host, every step
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    f0.record()
+    last = 0.0
+    for i in range(args.steps):
+        a, b = host[i % 4]
+        last = float(step.step(a.to(dev, non_blocking=True), b.to(dev, non_blocking=True)))
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+    if dist is not None:
+        tt = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+    if rank == 0:
+        tokens = world * mb * T * args.steps
+        total_ms = sum(v[1] for v in prof.values()) or 1.0
+        n_params = sum(p.numel() for p in step.flat.params)
+        line = {"metric": "optimizer-step tokens/s of the 12-layer NSA model (BASELINE config 5)",
+                "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": dict(workload="c5_model", **MODEL_C5, micro_batch_per_gpu=mb, params=n_params,
+                               optimizer="AdamW betas (0.9, 0.95) wd 0.1, clip 1.0, fp32 parameters, bf16 autocast",
+                               parallelism=f"dp{world}: bucketed NCCL all-reduce overlapping backward",
+                               l2="activations of a step exceed the 126 MB L2"),
+                "clocks": clocks, "final_loss": last,
+                "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s",
+                        "h2d_bytes_per_step": 2 * mb * T * 8, "d2h_bytes_per_step": 4},
+                "gpu_launches": int(launches),
+                "nsa_kernel_share_of_step": total_ms / ms,
+                "kernels": {k: {"launches": v[0], "ms": round(v[1], 3)} for k, v in
+                            sorted(prof.items(), key=lambda kv: -kv[1][1])[:12]},
+                "roofline": None, "cpu_baseline": None,
+                "peak_hbm_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c4_t32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4_t32k", choices=sorted(WORKLOADS) + ["c5_model"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload == "c5_model":
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "the CPU arm times the attention op; the model workload has no CPU arm"}))
+            return
+        model_workload(args, rank, world, local_rank)
+        return
+    w = WORKLOADS[args.workload]
     if args.impl == "reference":
         reference_arm(args, w, rank)
         return
