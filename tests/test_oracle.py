@@ -185,3 +185,64 @@ def test_generators_and_counts():
     assert n["slc"] == int(keep.sum())
     assert n["win"] == 2 * int(O.window_keep(0, 256, 256, 50).sum())
     assert n["cmp"] == 2 * int(O.compress_keep(0, 256, 8, 32).sum())
+
+
+# ---------------------------------------------------------------------------------------------
+# The generalised geometry (summaries of len tokens every stride, forced blocks) has no reference
+# code: what can be checked on the CPU is that each restatement collapses to its pinned form on
+# the reference's grid, that the analytic backward agrees with autograd, and the rule's invariants.
+# ---------------------------------------------------------------------------------------------
+def test_generalised_forms_collapse_to_the_pinned_ones():
+    g = torch.Generator().manual_seed(0)
+    B, H, T, D, bs = 2, 2, 200, 16, 32
+    x = torch.randn(B, H, T, D, generator=g)
+    ip, pl, W = 0.1 * torch.randn(bs, D, generator=g), torch.randn(bs, generator=g), torch.randn(D, D, generator=g)
+    assert O.n_summaries(T, bs, bs) == T // bs and O.n_summaries(10, bs, 8) == 0
+    assert torch.equal(O.ref_block_compressor(x, ip, pl, W, bs), O.ref_block_compressor(x, ip, pl, W, bs, bs))
+    assert torch.equal(O.compress_keep(0, T, T // bs, bs), O.compress_keep(0, T, T // bs, bs, bs))
+    imp = torch.rand(B, H, T, T // bs, generator=g) * O.compress_keep(0, T, T // bs, bs)[None, None]
+    valid = O.compress_keep(0, T, T // bs, bs)
+    ib, vb = O.block_importance(imp, T, bs, bs, bs)
+    assert torch.equal(ib[..., :T // bs], imp) and torch.equal(vb[:, :T // bs], valid) and not vb[:, T // bs:].any()
+    assert torch.equal(O.forced_topn(ib, vb, 3, T, bs, 0, 0), O.canonical_topn(imp, valid, 3))
+
+
+@pytest.mark.parametrize("stride", [32, 16, 8])
+def test_strided_compressor_backward_is_autograd(stride):
+    g = torch.Generator().manual_seed(1)
+    B, H, T, D, bs = 1, 2, 150, 8, 32
+    x = torch.randn(B, H, T, D, generator=g, requires_grad=True)
+    ps = [(0.1 * torch.randn(bs, D, generator=g)).requires_grad_(True), torch.randn(bs, generator=g).requires_grad_(True),
+          torch.randn(D, D, generator=g).requires_grad_(True)]
+    y = O.ref_block_compressor(x, *ps, bs, stride)
+    assert y.shape[2] == O.n_summaries(T, bs, stride)
+    do = torch.randn(y.shape, generator=g)
+    want = torch.autograd.grad(y, [x] + ps, do)
+    got = O.compressor_backward(x.detach(), *(p.detach() for p in ps), bs, do, stride)
+    for a, b in zip(got, want):
+        assert (a - b).abs().max().item() <= 1e-5
+
+
+def test_block_importance_and_forced_lists():
+    g = torch.Generator().manual_seed(2)
+    T, l, d, lsel, S = 400, 32, 16, 64, 6
+    n_cmp = O.n_summaries(T, l, d)
+    keep = O.compress_keep(0, T, n_cmp, l, d)
+    imp = torch.rand(1, 1, T, n_cmp, generator=g) * keep[None, None]
+    ib, vb = O.block_importance(imp, T, l, d, lsel)
+    r, o = lsel // d, l // d
+    for b in range(ib.shape[-1]):
+        j0, j1 = max(0, r * b - o + 1), min(n_cmp - 1, r * b + r - 1)
+        assert torch.allclose(ib[..., b], imp[..., j0:j1 + 1].sum(-1))
+        # a block is a candidate exactly when its first overlapping summary is visible
+        assert torch.equal(vb[:, b], keep[:, j0] if j0 < n_cmp else torch.zeros(T, dtype=torch.bool))
+    idx = O.forced_topn(ib, vb, S, T, lsel, 1, 2)
+    t = torch.arange(T)
+    cur = (t // lsel).view(1, 1, T, 1)
+    assert (idx[..., 0] == 0).all()                                  # block 0 first, always
+    assert (idx == cur).any(-1).all()                                # the block holding t is listed
+    assert ((idx == cur - 1).any(-1) | (cur[..., 0] == 0)).all()     # and the one before it
+    assert (idx <= cur).all()                                        # nothing from the future
+    for row in idx.view(-1, S)[::37]:                                # no block twice
+        kept = row[row >= 0]
+        assert kept.unique().numel() == kept.numel()
