@@ -43,9 +43,9 @@ METRIC = "NSA fwd+bwd tokens/s per B200 at T=32K bf16; % of tensor-pipe peak"
 
 # DRAM bytes (read + write) per launch at c4_t32k, one-pass ncu capture
 # (profiles/dram_traffic_pair_kernels_c4_t32k.md)
-TRAFFIC_C4 = {"tc_bwd_slc": 32.90e9, "tc_bwd_win": 13.93e9, "tc_bwd_cmp": 15.08e9,
-              "tc_fwd_slc_pairs": 24.13e9, "sel_combine_kernel": 18.80e9,
-              "dq_reduce_slc": 18.00e9, "dq_reduce_win": 10.63e9, "dq_reduce_cmp": 5.88e9}
+TRAFFIC_C4 = {"tc_bwd_slc": 37.62e9, "tc_bwd_win": 13.80e9, "tc_bwd_cmp": 15.09e9,
+              "tc_fwd_slc_pairs": 26.63e9, "sel_combine_kernel": 18.81e9, "dq_reduce3": 32.39e9,
+              "tc_fwd_win": 2.38e9, "tc_fwd_cmp": 2.14e9, "tc_score_topn": 1.12e9}
 
 NAMES = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
 COMP = ["k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj"]
@@ -336,6 +336,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c4_t32k", choices=sorted(WORKLOADS) + ["c5_model"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the extra leg on the 32/16/64 geometry")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -533,7 +534,7 @@ def main():
     # the reference cannot express and nothing of it pins: a few device-resident steps, reported
     # beside the headline, never instead of it
     line["also"] = None
-    if world == 1 and args.workload == "c4_t32k":
+    if world == 1 and args.workload == "c4_t32k" and not args.no_also:
         del t, comp, out, idx, grads, dbufs, host_in, host_out, host_outs
         torch.cuda.empty_cache()
         w2 = WORKLOADS["c4_t32k_l32d16"]
