@@ -398,20 +398,45 @@ __global__ void sel_stats_kernel(const int32_t* __restrict__ block_idx, unsigned
   if (lane == 0 && cnt) atomicAdd(stats, (unsigned long long)cnt);
 }
 
-// one thread per (batch, kv head, block): its row tiles in chunks of kSelChunkTiles, one work
-// item each (at least one, so that a block nobody lists still gets its zero gradients)
+// One CTA walks the (batch, kv head, block) entries in order: each block's row tiles in chunks of
+// kSelChunkTiles, one work item each (at least one, so that a block nobody lists still gets its
+// zero gradients).  An exclusive scan of the chunk counts places the items, so the list is in
+// (batch, kv head, block, chunk) order: CTAs that run together work on one (batch, kv head) and
+// share its q rows in L2.
 __global__ void sel_worklist_kernel(const int32_t* __restrict__ offsets, int n_ktiles, int units, int nq,
                                     SelWorkHeader* __restrict__ work, int max_items) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= units * n_ktiles) return;
-  const int bh = idx / n_ktiles, j = idx % n_ktiles;
-  const int n_q = offsets[(size_t)bh * (n_ktiles + 1) + j + 1] - offsets[(size_t)bh * (n_ktiles + 1) + j];
-  const int n_rt = (n_q + nq - 1) / nq;
-  const int n_chunks = max(1, (n_rt + kSelChunkTiles - 1) / kSelChunkTiles);
-  const int base = atomicAdd(&work->n_items, n_chunks);
+  __shared__ int part[1024];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
   int4* items = reinterpret_cast<int4*>(work + 1);
-  for (int c = 0; c < n_chunks && base + c < max_items; ++c)
-    items[base + c] = make_int4(bh, j, c * kSelChunkTiles, n_chunks);
+  const int total = units * n_ktiles;
+  for (int base0 = 0; base0 < total; base0 += 1024) {
+    const int idx = base0 + threadIdx.x;
+    int n_chunks = 0, bh = 0, j = 0;
+    if (idx < total) {
+      bh = idx / n_ktiles; j = idx % n_ktiles;
+      const int n_q = offsets[(size_t)bh * (n_ktiles + 1) + j + 1] - offsets[(size_t)bh * (n_ktiles + 1) + j];
+      const int n_rt = (n_q + nq - 1) / nq;
+      n_chunks = max(1, (n_rt + kSelChunkTiles - 1) / kSelChunkTiles);
+    }
+    part[threadIdx.x] = n_chunks;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      const int v = threadIdx.x >= o ? part[threadIdx.x - o] : 0;
+      __syncthreads();
+      part[threadIdx.x] += v;
+      __syncthreads();
+    }
+    const int incl = part[threadIdx.x] + carry;
+    const int first = incl - n_chunks;
+    for (int c = 0; c < n_chunks && first + c < max_items; ++c)
+      items[first + c] = make_int4(bh, j, c * kSelChunkTiles, n_chunks);
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = incl;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) work->n_items = min(carry, max_items);
 }
 
 size_t sel_work_max_items(size_t units, int n_ktiles, size_t cap_pairs, int nq) {
@@ -428,7 +453,7 @@ int sel_build_worklist(const int32_t* offsets, int n_ktiles, size_t units, size_
   const size_t n = units * n_ktiles;
   if (n == 0) return NSA_OK;
   KernelScope ks("sel_worklist_kernel", st);
-  sel_worklist_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+  sel_worklist_kernel<<<1, 1024, 0, st>>>(
       offsets, n_ktiles, (int)units, nq, (SelWorkHeader*)work,
       (int)sel_work_max_items(units, n_ktiles, cap_pairs, nq));
   NSA_LAUNCH_OK("sel_worklist_kernel");

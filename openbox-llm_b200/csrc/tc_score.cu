@@ -276,7 +276,7 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // which lane g holds the importance of the tile's blocks [g * 64/GP, (g+1) * 64/GP) and scans
 // exactly those for its top-16 list.  64 KB of shared memory: three CTAs per SM.
 // ------------------------------------------------------------------------------------------
-template <int D, int GP>
+template <int D, int GP, bool kAligned>
 __global__ void __launch_bounds__(128, 3)
 tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const ScoreArgs p) {
@@ -425,18 +425,23 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       // lane g now holds the summaries key0 + g * PER + k in v[k].  A selection block is r
       // consecutive summaries (plus, when the summaries overlap, the one before them); it is a
       // candidate once its first summary is visible.
-      float prev = __shfl_up_sync(0xffffffffu, v[PER - 1], 1);
-      if (g == 0) prev = carry;
-      carry = __shfl_sync(0xffffffffu, v[PER - 1], (threadIdx.x & 31 & ~(GP - 1)) + GP - 1);
+      // kAligned: summaries and blocks coincide (r = 1, no overlap), all of it folds away
+      const int r_ = kAligned ? 1 : p.r, ov_ = kAligned ? 0 : p.overlap;
+      float prev = 0.f;
+      if (!kAligned) {
+        prev = __shfl_up_sync(0xffffffffu, v[PER - 1], 1);
+        if (g == 0) prev = carry;
+        carry = __shfl_sync(0xffffffffu, v[PER - 1], (threadIdx.x & 31 & ~(GP - 1)) + GP - 1);
+      }
       float* out = (p.imp_out && t < p.T) ? p.imp_out + ((size_t)bh * p.T + t) * p.imp_cols : nullptr;
       float accb = 0.f;
 #pragma unroll
       for (int k = 0; k < PER; ++k) {
-        if ((k & (p.r - 1)) == 0) accb = p.overlap ? (k == 0 ? prev : v[k > 0 ? k - 1 : 0]) : 0.f;
+        if ((k & (r_ - 1)) == 0) accb = ov_ ? (k == 0 ? prev : v[k > 0 ? k - 1 : 0]) : 0.f;
         accb += v[k];
-        if (((k + 1) & (p.r - 1)) != 0) continue;
-        const int cj = (key0 + g * PER + k) / p.r;                  // block index
-        const bool visible = max(0, p.r * cj - p.overlap) < n_vis;  // first overlapping summary
+        if (((k + 1) & (r_ - 1)) != 0) continue;
+        const int cj = (key0 + g * PER + k) / r_;                  // block index
+        const bool visible = max(0, r_ * cj - ov_) < n_vis;        // first overlapping summary
         if (out && cj < p.imp_cols) out[cj] = visible ? accb : 0.f;
         float cv = visible ? accb : -1.f;
         if (forcing && cj <= my_cur && t < p.T) {
@@ -481,7 +486,7 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   // importance columns no tile covered are zero
   if (p.imp_out && t < p.T) {
     float* out = p.imp_out + ((size_t)bh * p.T + t) * p.imp_cols;
-    for (int c = n_tiles * kKeys / p.r + g; c < p.imp_cols; c += GP) out[c] = 0.f;
+    for (int c = n_tiles * kKeys / (kAligned ? 1 : p.r) + g; c < p.imp_cols; c += GP) out[c] = 0.f;
   }
 }
 
@@ -499,9 +504,14 @@ static int launch_score_lanes(const void* q, const void* k_cmp, const NsaDims& d
   if (rc == NSA_OK) rc = make_map(&tm_k, k_cmp, d.D, n_blk, d.B * d.Hkv, kKeys, 1);
   if (rc != NSA_OK) return rc;
   const size_t smem = score_lanes_smem_bytes(d.D);
-  NSA_CUDA_OK(cudaFuncSetAttribute(tc_score_lanes_kernel<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   KernelScope ks("tc_score_topn", st);
-  tc_score_lanes_kernel<D, GP><<<dim3(p.n_qtiles, d.B * d.Hkv), 128, smem, st>>>(tm_q, tm_k, p);
+  if (p.r == 1 && p.overlap == 0) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_score_lanes_kernel<D, GP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tc_score_lanes_kernel<D, GP, true><<<dim3(p.n_qtiles, d.B * d.Hkv), 128, smem, st>>>(tm_q, tm_k, p);
+  } else {
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_score_lanes_kernel<D, GP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tc_score_lanes_kernel<D, GP, false><<<dim3(p.n_qtiles, d.B * d.Hkv), 128, smem, st>>>(tm_q, tm_k, p);
+  }
   return NSA_OK;
 }
 
