@@ -38,6 +38,9 @@ WORKLOADS = {
     # BASELINE config 2
     "c2_t8k": dict(B=4, T=8192, Hq=16, Hkv=1, D=128, block_size=64, n_sel=16, window=512),
     "tiny": dict(B=1, T=2048, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
+    # BASELINE config 3: forward only at long context, 64 query / 4 kv heads (value = forward tokens/s)
+    "c3_t32k_fwd": dict(B=1, T=32768, Hq=64, Hkv=4, D=128, block_size=64, n_sel=16, window=512, fwd_only=True),
+    "c3_t128k_fwd": dict(B=1, T=131072, Hq=64, Hkv=4, D=128, block_size=64, n_sel=16, window=512, fwd_only=True),
 }
 METRIC = "NSA fwd+bwd tokens/s per B200 at T=32K bf16; % of tensor-pipe peak"
 
@@ -94,6 +97,13 @@ def device_inputs(w, seed, device):
 
 
 def run_step(nsa, t, comp, w):
+    if w.get("fwd_only"):
+        with torch.no_grad():
+            out, idx = nsa.nsa_attention(*(t[n] for n in NAMES), w["block_size"], w["n_sel"], w["window"],
+                                         compressor=comp, return_block_idx=True,
+                                         n_init_blocks=w.get("n_init", 0), n_local_blocks=w.get("n_local", 0),
+                                         cmp_len=w.get("cmp_len"), cmp_stride=w.get("cmp_stride"))
+        return out, idx, ()
     ins = [t[n].detach().requires_grad_(True) for n in NAMES]
     cps = {k: v.detach().requires_grad_(True) for k, v in comp.items()}
     out, idx = nsa.nsa_attention(*ins, w["block_size"], w["n_sel"], w["window"], compressor=cps,
@@ -396,7 +406,8 @@ def main():
     assert L.lib().nsa_device_status(None) == 0, L.lib().nsa_last_error()
 
     # ---- end to end: pinned host buffers in, results out, every step ---------------------------
-    host_in = {n: torch.empty(t[n].shape, dtype=t[n].dtype, pin_memory=True).copy_(t[n]) for n in NAMES + ["do"]}
+    in_names = NAMES if w.get("fwd_only") else NAMES + ["do"]
+    host_in = {n: torch.empty(t[n].shape, dtype=t[n].dtype, pin_memory=True).copy_(t[n]) for n in in_names}
     host_out = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in [out] + list(grads)]
     h2d = sum(x.numel() * x.element_size() for x in host_in.values())
     d2h = sum(x.numel() * x.element_size() for x in host_out)
@@ -508,9 +519,10 @@ def main():
                      "dram_gbs": traffic / sec / 1e9 if traffic else None,
                      "dram_frac_of_copy_peak": traffic / sec / 1e9 / pk["hbm"] if traffic else None,
                      "launch_ms": sec * 1e3, "share_of_kernel_time": tms / total_ms})
-    total_flops = 14 * D * sum(pairs.values())
+    total_flops = (4 if w.get("fwd_only") else 14) * D * sum(pairs.values())
     line = {
-        "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "metric": METRIC if not w.get("fwd_only") else "NSA forward tokens/s per B200 at long context, bf16",
+        "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
@@ -521,6 +533,7 @@ def main():
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
+        "peak_hbm_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
         "roofline": roof,
         "kernels": {k: {"launches": v[0], "ms": round(v[1], 3), "share": round(v[1] / total_ms, 4)}
                     for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
