@@ -29,6 +29,7 @@ TC_CONFIGS = [
     dict(B=1, Hq=16, Hkv=4, D=64, T=1000, block_size=64, S=16, window=77),   # ragged T
     dict(B=1, Hq=2, Hkv=1, D=128, T=320, block_size=64, S=2, window=3),
     dict(B=1, Hq=1, Hkv=1, D=64, T=256, block_size=64, S=4, window=300),
+    dict(B=2, Hq=6, Hkv=2, D=64, T=576, block_size=64, S=6, window=150),     # 3 heads per kv head (the model config)
 ]
 
 
