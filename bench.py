@@ -266,7 +266,10 @@ def model_workload(args, rank, world, local_rank):
     DP = importlib.import_module("openbox-llm_b200.dp_step")
     torch.manual_seed(0)                                     # identical replicas
     model = M.NSATransformerB200(**MODEL_C5).to(dev)
-    step = DP.DataParallelStep(model, lr=3e-4, weight_decay=0.1, grad_clip=1.0)
+    # forward + backward replayed from a CUDA graph: the eager step is bound by the host issuing
+    # ~3000 launches (112 ms to enqueue one step against ~90 ms of GPU work)
+    step = DP.DataParallelStep(model, lr=3e-4, weight_decay=0.1, grad_clip=1.0,
+                               use_graph=not args.no_graph, graph_warmup=2)
     mb, T = 8, MODEL_C5["max_seq_len"]
     g = torch.Generator().manual_seed(1234 + rank)           # every rank its own micro-batches
     host = [(torch.randint(0, MODEL_C5["vocab_size"], (mb, T), generator=g).pin_memory(),
@@ -322,13 +325,16 @@ def model_workload(args, rank, world, local_rank):
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": dict(workload="c5_model", **MODEL_C5, micro_batch_per_gpu=mb, params=n_params,
                                optimizer="AdamW betas (0.9, 0.95) wd 0.1, clip 1.0, fp32 parameters, bf16 autocast",
-                               parallelism=f"dp{world}: bucketed NCCL all-reduce overlapping backward",
+                               parallelism=(f"dp{world}: bucketed NCCL all-reduce overlapping backward, eager"
+                                            if args.no_graph else
+                                            f"dp{world}: forward+backward as one CUDA graph, one NCCL all-reduce after it"),
                                l2="activations of a step exceed the 126 MB L2"),
                 "clocks": clocks, "final_loss": last,
                 "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s",
                         "h2d_bytes_per_step": 2 * mb * T * 8, "d2h_bytes_per_step": 4},
                 "gpu_launches": int(launches),
-                "nsa_kernel_share_of_step": total_ms / ms,
+                # per-kernel events are not recorded inside a graph replay
+                "nsa_kernel_share_of_step": total_ms / ms if args.no_graph else None,
                 "kernels": {k: {"launches": v[0], "ms": round(v[1], 3)} for k, v in
                             sorted(prof.items(), key=lambda kv: -kv[1][1])[:12]},
                 "roofline": None, "cpu_baseline": None,
@@ -347,6 +353,7 @@ def main():
     ap.add_argument("--workload", default="c4_t32k", choices=sorted(WORKLOADS) + ["c5_model"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the extra leg on the 32/16/64 geometry")
+    ap.add_argument("--no-graph", action="store_true", help="c5_model: eager step with overlapped bucketed all-reduce")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -133,3 +133,29 @@ def test_training_step_matches_the_reference_recipe():
     assert {"tok_emb.weight", "pos_emb.weight", "blocks.0.ln1.weight", "blocks.0.attn.q_proj.weight",
             "blocks.0.attn.comp_k.intra_pos", "blocks.0.attn.gate.bias", "blocks.1.ffn.2.weight",
             "ln_f.bias", "lm_head.weight"} <= keys
+
+
+@pytest.mark.gpu
+def test_graph_replay_gives_the_eager_step():
+    """Forward + backward replayed from a CUDA graph: the same losses and parameters as the eager
+    step on the same batches (the attention kernels, their work lists and device-side choices all
+    run inside the capture)."""
+    M = importlib.import_module("openbox-llm_b200.model")
+    torch.manual_seed(0)
+    kw = dict(vocab_size=512, d_model=128, n_layers=2, n_q_heads=4, n_kv_heads=2, max_seq_len=256,
+              block_size=64, n_selected_blocks=2, window=64)
+    a = M.NSATransformerB200(**kw).cuda()
+    b = copy.deepcopy(a)
+    sa = DP.DataParallelStep(a, lr=1e-3, use_graph=True, graph_warmup=2)
+    sb = DP.DataParallelStep(b, lr=1e-3)
+    g = torch.Generator().manual_seed(2)
+    for i in range(6):
+        idx = torch.randint(0, 512, (2, 256), generator=g).cuda()
+        tgt = torch.randint(0, 512, (2, 256), generator=g).cuda()
+        la, lb = float(sa.step(idx, tgt)), float(sb.step(idx, tgt))
+        assert abs(la - lb) <= 2e-3 * max(1.0, abs(lb)), (i, la, lb)
+    assert sa.graph is not None
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert (p - q).abs().max().item() <= 2e-3, n
+    lib = importlib.import_module("openbox-llm_b200._lib").lib()
+    assert lib.nsa_device_status(None) == 0
