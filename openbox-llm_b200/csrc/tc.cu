@@ -78,6 +78,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint32_t* s_member = (uint32_t*)(s_scan + 132);   // [nb_sel * nw]   (selection only)
   uint16_t* s_tiles = (uint16_t*)(s_member + (p.kind == 2 ? p.nb_sel * p.nw : 0));
 
+  if (p.kind == 2 && p.stats != nullptr &&
+      prefer_pairs(p.stats, p.offsets, p.B * p.Hkv, p.nb_sel, p.nq, p.force))
+    return;   // the block-outer variant serves this call: leave before anything is set up
   const int tid = threadIdx.x, warp = tid >> 5;
   const int qtile = p.n_qtiles - 1 - (int)blockIdx.x;   // long rows first
   const int bh = blockIdx.y;
@@ -101,9 +104,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   __syncthreads();
   if (*s_abort) return;
-  if (p.kind == 2 && p.stats != nullptr &&
-      prefer_pairs(p.stats, p.offsets, p.B * p.Hkv, p.nb_sel, p.nq, p.force))
-    return;   // the block-outer variant serves this call
 
   // ---- tile list ------------------------------------------------------------------------
   int n_tiles = 0, first_key = 0;

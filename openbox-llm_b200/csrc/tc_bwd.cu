@@ -599,15 +599,16 @@ __global__ void dq_reduce3_kernel(const Reduce3Args a) {
   float acc[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  // four partial rows per trip: their loads are issued before the first is added
-  auto add4 = [&](const __nv_bfloat16* part, const long long (&rows)[4]) {
-    uint4 u[4];
+  // eight partial rows per trip: their loads are issued before the first is added
+  constexpr int kTrip = 8;
+  auto add_rows = [&](const __nv_bfloat16* part, const long long (&rows)[kTrip]) {
+    uint4 u[kTrip];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int k = 0; k < kTrip; ++k)
       u[k] = rows[k] >= 0 ? __ldg(reinterpret_cast<const uint4*>(part + ((size_t)rows[k] * a.G + g) * D + v * 8))
                           : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < kTrip; ++k) {
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[k]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -620,30 +621,30 @@ __global__ void dq_reduce3_kernel(const Reduce3Args a) {
   const long long qrow = (long long)(bh * a.T + t);
   if (a.part_slc) {
     const int32_t* ps = a.pair_of_slot + (size_t)qrow * a.S;
-    for (int s0 = 0; s0 < a.S; s0 += 4) {
-      long long rows[4];
+    for (int s0 = 0; s0 < a.S; s0 += kTrip) {
+      long long rows[kTrip];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) rows[k] = s0 + k < a.S ? (long long)__ldg(ps + s0 + k) : -1;
-      add4(a.part_slc, rows);
+      for (int k = 0; k < kTrip; ++k) rows[k] = s0 + k < a.S ? (long long)__ldg(ps + s0 + k) : -1;
+      add_rows(a.part_slc, rows);
     }
   }
   if (a.part_win) {
     const int first = max(0, t - a.window + 1) >> 6, last = t >> 6;
-    for (int j0 = first; j0 <= last; j0 += 4) {
-      long long rows[4];
+    for (int j0 = first; j0 <= last; j0 += kTrip) {
+      long long rows[kTrip];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) rows[k] = j0 + k <= last ? qrow * a.slots_win + (j0 + k) % a.slots_win : -1;
-      add4(a.part_win, rows);
+      for (int k = 0; k < kTrip; ++k) rows[k] = j0 + k <= last ? qrow * a.slots_win + (j0 + k) % a.slots_win : -1;
+      add_rows(a.part_win, rows);
     }
   }
   if (a.part_cmp) {
     const int n_vis = cmp_visible(t, a.cmp_len, a.cmp_stride, a.Lk_cmp);
     const int last = n_vis > 0 ? (n_vis - 1) >> 6 : -1;
-    for (int j0 = 0; j0 <= last; j0 += 4) {
-      long long rows[4];
+    for (int j0 = 0; j0 <= last; j0 += kTrip) {
+      long long rows[kTrip];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) rows[k] = j0 + k <= last ? qrow * a.slots_cmp + j0 + k : -1;
-      add4(a.part_cmp, rows);
+      for (int k = 0; k < kTrip; ++k) rows[k] = j0 + k <= last ? qrow * a.slots_cmp + j0 + k : -1;
+      add_rows(a.part_cmp, rows);
     }
   }
   const int b = (int)(bh / a.Hkv), hkv = (int)(bh % a.Hkv);
