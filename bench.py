@@ -46,8 +46,8 @@ METRIC = "NSA fwd+bwd tokens/s per B200 at T=32K bf16; % of tensor-pipe peak"
 
 # DRAM bytes (read + write) per launch at c4_t32k, one-pass ncu capture
 # (profiles/dram_traffic_pair_kernels_c4_t32k.md)
-TRAFFIC_C4 = {"tc_bwd_slc": 37.62e9, "tc_bwd_win": 13.80e9, "tc_bwd_cmp": 15.09e9,
-              "tc_fwd_slc_pairs": 26.63e9, "sel_combine_kernel": 18.81e9, "dq_reduce3": 32.39e9,
+TRAFFIC_C4 = {"tc_bwd_slc": 31.29e9, "tc_bwd_win": 14.29e9, "tc_bwd_cmp": 15.07e9,
+              "tc_fwd_slc_pairs": 23.33e9, "sel_combine_kernel": 18.81e9, "dq_reduce3": 32.39e9,
               "tc_fwd_win": 2.38e9, "tc_fwd_cmp": 2.14e9, "tc_score_topn": 1.12e9}
 
 NAMES = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
