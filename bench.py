@@ -29,16 +29,16 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE config 4: the T=32K training shape of the headline metric
+    # the T=32K training shape the headline metric is quoted on
     "c4_t32k": dict(B=8, T=32768, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
-    # the same shape with the geometry BASELINE.json words (not expressible in the reference):
+    # the same shape with the published NSA geometry (not expressible in the reference):
     # summaries of 32 tokens every 16, block 0 and the two local blocks in every list
     "c4_t32k_l32d16": dict(B=8, T=32768, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512,
                            cmp_len=32, cmp_stride=16, n_init=1, n_local=2),
-    # BASELINE config 2
+    # the single-kv-head 8K shape (16 query heads share one kv head)
     "c2_t8k": dict(B=4, T=8192, Hq=16, Hkv=1, D=128, block_size=64, n_sel=16, window=512),
     "tiny": dict(B=1, T=2048, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
-    # BASELINE config 3: forward only at long context, 64 query / 4 kv heads (value = forward tokens/s)
+    # forward only at long context, 64 query / 4 kv heads (value = forward tokens/s)
     "c3_t32k_fwd": dict(B=1, T=32768, Hq=64, Hkv=4, D=128, block_size=64, n_sel=16, window=512, fwd_only=True),
     "c3_t128k_fwd": dict(B=1, T=131072, Hq=64, Hkv=4, D=128, block_size=64, n_sel=16, window=512, fwd_only=True),
 }
@@ -249,7 +249,7 @@ MODEL_C5 = dict(vocab_size=50304, d_model=768, n_layers=12, n_q_heads=12, n_kv_h
 
 
 def model_workload(args, rank, world, local_rank):
-    """BASELINE config 5: one optimizer step of the 12-layer model (d_model 768, 12 query / 4 kv
+    """The model-level workload: one optimizer step of the 12-layer model (d_model 768, 12 query / 4 kv
     heads, head dim 64, T=4096, micro-batch 8 per GPU; the reference's ~150 M configuration),
     replicas kept in step by the bucketed NCCL gradient all-reduce of dp_step.py.  Token ids and
     targets are uniform random (no corpus here), uploaded from pinned host memory every step;
@@ -319,7 +319,7 @@ def model_workload(args, rank, world, local_rank):
         tokens = world * mb * T * args.steps
         total_ms = sum(v[1] for v in prof.values()) or 1.0
         n_params = sum(p.numel() for p in step.flat.params)
-        line = {"metric": "optimizer-step tokens/s of the 12-layer NSA model (BASELINE config 5)",
+        line = {"metric": "optimizer-step tokens/s of the 12-layer NSA model (d_model 768, T=4096, micro-batch 8 per GPU)",
                 "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -550,7 +550,7 @@ def main():
         line["cpu_baseline"] = cpu_baseline(w, os.cpu_count() or 1)
     else:
         line["cpu_baseline"] = None
-    # the same shape on the geometry BASELINE.json words (summaries 32 / 16, forced blocks), which
+    # the same shape on the published NSA geometry (summaries 32 / 16, forced blocks), which
     # the reference cannot express and nothing of it pins: a few device-resident steps, reported
     # beside the headline, never instead of it
     line["also"] = None
