@@ -393,7 +393,7 @@ def test_edge_cases():
 
 
 def test_headline_shape_properties():
-    """BASELINE config 2 at full size (B=4, T=8192, 16 q heads / 1 kv head, D=128, bf16):
+    """The single-kv-head 8K benchmark shape at full size (B=4, T=8192, 16 q heads / 1 kv head, D=128, bf16):
     size-independent checks plus the oracle on sampled query rows."""
     nsa = pkg()
     c = dict(B=4, Hq=16, Hkv=1, D=128, T=8192, block_size=64, S=16)
