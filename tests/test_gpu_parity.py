@@ -604,3 +604,59 @@ def test_whole_op_general_geometry(case):
                 lim = 5e-3 if dtype == torch.float32 else 5e-2
                 assert rl <= lim or ma <= lim, f"{impl} d{k}: abs {ma:.3e} rel {rl:.3e}"
     nsa.set_impl("auto")
+
+
+def test_metric_shape_properties():
+    """The T=32K training shape the headline metric is quoted on, at full size (B=8, T=32768,
+    16 q heads / 2 kv heads, D=128, bf16, learned pooling, own scorer): index sanity, the oracle
+    on sampled query rows of one batch element, the gradient checksum identity, finiteness."""
+    nsa = pkg()
+    B, Hq, Hkv, T, D, bs, S, W = 8, 16, 2, 32768, 128, 64, 16, 512
+    dtype = torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda *shape: (torch.randn(*shape, generator=g, device="cuda") * D ** -0.25).to(dtype)
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+    t = {"q": mk(B, Hq, T, D)}
+    for n in names[1:7]:
+        t[n] = mk(B, Hkv, T, D)
+    t["gate"] = torch.randn(B, Hq, T, 3, generator=g, device="cuda").to(dtype)
+    do = torch.randn(B, Hq, T, D, generator=g, device="cuda").to(dtype)
+    cg = torch.Generator().manual_seed(1)
+    comp = {}
+    for p_ in ("k", "v"):
+        comp[p_ + "_intra"] = 0.02 * torch.randn(bs, D, generator=cg)
+        comp[p_ + "_logits"] = 0.02 * torch.randn(bs, generator=cg)
+        comp[p_ + "_proj"] = torch.randn(D, D, generator=cg) * D ** -0.5
+    ins = [t[n].clone().requires_grad_(True) for n in names]
+    out, idx = nsa.nsa_attention(*ins, bs, S, W, compressor={k: v.cuda() for k, v in comp.items()},
+                                 return_block_idx=True)
+    out.backward(do)
+    assert nsa.lib().nsa_device_status(None) == 0
+    # index sanity on the device: valid, causal (complete blocks only), distinct, -1 only when
+    # fewer than S blocks are complete
+    tt = torch.arange(T, device="cuda").view(1, 1, T, 1)
+    assert ((idx == -1) | ((idx >= 0) & ((idx + 1) * bs - 1 <= tt))).all()
+    assert ((idx >= 0).sum(-1) == torch.clamp((tt.squeeze(-1) + 1) // bs, max=S)).all()
+    srt = idx.sort(-1).values
+    assert ((srt[..., 1:] != srt[..., :-1]) | (srt[..., 1:] == -1)).all()
+    # oracle on one batch element and sampled row windows, with the kernel's block choice
+    b = 5
+    sl = lambda x: x[b:b + 1].float().cpu()
+    k_cmp = O.ref_block_compressor(sl(t["kc"]), comp["k_intra"], comp["k_logits"], comp["k_proj"], bs).to(dtype).float()
+    v_cmp = O.ref_block_compressor(sl(t["vc"]), comp["v_intra"], comp["v_logits"], comp["v_proj"], bs).to(dtype).float()
+    ks, vs, kw, vw, idx_b = sl(t["ks"]), sl(t["vs"]), sl(t["kw"]), sl(t["vw"]), idx[b:b + 1].cpu()
+    for t0, t1 in [(0, 128), (16320, 16448), (32640, 32768)]:
+        qs = sl(t["q"][:, :, t0:t1])
+        parts = []
+        for k, v, keep in ((k_cmp, v_cmp, O.compress_keep(t0, t1, T // bs, bs)),
+                           (ks, vs, O.selection_keep(idx_b, t0, t1, T, bs)),
+                           (kw, vw, O.window_keep(t0, t1, T, W))):
+            o_b, _ = O.stream_attn_forward(qs, k, v, lambda a, bb, keep=keep: keep[..., a:bb, :])
+            parts.append(o_b)
+        ref = O.ref_gate_combine(*parts, sl(t["gate"][:, :, t0:t1]))
+        check(out[b:b + 1, :, t0:t1], ref, dtype, f"rows {t0}:{t1}", scale_abs=False)
+    # (the checksum identity sum dq.q == sum dk.k of the mean-pooling test does not hold here: the
+    # learned pooling adds intra_pos to the tokens, so k_cmp is not homogeneous in kc)
+    for n, x in zip(names, ins):
+        assert torch.isfinite(x.grad).all(), n
+        assert x.grad.float().abs().max().item() > 0, n
