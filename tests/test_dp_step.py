@@ -78,6 +78,17 @@ def test_two_gloo_ranks_average_their_gradients():
     assert (got[0][2] - want).abs().max().item() <= 1e-6
 
 
+def _same_training(a, b, lr, steps):
+    """Two replicas trained on the same batches by two implementations of one step.  Kernels that
+    accumulate with fp32 atomics make the gradients differ in the last bits from run to run, and
+    Adam turns a gradient whose sign is noise into a step of +-lr either way: single entries may
+    drift by up to 2 * lr per step, the bulk may not."""
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        d = (p - q).abs()
+        assert d.max().item() <= 2.5 * lr * steps, n
+        assert d.mean().item() <= 0.05 * lr * steps, n
+
+
 @pytest.mark.gpu
 def test_fused_clip_adamw_matches_torch():
     m = _mlp(1).cuda()
@@ -126,8 +137,7 @@ def test_training_step_matches_the_reference_recipe():
         losses.append((float(la), float(lb.detach())))
     for la, lb in losses:
         assert abs(la - lb) <= 2e-3 * max(1.0, abs(lb)), losses
-    for (n, p), q in zip(a.named_parameters(), b.parameters()):
-        assert (p - q).abs().max().item() <= 2e-3, n
+    _same_training(a, b, 1e-3, 3)
     # a snapshot with the reference's key names loads (nsa_model.py:455-478 module tree)
     keys = set(a.state_dict())
     assert {"tok_emb.weight", "pos_emb.weight", "blocks.0.ln1.weight", "blocks.0.attn.q_proj.weight",
@@ -155,7 +165,6 @@ def test_graph_replay_gives_the_eager_step():
         la, lb = float(sa.step(idx, tgt)), float(sb.step(idx, tgt))
         assert abs(la - lb) <= 2e-3 * max(1.0, abs(lb)), (i, la, lb)
     assert sa.graph is not None
-    for (n, p), q in zip(a.named_parameters(), b.parameters()):
-        assert (p - q).abs().max().item() <= 2e-3, n
+    _same_training(a, b, 1e-3, 6)
     lib = importlib.import_module("openbox-llm_b200._lib").lib()
     assert lib.nsa_device_status(None) == 0
