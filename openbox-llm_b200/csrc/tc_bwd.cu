@@ -7,7 +7,9 @@
 //   window      queries [64 j, 64 j + 63 + W - 1]
 //   compression queries t >= (64 j + 1) * Bsz - 1
 //   selection   the queries that list block j, from the block -> query CSR
-// Q and dO rows are gathered with 16-byte cp.async into 128B-swizzled tiles.
+// Q and dO rows arrive by TMA into 128B-swizzled tiles: one box per row tile for the window and
+// compression branches (consecutive queries), one box per query and 64-column slab for
+// selection.  Selection CTAs take (block, chunk of row tiles) items from a device-built work list.
 // Per row tile, five MMAs:
 //   S    = Q K^T          (A: Q  K-major,   B: K  K-major)
 //   dP   = dO V^T         (A: dO K-major,   B: V  K-major)
@@ -16,8 +18,8 @@
 //   dQ   = dS K           (A: dS K-major,   B: K  MN-major)
 // with p = exp2(s*scale*log2e - lse*log2e) and dS = scale * p * (dP - delta) computed by the
 // thread that owns the row (TMEM lane = row).  dQ of a row is the sum over the key tiles it
-// attends; every (row tile, key tile) result is written as a bf16 partial and a second kernel
-// adds the partials of each query in fp32.
+// attends; every (row tile, key tile) result leaves as a bf16 partial tile (TMA store) and a
+// second kernel adds the partials of each query in fp32.
 #include "tc_common.cuh"
 #include "tc_host.cuh"
 
@@ -95,8 +97,8 @@ __device__ __forceinline__ void group_sync(int group) {
 // group's arithmetic.  Inside a group, the two warps of a TMEM lane quadrant split the 64 key
 // columns of a row between them.  Row r of a tile is head r % G of the tile's query r / G: the
 // G rows of a query arrive by one TMA box each for Q and dO (128B swizzle), whatever the query
-// list looks like, and leave as bf16 dQ partials through a swizzled staging tile so that the
-// global stores are whole 256-byte rows.
+// list looks like, and leave as bf16 dQ partials through a 128B-swizzled staging tile: a full
+// tile by one asynchronous TMA store per slab, the ragged last tile as whole rows by hand.
 template <int D>
 __global__ void __launch_bounds__(512, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
