@@ -109,6 +109,25 @@ int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int cmp_len, int cmp_stride,
                    int window, const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
                    void* stream);
 
+/* The same without partial buffers for the window and compression branches (tcgen05 shapes only;
+ * no counterpart in the reference, whose q-tiled backward kernels store dQ per query tile,
+ * nsa_fused_kernel.py:420-425).  nsa_range_attn_bwd_acc is nsa_range_attn_bwd with the branch's
+ * dQ ADDED, tile by tile (TMA reduce-add), to dq_acc, an fp32 buffer [B*Hkv][T][Hq/Hkv][D] that
+ * the caller has zeroed and may hand to both branches in turn; its workspace
+ * (nsa_range_attn_bwd_acc_workspace_bytes) then holds no partials.  nsa_dq_finish adds the
+ * selection branch's partials (ws_slc: the workspace of an nsa_selection_bwd call with dq = NULL,
+ * or NULL) to the accumulator and writes dq [B,Hq,T,D] in the input dtype.  The adds into dq_acc
+ * happen in no fixed order, so dq can differ in its last bits from run to run; nsa_dq_reduce3 is
+ * the bit-reproducible form. */
+size_t nsa_range_attn_bwd_acc_workspace_bytes(const NsaDims* dims, int Lk, int mode, int window);
+int nsa_range_attn_bwd_acc(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                           const void* d_o, float* dq_acc, void* dk, void* dv, const NsaDims* dims,
+                           int Lk, int mode, int window, int block_size,
+                           const float* row_scale, const float* row_dot,
+                           void* workspace, size_t workspace_bytes, void* stream);
+int nsa_dq_finish(const NsaDims* dims, int S, int block_size, const float* dq_acc, const void* ws_slc,
+                  void* dq, void* stream);
+
 /* ---- block -> query CSR ---------------------------------------------------------------------
  * Replaces build_block_to_query_csr (nsa_fsa.py:14-64): pairs (query i, block j) with j >= 0
  * and j*block_size <= i, grouped by (b, hkv, j), queries ascending.  block_offsets is
@@ -256,9 +275,17 @@ int nsa_profile_summary(char* buf, size_t cap);
  * beyond its USE_FSA_FWD module flag (nsa_selection_kernel.py:48). */
 int nsa_set_option(const char* name, int value);
 
-/* error flag raised by a kernel whose bounded wait ran out (0 = none); reading it synchronises
- * the stream. */
+/* Error word of the current device, raised by a kernel whose bounded wait ran out (0 = none).
+ * Reading it synchronises the stream, returns NSA_ERR_DEVICE_WAIT when it was set and clears it.
+ * While the word is set every tcgen05 kernel returns at entry and leaves its outputs unwritten, so
+ * a caller that launches many steps without looking should read it at its own synchronisation
+ * points.  The kernels of the reference have no status return (Python asserts only). */
 int nsa_device_status(void* stream);
+
+/* Sets the error word from the host (stream-ordered).  For tests of the give-up path: with the
+ * word set, a launch returns without touching its outputs and nsa_device_status reports it, all
+ * without making any kernel wait.  No counterpart in the reference. */
+int nsa_debug_set_device_status(int value, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,7 @@
 """ctypes binding of libnsa_b200.so.  There is no fallback: if the library is missing or a
 call fails, an exception is raised."""
 import ctypes
+import functools
 import os
 
 import torch
@@ -32,6 +33,7 @@ SIGNATURES = {
     "nsa_version": (_i, []),
     "nsa_tc_supported": (_i, [_dp, _i]),
     "nsa_device_status": (_i, [_vp]),
+    "nsa_debug_set_device_status": (_i, [_i, _vp]),
     "nsa_launch_count": (ctypes.c_longlong, []),
     "nsa_set_option": (_i, [ctypes.c_char_p, _i]),
     "nsa_profile_enable": (None, [_i]),
@@ -63,6 +65,9 @@ SIGNATURES = {
     "nsa_sumsq_f32": (_i, [_vp, _sz, _vp, _vp]),
     "nsa_adamw_step_f32": (_i, [_vp] * 4 + [_sz] + [_f] * 5 + [_i, _vp, _f, _f, _vp]),
     "nsa_dq_reduce3": (_i, [_dp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "nsa_range_attn_bwd_acc_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
+    "nsa_range_attn_bwd_acc": (_i, [_vp] * 9 + [_dp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    "nsa_dq_finish": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp]),
     "nsa_gate_combine_fwd": (_i, [_vp] * 5 + [_dp, _vp]),
     "nsa_gate_combine_bwd": (_i, [_vp] * 9 + [_dp, _vp]),
 }
@@ -109,6 +114,39 @@ def stream():
 
 def dims(B, Hq, Hkv, T, D, dtype):
     return NsaDims(B, Hq, Hkv, T, D, dtype)
+
+
+def on_device(fn):
+    """Decorator of every wrapper that launches library kernels: the CUDA tensors among the
+    arguments must live on ONE device, and the call runs with that device current, so that the
+    stream, the TMA tensor maps and the library's per-device symbols (status word, built-in
+    scratch) belong to the device that holds the data.  Without it, tensors on cuda:1 while
+    cuda:0 is current would launch on GPU 0 with GPU 1's pointers."""
+    @functools.wraps(fn)
+    def wrapper(*args, **kw):
+        dev = None
+        for a in list(args) + list(kw.values()):
+            if isinstance(a, torch.Tensor) and a.is_cuda:
+                if dev is None:
+                    dev = a.device
+                elif a.device != dev:
+                    raise NsaError(f"libnsa_b200: tensors on different devices ({dev} and {a.device})")
+        if dev is None or dev.index == torch.cuda.current_device():
+            return fn(*args, **kw)
+        with torch.cuda.device(dev):
+            return fn(*args, **kw)
+    return wrapper
+
+
+def check_device_status():
+    """Read (and clear) the current device's status word, synchronising the current stream; raise
+    when a kernel gave up a bounded wait.  After such a give-up every later tcgen05 kernel
+    returns at entry and leaves its outputs unwritten until the word is read, so long-running
+    callers poll this at their own synchronisation points."""
+    check(lib().nsa_device_status(stream()))
+
+
+CHECK_STATUS_EVERY_CALL = os.environ.get("NSA_B200_CHECK_STATUS", "0") not in ("", "0")
 
 
 def workspace(nbytes, device):

@@ -194,6 +194,15 @@ extern "C" int nsa_device_status(void* stream) {
   return NSA_OK;
 }
 
+extern "C" int nsa_debug_set_device_status(int value, void* stream) {
+  int* p = device_status_ptr();
+  if (!p) { set_error("cudaGetSymbolAddress failed"); return NSA_ERR_CUDA; }
+  // the value travels inside the call (pageable 4-byte source: copied before the call returns)
+  NSA_CUDA_OK(cudaMemcpyAsync(p, &value, sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  NSA_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  return NSA_OK;
+}
+
 // ---- range attention -------------------------------------------------------------------------
 extern "C" int nsa_range_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                                   const NsaDims* dims, int Lk, int mode, int window, int block_size,
@@ -221,25 +230,35 @@ extern "C" int nsa_range_attn_fwd(const void* q, const void* k, const void* v, v
   return simt_attn_fwd(a, dims->dtype, (cudaStream_t)stream);
 }
 
-extern "C" size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int mode,
-                                                     int window, int impl) {
+static size_t range_bwd_ws(const NsaDims* dims, int Lk, int mode, int window, int impl, bool acc) {
   if (check_dims(dims) != NSA_OK) return 0;
   int rc;
-  size_t need = simt_bwd_ws(dims, Lk);
+  size_t need = acc ? 0 : simt_bwd_ws(dims, Lk);
   if (use_tc(dims, 64, impl, &rc)) {
     AttnArgs a = base_args(dims, Lk);
     a.kind = mode == NSA_MODE_COMPRESS_STRIDED ? NSA_MODE_COMPRESS : mode;
     a.window = window > 0 ? window : 1;
+    if (acc) a.dq_acc = reinterpret_cast<float*>(sizeof(float));   // only "not null" matters for the plan
     need = need > tc_attn_bwd_workspace(a) ? need : tc_attn_bwd_workspace(a);
   }
   return need;
 }
 
-extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o,
-                                  const float* lse, const void* d_o, void* dq, void* dk, void* dv,
-                                  const NsaDims* dims, int Lk, int mode, int window, int block_size,
-                                  const float* row_scale, const float* row_dot,
-                                  void* workspace, size_t workspace_bytes, int impl, void* stream) {
+extern "C" size_t nsa_range_attn_bwd_workspace_bytes(const NsaDims* dims, int Lk, int mode,
+                                                     int window, int impl) {
+  return range_bwd_ws(dims, Lk, mode, window, impl, false);
+}
+
+extern "C" size_t nsa_range_attn_bwd_acc_workspace_bytes(const NsaDims* dims, int Lk, int mode,
+                                                         int window) {
+  return range_bwd_ws(dims, Lk, mode, window, NSA_IMPL_TC, true);
+}
+
+static int range_attn_bwd(const void* q, const void* k, const void* v, const void* o,
+                          const float* lse, const void* d_o, void* dq, float* dq_acc, void* dk, void* dv,
+                          const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                          const float* row_scale, const float* row_dot,
+                          void* workspace, size_t workspace_bytes, int impl, void* stream) {
   int rc = check_dims(dims);
   if (rc != NSA_OK) return rc;
   NSA_CHECK_ARG(mode == NSA_MODE_WINDOW || mode == NSA_MODE_COMPRESS || mode == NSA_MODE_COMPRESS_STRIDED,
@@ -267,6 +286,7 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
     a.kind = NSA_MODE_COMPRESS;
   }
   a.row_scale = row_scale; a.row_dot = row_dot;
+  a.dq_acc = dq_acc;
   NSA_CHECK_ARG((row_scale == nullptr) == (row_dot == nullptr), "row_scale and row_dot go together");
   if (use_tc(dims, 64, impl, &rc)) {
     a.dk_acc = (float*)dk;   // tc path writes dk/dv itself; pass the outputs through
@@ -274,8 +294,28 @@ extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, c
     return tc_attn_bwd(a, workspace, workspace_bytes, st);
   }
   if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(!dq_acc, "the dQ accumulator needs a shape the tcgen05 kernels serve");
   NSA_CHECK_ARG(dq, "dq may be null only when the tcgen05 kernels serve the call");
   return simt_bwd(a, dims, dk, dv, workspace, workspace_bytes, st);
+}
+
+extern "C" int nsa_range_attn_bwd(const void* q, const void* k, const void* v, const void* o,
+                                  const float* lse, const void* d_o, void* dq, void* dk, void* dv,
+                                  const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                                  const float* row_scale, const float* row_dot,
+                                  void* workspace, size_t workspace_bytes, int impl, void* stream) {
+  return range_attn_bwd(q, k, v, o, lse, d_o, dq, nullptr, dk, dv, dims, Lk, mode, window, block_size,
+                        row_scale, row_dot, workspace, workspace_bytes, impl, stream);
+}
+
+extern "C" int nsa_range_attn_bwd_acc(const void* q, const void* k, const void* v, const void* o,
+                                      const float* lse, const void* d_o, float* dq_acc, void* dk, void* dv,
+                                      const NsaDims* dims, int Lk, int mode, int window, int block_size,
+                                      const float* row_scale, const float* row_dot,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+  NSA_CHECK_ARG(dq_acc, "null dq accumulator");
+  return range_attn_bwd(q, k, v, o, lse, d_o, nullptr, dq_acc, dk, dv, dims, Lk, mode, window, block_size,
+                        row_scale, row_dot, workspace, workspace_bytes, NSA_IMPL_TC, stream);
 }
 
 // ---- selection attention ---------------------------------------------------------------------
@@ -367,6 +407,17 @@ extern "C" int nsa_dq_reduce3(const NsaDims* dims, int Lk_cmp, int cmp_len, int 
   NSA_CHECK_ARG(!ws_slc || S > 0, "bad S");
   NSA_CHECK_ARG(!ws_win || window >= 1, "bad window");
   const AttnArgs a = base_args(dims, dims->T);
-  return tc_dq_reduce3(a, Lk_cmp, cmp_len, cmp_stride, S, block_size, window, ws_cmp, ws_slc, ws_win, dq,
-                       (cudaStream_t)stream);
+  return tc_dq_reduce3(a, Lk_cmp, cmp_len, cmp_stride, S, block_size, window, ws_cmp, ws_slc, ws_win,
+                       nullptr, dq, (cudaStream_t)stream);
+}
+
+extern "C" int nsa_dq_finish(const NsaDims* dims, int S, int block_size, const float* dq_acc,
+                             const void* ws_slc, void* dq, void* stream) {
+  int rc = check_dims(dims);
+  if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(dq && dq_acc, "null dq or accumulator");
+  NSA_CHECK_ARG(use_tc(dims, block_size, NSA_IMPL_AUTO, &rc), "nsa_dq_finish needs a shape the tcgen05 kernels serve");
+  NSA_CHECK_ARG(!ws_slc || S > 0, "bad S");
+  const AttnArgs a = base_args(dims, dims->T);
+  return tc_dq_reduce3(a, 0, 0, 0, S, block_size, 1, nullptr, ws_slc, nullptr, dq_acc, dq, (cudaStream_t)stream);
 }

@@ -98,6 +98,7 @@ struct AttnArgs {
   void* o; float* lse;
   const void* d_o; void* dq; float* dk_acc; float* dv_acc;   // backward
   const float* row_scale; const float* row_dot;   // backward of a gated branch (may be null)
+  float* dq_acc;     // tcgen05 window / compression backward: fp32 accumulator [B*Hkv][T][G][D] that takes dQ (or null)
   int B, Hq, Hkv, T, Lk, D, S;
   int kind;          // 0 window, 1 compress, 2 selection
   int window, block_size;
@@ -115,7 +116,7 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t tc_attn_bwd_workspace(const AttnArgs& a);
 int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int cmp_len, int cmp_stride, int S, int block_size,
-                  int window, const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
-                  cudaStream_t st);
+                  int window, const void* ws_cmp, const void* ws_slc, const void* ws_win,
+                  const float* dq_acc, void* dq, cudaStream_t st);
 
 }  // namespace nsa

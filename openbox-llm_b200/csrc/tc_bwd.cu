@@ -18,8 +18,14 @@
 //   dQ   = dS K           (A: dS K-major,   B: K  MN-major)
 // with p = exp2(s*scale*log2e - lse*log2e) and dS = scale * p * (dP - delta) computed by the
 // thread that owns the row (TMEM lane = row).  dQ of a row is the sum over the key tiles it
-// attends; every (row tile, key tile) result leaves as a bf16 partial tile (TMA store) and a
-// second kernel adds the partials of each query in fp32.
+// attends.  Two ways out of the CTA:
+//   slots        every (row tile, key tile) result leaves as a bf16 partial tile (TMA store) and a
+//                second kernel adds the partials of each query in fp32, in a fixed order
+//                (selection always; window / compression when the caller wants dq itself);
+//   accumulator  window / compression inside the whole op: the fp32 tile is added to one fp32
+//                accumulator [units][T][G][D] by TMA reduce-add.  Consecutive key tiles hit the same
+//                consecutive query rows at nearby times, so the adds meet in L2 and no partial
+//                buffer exists; the order of the adds, hence the last bits of dq, is not fixed.
 #include "tc_common.cuh"
 #include "tc_host.cuh"
 
@@ -45,22 +51,9 @@ struct BwdArgs {
   int B, Hq, Hkv, T, Lk, G, nq;
   int kind, window, block_size;
   int n_ktiles, n_slots;
+  int dq_acc_mode;             // 1: dQ tiles are added to the fp32 accumulator (window / compression)
   float scale, scale_log2;
-#ifdef NSA_TRACE
-  long long* trace;            // development builds only: stage time stamps of one CTA
-#endif
 };
-
-#ifdef NSA_TRACE
-#define NSA_STAMP(k)                                                                       \
-  do {                                                                                     \
-    if (p.trace && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0 &&    \
-        lt == 33 && it_no < 48)                                                            \
-      p.trace[(grp * 48 + it_no) * 12 + (k)] = clock64();                                   \
-  } while (0)
-#else
-#define NSA_STAMP(k) do {} while (0)
-#endif
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
@@ -104,7 +97,8 @@ __global__ void __launch_bounds__(512, 1)
 tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_q_run, const __grid_constant__ CUtensorMap tm_do_run,
-              const __grid_constant__ CUtensorMap tm_dq, const BwdArgs p) {
+              const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dqacc,
+              const BwdArgs p) {
   constexpr int kSlabs = D / 64;
   constexpr int kKVBytes = kKeys * 128 * kSlabs;
   constexpr uint32_t kTmemCols = 512;
@@ -199,7 +193,8 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     for (int k = 0; k <= 6; ++k) mbar_init(bars + k, (k == 1 || k == 4) ? 2 : 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
-    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_do); prefetch_tensormap(&tm_dq);
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_do);
+    prefetch_tensormap(p.dq_acc_mode ? &tm_dqacc : &tm_dq);
   }
   __syncthreads();
   if (*s_abort) return;
@@ -254,16 +249,18 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   auto row_index = [&](int t) -> size_t { return (size_t)(b * p.Hq + head) * p.T + t; };
   // one TMA box per query and slab for Q and for dO; a missing query reads past T: zeros
   const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs * 2);
-  auto gather = [&](const int* rowt) {
+  // part (window / compression only): 0 = Q and dO, 1 = Q now (the byte count of both is
+  // announced), 2 = dO, issued later because its tile served as staging meanwhile
+  auto gather = [&](const int* rowt, int part = 0) {
     if (p.kind != 2) {
       // window / compression: the tile's queries are consecutive tokens, one box per slab
       if (lt == 0) {
-        mbar_expect_tx(bar_g, gather_bytes);
+        if (part != 2) mbar_expect_tx(bar_g, gather_bytes);
         const int tq = rowt[0] >= 0 ? rowt[0] : p.T;
 #pragma unroll
         for (int s = 0; s < kSlabs; ++s) {
-          tma_load_3d(sQ + s * (kRows * 128), &tm_q_run, bar_g, s * 64, b * p.Hq + hkv * p.G, tq);
-          tma_load_3d(sDO + s * (kRows * 128), &tm_do_run, bar_g, s * 64, b * p.Hq + hkv * p.G, tq);
+          if (part != 2) tma_load_3d(sQ + s * (kRows * 128), &tm_q_run, bar_g, s * 64, b * p.Hq + hkv * p.G, tq);
+          if (part != 1) tma_load_3d(sDO + s * (kRows * 128), &tm_do_run, bar_g, s * 64, b * p.Hq + hkv * p.G, tq);
         }
       }
     } else {
@@ -304,10 +301,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     gather(s_rowt);
   }
   uint32_t phase = 0;
-  int it_no = 0;
-  (void)it_no;
-  for (; i < rt_end; i += 2, phase ^= 1, ++it_no, buf ^= 1) {
-    NSA_STAMP(0);
+  for (; i < rt_end; i += 2, phase ^= 1, buf ^= 1) {
     const int t_nn = (i + 4 < rt_end) ? row_query(i + 4) : -1;
     float lse_nxt = 0.f, delta_nxt = 0.f, gate_nxt = 1.f;
     if (t_nxt >= 0) {
@@ -318,9 +312,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     // query positions of this group's next tile, for the gather issued further down
     if (g == 0 && half == 0 && row_slot_ok) s_rowt[(buf ^ 1) * kMaxNq + ql] = t_nxt;
     mbar_wait(bar_g, phase, p.status, s_abort, 512);
-    NSA_STAMP(1);
     group_sync(grp);       // also: the staging tile of the previous iteration has been read
-    NSA_STAMP(2);
     if (lt == 0) {
       tc_fence_after();
       const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), da = desc_lo_kmajor(smem_u32(sDO));
@@ -355,7 +347,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     const float lse2_cur = lse_cur * kLog2e;
     mbar_wait(bar_sp, phase, p.status, s_abort, 64);
-    NSA_STAMP(3);
     tc_fence_after();
     __syncwarp();
     {
@@ -390,7 +381,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     fence_proxy_async();
     tc_fence_before();
-    NSA_STAMP(4);
     group_sync(grp);
     if (lt == 0) {
       tc_fence_after();
@@ -423,63 +413,99 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       s_prow[row] = prow;
     }
     mbar_wait(bar_acc, phase, p.status, s_abort, 128);
-    NSA_STAMP(5);
     tc_fence_after();
-    // the row tiles are free again: fetch this group's next tile
-    if (i + 2 < rt_end) gather(s_rowt + (buf ^ 1) * kMaxNq);
-    NSA_STAMP(6);
-    __syncwarp();
-    // dQ: TMEM -> bf16 -> staging tile (the P / dS region): one slab of 128-byte rows per 64
-    // columns, 16-byte chunks XOR row, which is the layout of a 128B-swizzled TMA box
-    {
+    if (p.dq_acc_mode) {
+      // dQ: TMEM -> fp32 staging -> TMA reduce-add into the accumulator.  The fp32 tile is D / 32
+      // slabs of 128 rows x 128 bytes (128B swizzle): the first two lie over the P / dS tiles, the
+      // other two (D = 128) over the dO tile, whose refill therefore waits until the reduction has
+      // read them; Q is refilled at once.
+      constexpr bool kTwoStep = D > 64;
+      if (i + 2 < rt_end) gather(s_rowt + (buf ^ 1) * kMaxNq, kTwoStep ? 1 : 0);
+      __syncwarp();
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) {          // this thread's half of the D columns
         const int col0 = half * (D / 2) + cc * 32;
+        const int slab = col0 >> 5;
+        uint8_t* sbase = slab < 2 ? sP + slab * (kRows * 128) : sDO + (slab - 2) * (kRows * 128);
         uint32_t r32[32];
         tmem_ld32(lane_base + colDQ + col0, r32);
         tmem_wait_ld();
+        const uint32_t rbase = smem_u32(sbase) + row * 128;
 #pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          const uint32_t chunk = (uint32_t)((col0 >> 3) + v4);
-          st_shared_v4(smem_u32(sP) + (chunk >> 3) * (kRows * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4),
-                       pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1])),
-                       pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3])),
-                       pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5])),
-                       pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7])));
-        }
+        for (int c = 0; c < 8; ++c)
+          st_shared_v4(rbase + (((uint32_t)c ^ (uint32_t)(row & 7)) << 4), r32[c * 4], r32[c * 4 + 1],
+                       r32[c * 4 + 2], r32[c * 4 + 3]);
       }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    NSA_STAMP(8);
-    group_sync(grp);
-    NSA_STAMP(9);
-    if ((i + 1) * p.nq <= n_q) {
-      // a full tile: its rows are consecutive in the partial buffer, one TMA store per slab
+      fence_proxy_async();
+      tc_fence_before();
+      group_sync(grp);
       if (lt == 0) {
-        const int slot = p.kind == 2 ? 0 : (p.kind == 0 ? j % p.n_slots : j);
-        const int mid = p.kind == 2 ? pair_base + i * p.nq : t_lo + i * p.nq;
-        const int outer = p.kind == 2 ? 0 : bh;
+        // rows of queries past the tile's range carry zeros (p = 0 there); rows past T are dropped
+        const int t_tile = t_lo + i * p.nq;
 #pragma unroll
-        for (int sl = 0; sl < kSlabs; ++sl)
-          tma_store_5d(&tm_dq, sP + sl * (kRows * 128), sl * 64, 0, slot, mid, outer);
+        for (int sl = 0; sl < D / 32; ++sl) {
+          const uint8_t* sbase = sl < 2 ? sP + sl * (kRows * 128) : sDO + (sl - 2) * (kRows * 128);
+          tma_reduce_add_4d(&tm_dqacc, sbase, sl * 32, 0, t_tile, bh);
+        }
         bulk_commit();
+        if (kTwoStep && i + 2 < rt_end) {
+          bulk_wait_read();
+          gather(s_rowt + (buf ^ 1) * kMaxNq, 2);
+        }
       }
-    } else {   // the ragged last tile: 16 lanes write the 256 (D = 128) or 128 bytes of one row
-      constexpr int kChunks = D / 8;
-      constexpr int kRowsPerPass = kGroupThreads / kChunks;
-      const int c = lt % kChunks;
+    } else {
+      // the row tiles are free again: fetch this group's next tile
+      if (i + 2 < rt_end) gather(s_rowt + (buf ^ 1) * kMaxNq);
+      __syncwarp();
+      // dQ: TMEM -> bf16 -> staging tile (the P / dS region): one slab of 128-byte rows per 64
+      // columns, 16-byte chunks XOR row, which is the layout of a 128B-swizzled TMA box
+      {
+#pragma unroll
+        for (int cc = 0; cc < D / 64; ++cc) {          // this thread's half of the D columns
+          const int col0 = half * (D / 2) + cc * 32;
+          uint32_t r32[32];
+          tmem_ld32(lane_base + colDQ + col0, r32);
+          tmem_wait_ld();
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            const uint32_t chunk = (uint32_t)((col0 >> 3) + v4);
+            st_shared_v4(smem_u32(sP) + (chunk >> 3) * (kRows * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4),
+                         pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1])),
+                         pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3])),
+                         pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5])),
+                         pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7])));
+          }
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      group_sync(grp);
+      if ((i + 1) * p.nq <= n_q) {
+        // a full tile: its rows are consecutive in the partial buffer, one TMA store per slab
+        if (lt == 0) {
+          const int slot = p.kind == 2 ? 0 : (p.kind == 0 ? j % p.n_slots : j);
+          const int mid = p.kind == 2 ? pair_base + i * p.nq : t_lo + i * p.nq;
+          const int outer = p.kind == 2 ? 0 : bh;
+#pragma unroll
+          for (int sl = 0; sl < kSlabs; ++sl)
+            tma_store_5d(&tm_dq, sP + sl * (kRows * 128), sl * 64, 0, slot, mid, outer);
+          bulk_commit();
+        }
+      } else {   // the ragged last tile: 16 lanes write the 256 (D = 128) or 128 bytes of one row
+        constexpr int kChunks = D / 8;
+        constexpr int kRowsPerPass = kGroupThreads / kChunks;
+        const int c = lt % kChunks;
 #pragma unroll 4
-      for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
-        const uint32_t prow = s_prow[r];
-        if (prow != 0xffffffffu) {
-          const uint4 v = *reinterpret_cast<const uint4*>(sP + (c >> 3) * (kRows * 128) + r * 128 +
-                                                          (((c & 7) ^ (r & 7)) << 4));
-          *reinterpret_cast<uint4*>(p.dq_part + (size_t)prow * D + c * 8) = v;
+        for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
+          const uint32_t prow = s_prow[r];
+          if (prow != 0xffffffffu) {
+            const uint4 v = *reinterpret_cast<const uint4*>(sP + (c >> 3) * (kRows * 128) + r * 128 +
+                                                            (((c & 7) ^ (r & 7)) << 4));
+            *reinterpret_cast<uint4*>(p.dq_part + (size_t)prow * D + c * 8) = v;
+          }
         }
       }
     }
-    NSA_STAMP(7);
     t_cur = t_nxt; t_nxt = t_nn; lse_cur = lse_nxt; delta_cur = delta_nxt; gate_cur = gate_nxt;
   }
 
@@ -584,6 +610,7 @@ struct Reduce3Args {
   const __nv_bfloat16* part_cmp; int slots_cmp, Lk_cmp, cmp_len, cmp_stride;
   const __nv_bfloat16* part_slc; const int32_t* pair_of_slot; int S;
   const __nv_bfloat16* part_win; int slots_win, window;
+  const float* acc;            // fp32 accumulator [units][T][G][D] holding the window + compression part, or null
   __nv_bfloat16* dq;
   int B, Hq, Hkv, T, G;
 };
@@ -621,6 +648,12 @@ __global__ void dq_reduce3_kernel(const Reduce3Args a) {
     }
   };
   const long long qrow = (long long)(bh * a.T + t);
+  if (a.acc) {
+    const float4* src = reinterpret_cast<const float4*>(a.acc + ((size_t)qrow * a.G + g) * D + v * 8);
+    const float4 lo = __ldg(src), hi = __ldg(src + 1);
+    acc[0] = lo.x; acc[1] = lo.y; acc[2] = lo.z; acc[3] = lo.w;
+    acc[4] = hi.x; acc[5] = hi.y; acc[6] = hi.z; acc[7] = hi.w;
+  }
   if (a.part_slc) {
     const int32_t* ps = a.pair_of_slot + (size_t)qrow * a.S;
     for (int s0 = 0; s0 < a.S; s0 += kTrip) {
@@ -655,18 +688,6 @@ __global__ void dq_reduce3_kernel(const Reduce3Args a) {
   u.z = pack_bf16(acc[4], acc[5]); u.w = pack_bf16(acc[6], acc[7]);
   *reinterpret_cast<uint4*>(a.dq + (((size_t)b * a.Hq + hkv * a.G + g) * a.T + t) * D + v * 8) = u;
 }
-
-#ifdef NSA_TRACE
-}  // namespace tc
-}  // namespace nsa
-static long long* g_trace_dev = nullptr;
-extern "C" long long* nsa_trace_buffer() {
-  if (!g_trace_dev) { cudaMalloc(&g_trace_dev, 2 * 48 * 12 * sizeof(long long)); cudaMemset(g_trace_dev, 0, 2 * 48 * 12 * sizeof(long long)); }
-  return g_trace_dev;
-}
-namespace nsa {
-namespace tc {
-#endif
 
 // Selection blocks whose row tiles were split over several work items collect dK / dV in the fp32
 // accumulators: this kernel clears the accumulator rows of those blocks before the backward
@@ -721,7 +742,7 @@ static BwdPlan plan_bwd(const AttnArgs& a) {
   } else {
     pl.n_slots = a.kind == 0 ? (a.window + kKeys - 2) / kKeys + 1 : pl.n_ktiles;
     pl.cap_pairs = 0;
-    part_rows = units * a.T * pl.n_slots;
+    part_rows = a.dq_acc ? 0 : units * a.T * pl.n_slots;   // accumulator mode: no partial buffer
   }
   size_t off = 0;
   pl.off_delta = off; off += align_up((size_t)a.B * a.Hq * a.T * sizeof(float), 256);
@@ -787,11 +808,9 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.T = a.T; p.Lk = a.Lk; p.G = G; p.nq = pl.nq;
   p.kind = a.kind; p.window = a.window; p.block_size = a.block_size;
   p.n_ktiles = pl.n_ktiles; p.n_slots = pl.n_slots;
+  p.dq_acc_mode = (a.dq_acc && a.kind != 2) ? 1 : 0;
   p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
   p.split_chunk = pl.split_chunk;
-#ifdef NSA_TRACE
-  p.trace = nsa_trace_buffer();
-#endif
   const size_t n_kv = (size_t)a.B * a.Hkv * a.Lk * a.D;
   p.dk_acc = (float*)(base + pl.off_acc);
   p.dv_acc = (float*)(base + pl.off_acc + align_up(n_kv * sizeof(float), 256));
@@ -828,10 +847,15 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   CUtensorMap tm_q_run, tm_do_run;
   if (rc == NSA_OK) rc = make_map_query_rows(&tm_q_run, a.q, a.D, a.T, a.B * a.Hq, G, pl.nq);
   if (rc == NSA_OK) rc = make_map_query_rows(&tm_do_run, a.d_o, a.D, a.T, a.B * a.Hq, G, pl.nq);
-  CUtensorMap tm_dq;
-  if (rc == NSA_OK)
+  CUtensorMap tm_dq, tm_dqacc;
+  if (rc == NSA_OK && p.dq_acc_mode) {
+    rc = make_map_dq_acc(&tm_dqacc, a.dq_acc, a.D, G, (size_t)a.T, (size_t)a.B * a.Hkv, pl.nq);
+    tm_dq = tm_dqacc;        // the partial-tile map is not used in this mode
+  } else if (rc == NSA_OK) {
     rc = a.kind == 2 ? make_map_partial(&tm_dq, p.dq_part, a.D, G, 1, pl.cap_pairs ? pl.cap_pairs : 1, 1, pl.nq)
                      : make_map_partial(&tm_dq, p.dq_part, a.D, G, pl.n_slots, a.T, (size_t)a.B * a.Hkv, pl.nq);
+    tm_dqacc = tm_dq;        // likewise
+  }
   if (rc != NSA_OK) return rc;
   const size_t smem = bwd_smem_bytes(a.D);
   dim3 grid(pl.n_ktiles, a.B * a.Hkv, pl.n_splits);
@@ -840,11 +864,11 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, p);
+    tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, tm_dqacc, p);
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
-    tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, p);
+    tc_bwd_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, tm_dqacc, p);
   }
   NSA_LAUNCH_OK("tc_bwd_kernel");
   if (a.kind == 2) {
@@ -858,7 +882,7 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
     if (rc2 == NSA_OK) rc2 = cast_f32_to(p.dv_acc, p.dv, n_kv, NSA_DTYPE_BF16, st);
     if (rc2 != NSA_OK) return rc2;
   }
-  if (!a.dq) return NSA_OK;   // the partials stay in the workspace for tc_dq_reduce3
+  if (!a.dq) return NSA_OK;   // the partials stay in the workspace (or the accumulator) for tc_dq_reduce3
   const size_t nthreads = (size_t)a.B * a.Hkv * a.T * G * (a.D / 8);
   const unsigned rgrid = (unsigned)((nthreads + 255) / 256);
   {
@@ -878,12 +902,14 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
 
 
 // dq of the whole op from the three branch workspaces (each written by tc_attn_bwd with a null
-// dq): `base` carries B, Hq, Hkv, T, D; a null workspace means the branch is absent.
+// dq) and / or the fp32 accumulator: `base` carries B, Hq, Hkv, T, D; a null workspace means the
+// branch is absent (or sits in the accumulator).
 int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int cmp_len, int cmp_stride, int S, int block_size,
-                  int window, const void* ws_cmp, const void* ws_slc, const void* ws_win, void* dq,
-                  cudaStream_t st) {
+                  int window, const void* ws_cmp, const void* ws_slc, const void* ws_win,
+                  const float* dq_acc, void* dq, cudaStream_t st) {
   using namespace tc;
   Reduce3Args r;
+  r.acc = dq_acc;
   r.part_cmp = r.part_slc = r.part_win = nullptr;
   r.pair_of_slot = nullptr;
   r.slots_cmp = r.slots_win = 1;

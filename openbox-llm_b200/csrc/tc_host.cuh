@@ -77,6 +77,25 @@ static inline int make_map_partial(CUtensorMap* m, void* base, int D, int G, siz
   return NSA_OK;
 }
 
+// 4-D map over the fp32 dQ accumulator [units][T][G][D] for reductions of boxes
+// 32 floats x G x box_tokens x 1: the G rows of box_tokens consecutive queries, one 128-byte
+// column slab at a time.
+static inline int make_map_dq_acc(CUtensorMap* m, void* base, int D, int G, size_t T, size_t units,
+                                  int box_tokens) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available"); return NSA_ERR_CUDA; }
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)G, (cuuint64_t)T, (cuuint64_t)units};
+  const cuuint64_t row = (cuuint64_t)D * 4;
+  cuuint64_t strides[3] = {row, row * G, row * G * T};
+  cuuint32_t box[4] = {32u, (cuuint32_t)G, (cuuint32_t)box_tokens, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (dq accumulator) failed with %d", (int)r); return NSA_ERR_CUDA; }
+  return NSA_OK;
+}
+
 static inline int group_pad(int G) {
   int gp = 1;
   while (gp < G) gp <<= 1;

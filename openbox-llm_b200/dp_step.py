@@ -117,6 +117,10 @@ class FusedAdamW:
         self.t = 0
 
     def step(self, grad_scale=1.0, lr=None):
+        with torch.cuda.device(self.flat.flat.device):    # the buffers' device, whatever is current
+            self._step(grad_scale, lr)
+
+    def _step(self, grad_scale, lr):
         f = self.flat
         self.t += 1
         self.sumsq.zero_()
@@ -143,13 +147,17 @@ class DataParallelStep:
     capture), which costs a millisecond of exposed transfer at this parameter count."""
 
     def __init__(self, model, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, grad_clip=1.0,
-                 bucket_bytes=64 << 20, group=None, use_graph=False, graph_warmup=3):
+                 bucket_bytes=64 << 20, group=None, use_graph=False, graph_warmup=3, status_every=50):
         self.model = model
         self.flat = FlatParams(model)
         self.buckets = GradBuckets(self.flat, group, bucket_bytes)
         self.opt = FusedAdamW(self.flat, lr, betas, eps, weight_decay, grad_clip)
         self.use_graph, self.graph_warmup = use_graph, graph_warmup
         self.graph, self.calls = None, 0
+        # every `status_every` steps the device status word is read (one stream synchronisation):
+        # a kernel that gave up a bounded wait makes every later attention kernel return at entry,
+        # which would otherwise go unnoticed for the rest of the run
+        self.status_every = status_every
 
     def _forward_backward(self, idx, targets):
         self.flat.zero_grad()
@@ -180,4 +188,11 @@ class DataParallelStep:
                 loss = self.g_loss
             self.buckets.reduce_all()
         self.opt.step(grad_scale=1.0 / self.buckets.world, lr=lr)
+        if self.status_every and self.calls % self.status_every == 0:
+            self.check_status()
         return loss
+
+    def check_status(self):
+        """Raise NsaError when a kernel of this device gave up a bounded wait since the last check."""
+        with torch.cuda.device(self.flat.flat.device):
+            L.check_device_status()

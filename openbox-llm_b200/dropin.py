@@ -52,12 +52,15 @@ def install(allow_synthetic=True):
     for mod_name, names in _EXPORTS.items():
         try:
             mod = importlib.import_module(mod_name)
-            how = "patched"
+            how = "synthetic" if getattr(mod, "_nsa_b200_synthetic", False) else "patched"
+            if how == "synthetic" and not allow_synthetic:
+                raise ImportError(f"{mod_name} is a stand-in registered by an earlier install()")
         except ImportError:
             if not allow_synthetic:
                 raise
             mod = types.ModuleType(mod_name)
             mod.__doc__ = "kernel-path names served by openbox-llm_b200"
+            mod._nsa_b200_synthetic = True
             sys.modules[mod_name] = mod
             how = "synthetic"
         for name, obj in names.items():

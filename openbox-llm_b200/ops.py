@@ -20,6 +20,7 @@ MODE_COMPRESS = L.MODE_COMPRESS
 MODE_COMPRESS_STRIDED = L.MODE_COMPRESS_STRIDED
 
 _impl = "auto"
+_deterministic = False
 
 
 def set_impl(name: str):
@@ -31,6 +32,20 @@ def set_impl(name: str):
 
 def get_impl() -> str:
     return _impl
+
+
+def set_deterministic(on: bool):
+    """Whole-op backward on tcgen05 shapes.  False (default): the window and compression
+    branches add their dQ tiles into one fp32 accumulator by TMA reduce-add (no partial buffers;
+    the order of the adds, hence the last bits of dq, varies from run to run).  True: every
+    branch keeps bf16 dQ partials and one kernel adds them in a fixed order, which makes dq
+    bit-reproducible at the price of the partial buffers."""
+    global _deterministic
+    _deterministic = bool(on)
+
+
+def get_deterministic() -> bool:
+    return _deterministic
 
 
 def set_option(name: str, value: int):
@@ -56,6 +71,7 @@ def _check_qkv(q, k, v):
 # ---------------------------------------------------------------------------------------
 # raw launch wrappers
 # ---------------------------------------------------------------------------------------
+@L.on_device
 def range_attn_forward(q, k, v, mode, window, block_size):
     """o, lse of the window (mode 0) or compression (mode 1) branch."""
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
@@ -69,6 +85,7 @@ def range_attn_forward(q, k, v, mode, window, block_size):
     return o, lse
 
 
+@L.on_device
 def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size, row_scale=None, row_dot=None,
                         defer_dq=False):
     """dq, dk, dv of a range branch.  With row_scale / row_dot (see nsa_gate_combine_bwd_rows) `do`
@@ -89,6 +106,24 @@ def range_attn_backward(q, k, v, o, lse, do, mode, window, block_size, row_scale
     return (ws if defer_dq else dq), dk, dv
 
 
+@L.on_device
+def range_attn_backward_acc(q, k, v, o, lse, do, mode, window, block_size, row_scale, row_dot, dq_acc):
+    """dk, dv of a gated range branch on a tcgen05 shape; its dQ is added to dq_acc
+    [B*Hkv, T, G, D] float32 (see nsa_range_attn_bwd_acc)."""
+    B, Hq, Hkv, T, D = _check_qkv(q, k, v)
+    q, k, v, do = (t.contiguous() for t in (q, k, v, do))
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
+    nws = L.lib().nsa_range_attn_bwd_acc_workspace_bytes(d, k.shape[2], mode, int(window))
+    ws = L.workspace(nws, q.device)
+    L.check(L.lib().nsa_range_attn_bwd_acc(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse), L.ptr(do),
+                                           L.ptr(dq_acc), L.ptr(dk), L.ptr(dv), d, k.shape[2], mode,
+                                           int(window), int(block_size), L.ptr(row_scale),
+                                           L.ptr(row_dot), L.ptr(ws), nws, L.stream()))
+    return dk, dv
+
+
+@L.on_device
 def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False):
     """nsa_selection_kernel.py:175-213.  q [B,Hq,T,D], k/v [B,Hkv,T,D], block_idx [B,Hkv,T,S]."""
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
@@ -108,6 +143,7 @@ def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False):
     return (o, lse) if return_lse else o
 
 
+@L.on_device
 def _selection_backward(q, k, v, block_idx, block_size, do, o, lse, row_scale=None, row_dot=None,
                         defer_dq=False):
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
@@ -135,6 +171,7 @@ def selection_backward_triton(q, k, v, block_idx, block_size, do, o):
 
 
 @torch.no_grad()
+@L.on_device
 def build_block_to_query_csr(block_idx, block_size):
     """nsa_fsa.py:14-64: (q_of_block [P], block_offsets [B,Hkv,n_blk+1], pair_bh [P]), int32."""
     B, Hkv, T, S = block_idx.shape
@@ -159,6 +196,7 @@ def _pool_dims(x, block_size):
     return B, H, T, D, T // block_size
 
 
+@L.on_device
 def _mean_pool_fwd(x, block_size):
     B, H, T, D, n_blk = _pool_dims(x, block_size)
     x = x.contiguous()
@@ -168,6 +206,7 @@ def _mean_pool_fwd(x, block_size):
     return out
 
 
+@L.on_device
 def _mean_pool_bwd(d_out, T, block_size):
     B, H, n_blk, D = d_out.shape
     d_out = d_out.contiguous()
@@ -182,6 +221,7 @@ def n_summaries(T, cmp_len, cmp_stride):
     return (T - cmp_len) // cmp_stride + 1 if T >= cmp_len else 0
 
 
+@L.on_device
 def _compress_fwd(x, intra, logits, proj, block_size, stride=None):
     stride = block_size if stride is None else stride
     B, H, T, D = x.shape
@@ -193,6 +233,7 @@ def _compress_fwd(x, intra, logits, proj, block_size, stride=None):
     return out
 
 
+@L.on_device
 def _compress_bwd(x, intra, logits, proj, d_out, block_size, stride=None):
     stride = block_size if stride is None else stride
     B, H, T, D = x.shape
@@ -209,6 +250,7 @@ def _compress_bwd(x, intra, logits, proj, d_out, block_size, stride=None):
 
 
 @torch.no_grad()
+@L.on_device
 def topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, return_importance=False, n_init_blocks=0,
                 n_local_blocks=0, cmp_len=None, cmp_stride=None):
     """Block scoring + top-n (nsa_model.py:343-355): block_idx [B,Hkv,T,n_sel] int32, ordered by
@@ -235,6 +277,7 @@ def topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, return_importance=False, n
     return (idx, imp) if return_importance else idx
 
 
+@L.on_device
 def _gate_fwd(o_cmp, o_slc, o_win, gate):
     B, Hq, T, D = o_cmp.shape
     out = torch.empty_like(o_cmp)
@@ -244,6 +287,7 @@ def _gate_fwd(o_cmp, o_slc, o_win, gate):
     return out
 
 
+@L.on_device
 def _gate_bwd(o_cmp, o_slc, o_win, gate, d_out):
     B, Hq, T, D = o_cmp.shape
     d_out = d_out.contiguous()
@@ -384,6 +428,7 @@ class _NSAAttention(torch.autograd.Function):
     top-n -> selection attention -> window attention -> gate combine.  Saves q once."""
 
     @staticmethod
+    @L.on_device
     def forward(ctx, q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
                 block_idx, forced, k_intra, k_logits, k_proj, v_intra, v_logits, v_proj):
         learned = k_intra is not None
@@ -414,9 +459,12 @@ class _NSAAttention(torch.autograd.Function):
                    tuple(t.dtype for t in (k_intra, k_logits, k_proj, v_intra, v_logits, v_proj))
                    if learned else None, cl, cs)
         ctx.mark_non_differentiable(block_idx)
+        if L.CHECK_STATUS_EVERY_CALL:
+            L.check_device_status()
         return out, block_idx
 
     @staticmethod
+    @L.on_device
     def backward(ctx, d_out, _d_idx):
         (q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o_cmp, o_slc, o_win,
          lse_cmp, lse_slc, lse_win, block_idx, *cp) = ctx.saved_tensors
@@ -436,23 +484,42 @@ class _NSAAttention(torch.autograd.Function):
         # kernel adds them all; otherwise three dq tensors and a sum
         fused = (_impl != "simt" and S > 0 and q.dtype == torch.bfloat16 and
                  tc_supported(B, Hq, ks.shape[1], T, q.shape[3], q.dtype, block_size))
-        dq, dk_cmp, dv_cmp = range_attn_backward(q, k_cmp, v_cmp, o_cmp, lse_cmp, d_out,
-                                                 MODE_COMPRESS_STRIDED, cs, cl, rs[0], rd[0],
-                                                 defer_dq=fused)
-        dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
-                                            rs[1], rd[1], defer_dq=fused)
-        dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, d_out, MODE_WINDOW, window, 0,
-                                            rs[2], rd[2], defer_dq=fused)
         dq_sum = torch.empty_like(q)
-        if fused:
-            n_cmp = k_cmp.shape[2]
-            d = L.dims(B, Hq, ks.shape[1], T, q.shape[3], L.dtype_code(q))
-            L.check(L.lib().nsa_dq_reduce3(d, n_cmp, int(cl), int(cs), S, int(block_size), int(window),
-                                           L.ptr(dq) if n_cmp > 0 else None, L.ptr(dq2), L.ptr(dq3),
-                                           L.ptr(dq_sum), L.stream()))
+        dm = L.dims(B, Hq, ks.shape[1], T, q.shape[3], L.dtype_code(q))
+        n_cmp = k_cmp.shape[2]
+        if fused and not _deterministic:
+            # window and compression add their dQ into one fp32 accumulator; only the selection
+            # branch keeps partials (its rows are gathered, the adds would miss L2)
+            G = Hq // ks.shape[1]
+            dq_acc = torch.zeros(B * ks.shape[1], T, G, q.shape[3], device=q.device, dtype=torch.float32)
+            if n_cmp > 0:
+                dk_cmp, dv_cmp = range_attn_backward_acc(q, k_cmp, v_cmp, o_cmp, lse_cmp, d_out,
+                                                         MODE_COMPRESS_STRIDED, cs, cl, rs[0], rd[0], dq_acc)
+            else:
+                dk_cmp, dv_cmp = torch.zeros_like(k_cmp), torch.zeros_like(v_cmp)
+            dkw, dvw = range_attn_backward_acc(q, kw, vw, o_win, lse_win, d_out, MODE_WINDOW, window, 0,
+                                               rs[2], rd[2], dq_acc)
+            ws2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
+                                                rs[1], rd[1], defer_dq=True)
+            L.check(L.lib().nsa_dq_finish(dm, S, int(block_size), L.ptr(dq_acc), L.ptr(ws2), L.ptr(dq_sum),
+                                          L.stream()))
+            del ws2, dq_acc
         else:
-            L.check(L.lib().nsa_sum3(L.ptr(dq), L.ptr(dq2), L.ptr(dq3), L.ptr(dq_sum), dq.numel(),
-                                     L.dtype_code(dq), L.stream()))
+            dq, dk_cmp, dv_cmp = range_attn_backward(q, k_cmp, v_cmp, o_cmp, lse_cmp, d_out,
+                                                     MODE_COMPRESS_STRIDED, cs, cl, rs[0], rd[0],
+                                                     defer_dq=fused)
+            dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
+                                                rs[1], rd[1], defer_dq=fused)
+            dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, d_out, MODE_WINDOW, window, 0,
+                                                rs[2], rd[2], defer_dq=fused)
+            if fused:
+                L.check(L.lib().nsa_dq_reduce3(dm, n_cmp, int(cl), int(cs), S, int(block_size), int(window),
+                                               L.ptr(dq) if n_cmp > 0 else None, L.ptr(dq2), L.ptr(dq3),
+                                               L.ptr(dq_sum), L.stream()))
+            else:
+                L.check(L.lib().nsa_sum3(L.ptr(dq), L.ptr(dq2), L.ptr(dq3), L.ptr(dq_sum), dq.numel(),
+                                         L.dtype_code(dq), L.stream()))
+            del dq, dq2, dq3
         dq = dq_sum
         pgrads = [None] * 6
         if learned:
@@ -462,6 +529,8 @@ class _NSAAttention(torch.autograd.Function):
         else:
             dkc = _mean_pool_bwd(dk_cmp, T, block_size)
             dvc = _mean_pool_bwd(dv_cmp, T, block_size)
+        if L.CHECK_STATUS_EVERY_CALL:
+            L.check_device_status()
         return (dq, dkc, dvc, dks, dvs, dkw, dvw, d_gate.to(gate_dtype), None, None, None, None, None,
                 *pgrads)
 
@@ -479,7 +548,9 @@ def nsa_attention(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, win
     list ahead of the scored ones (the published NSA recipe; the reference has no such option).
     cmp_len / cmp_stride (learned pooling only; default block_size, the reference's grid) make
     the summaries windows of cmp_len tokens every cmp_stride tokens, e.g. 32 / 16 with 64-token
-    selection blocks; the compressor parameters then have cmp_len positions."""
+    selection blocks; the compressor parameters then have cmp_len positions.
+    With NSA_B200_CHECK_STATUS=1 in the environment the device status word is read (one stream
+    synchronisation) after every forward and backward and a give-up raises NsaError."""
     cp = [None] * 6
     if compressor is not None:
         cp = [compressor[n] for n in ("k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj")]

@@ -20,3 +20,17 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The worst measured error of each kind of tensor over the session, next to its bound."""
+    try:
+        from tests.util import WORST
+    except Exception:
+        return
+    if not WORST:
+        return
+    terminalreporter.write_line("worst measured errors (max-abs, rel-L2, fraction of the max-abs bound, where):")
+    for key in sorted(WORST):
+        ma, rl, frac, what = WORST[key]
+        terminalreporter.write_line(f"  {key:<14s} {ma:.3e}  {rl:.3e}  {frac:5.2f}  {what}")

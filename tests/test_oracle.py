@@ -246,3 +246,32 @@ def test_block_importance_and_forced_lists():
     for row in idx.view(-1, S)[::37]:                                # no block twice
         kept = row[row >= 0]
         assert kept.unique().numel() == kept.numel()
+
+
+def test_sampled_unit_check_agrees_with_the_whole_oracle():
+    """The sampled checks the GPU tests use at the benchmark sizes (tests/util.check_unit_sampled:
+    some query rows, some window key tiles, some selection blocks, the compression branch of one
+    unit) reproduce the whole-op oracle when fed the oracle's own results."""
+    from tests.util import check_unit_sampled, unit_slices
+    B, Hq, Hkv, T, D, bs, S, W = 2, 8, 2, 640, 32, 64, 3, 100
+    G = Hq // Hkv
+    g = torch.Generator().manual_seed(3)
+    t = {"q": torch.randn(B, Hq, T, D, generator=g) * D ** -0.5}
+    for n in ("kc", "vc", "ks", "vs", "kw", "vw"):
+        t[n] = torch.randn(B, Hkv, T, D, generator=g) * D ** -0.5
+    t["gate"] = torch.randn(B, Hq, T, 3, generator=g)
+    t["do"] = torch.randn(B, Hq, T, D, generator=g)
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+    fwd = O.stream_nsa_forward(*(t[n] for n in names), bs, S, W)
+    grads = O.stream_nsa_backward(*(t[n] for n in names), bs, W, fwd, t["do"])
+    t["block_idx"] = fwd["block_idx"]
+    for b, h in ((0, 1), (1, 0)):
+        u = unit_slices(t, b, h, G)
+        got = unit_slices({"q": grads["q"], "gate": grads["gate"], "ks": grads["ks"], "vs": grads["vs"],
+                           "kw": grads["kw"], "vw": grads["vw"]}, b, h, G)
+        got["out"] = fwd["out"][b:b + 1, h * G:(h + 1) * G]
+        k_cmp, v_cmp = fwd["k_cmp"][b:b + 1, h:h + 1], fwd["v_cmp"][b:b + 1, h:h + 1]
+        dk_cmp, dv_cmp = check_unit_sampled(u, k_cmp, v_cmp, got, T, bs, W, torch.float32, "self",
+                                            [(0, 70), (300, 420), (600, 640)], [0, 4, 9], [0, 3, 8])
+        dkc = O.mean_pool_backward(dk_cmp, T, bs)
+        assert (dkc - grads["kc"][b:b + 1, h:h + 1]).abs().max().item() <= 1e-5

@@ -72,3 +72,56 @@ def test_two_ranks_reproduce_the_unsharded_op():
                                 t["gate"], 16, 3, 24)
     assert torch.equal(idx, full["block_idx"])
     assert (merged - full["out"]).abs().max().item() <= 1e-6
+
+
+@pytest.mark.gpu
+def test_unit_shards_on_the_gpu_reproduce_the_unsharded_call_bit_for_bit():
+    """What bench.py does under torchrun, on one GPU: the 4 (batch, kv-head) units of a call are
+    run as two shards of two units, back to back, through the CUDA kernels; the merged out, block
+    lists and every per-unit gradient equal the unsharded call bit for bit (bit-reproducible dq
+    path), and the shards' compressor parameter gradients add up to the unsharded ones."""
+    nsa = importlib.import_module("openbox-llm_b200")
+    dtype = torch.bfloat16
+    B, Hq, Hkv, T, D, bs, n_sel, W = 2, 16, 2, 1024, 128, 64, 8, 200
+    G = Hq // Hkv
+    g = torch.Generator().manual_seed(12)
+    mk = lambda h: (torch.randn(B, h, T, D, generator=g) * D ** -0.5).to(dtype).cuda()
+    t = {"q": mk(Hq)}
+    for n in ("kc", "vc", "ks", "vs", "kw", "vw"):
+        t[n] = mk(Hkv)
+    t["gate"] = torch.randn(B, Hq, T, 3, generator=g).to(dtype).cuda()
+    do = torch.randn(B, Hq, T, D, generator=g).to(dtype).cuda()
+    comp = {}
+    for p in ("k", "v"):
+        comp[p + "_intra"] = (0.02 * torch.randn(bs, D, generator=g)).cuda()
+        comp[p + "_logits"] = (0.3 * torch.randn(bs, generator=g)).cuda()
+        comp[p + "_proj"] = (torch.randn(D, D, generator=g) * D ** -0.5).cuda()
+    names = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
+
+    def run(tensors, d_out):
+        ins = [tensors[n].clone().requires_grad_(True) for n in names]
+        cps = {k: v.clone().requires_grad_(True) for k, v in comp.items()}
+        out, idx = nsa.nsa_attention(*ins, bs, n_sel, W, compressor=cps, return_block_idx=True)
+        out.backward(d_out)
+        return out.detach(), idx, [x.grad for x in ins], {k: v.grad for k, v in cps.items()}
+
+    nsa.set_deterministic(True)
+    try:
+        full_out, full_idx, full_g, full_p = run(t, do)
+        parts = []
+        for rank in range(2):
+            a, b = S.unit_range(B * Hkv, 2, rank)
+            loc = {n: S.slice_units(x, Hkv, a, b).contiguous() for n, x in t.items()}
+            parts.append(run(loc, S.slice_units(do, Hkv, a, b).contiguous()))
+    finally:
+        nsa.set_deterministic(False)
+    assert torch.equal(S.merge_units([p[0] for p in parts], B, Hkv), full_out)
+    assert torch.equal(torch.cat([p[1] for p in parts], 0).reshape(B, Hkv, T, n_sel), full_idx)
+    for i, n in enumerate(names):
+        merged = S.merge_units([p[2][i] for p in parts], B, Hkv)
+        assert torch.equal(merged, full_g[i]), n
+    for k in comp:
+        s = parts[0][3][k] + parts[1][3][k]
+        ref = full_p[k]
+        assert (s - ref).abs().max().item() <= 1e-3 * max(1.0, ref.abs().max().item()), k
+    assert nsa.lib().nsa_device_status(None) == 0
