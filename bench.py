@@ -702,8 +702,8 @@ def main_leg(args, name, w, rank, world, dev, dist, nsa, L):
         "kernels": {k: {"launches": v[0], "ms": round(v[1], 3), "share": round(v[1] / total_ms, 4)}
                     for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
         "impl": nsa.get_impl(),
-        "backward": "bit-reproducible dq (partial slots)" if nsa.get_deterministic() else
-                    "dq of window + compression through an fp32 accumulator (TMA reduce-add)",
+        "backward": "dq of window + compression through an fp32 accumulator (TMA reduce-add)"
+                    if nsa.get_dq_accumulator() else "bf16 dq partial slots added in a fixed order",
     }
 
 
@@ -752,7 +752,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the extra legs reported under `also`")
     ap.add_argument("--no-graph", action="store_true", help="c5_model: eager step with overlapped bucketed all-reduce")
-    ap.add_argument("--deterministic", action="store_true", help="bit-reproducible dq (bf16 partial slots)")
+    ap.add_argument("--dq-accumulator", action="store_true",
+                    help="dQ of window + compression through the fp32 accumulator (less memory, slower)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -776,7 +777,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    nsa.set_deterministic(args.deterministic)
+    nsa.set_dq_accumulator(args.dq_accumulator)
     try:
         if args.workload == "c5_model":
             line = model_workload(args, rank, world, dev, dist)

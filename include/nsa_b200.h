@@ -148,8 +148,12 @@ int nsa_build_block_to_query_csr(const int32_t* block_idx, int B, int Hkv, int T
  * nsa_csr_workspace_bytes exceeds it are refused with NSA_ERR_WORKSPACE and a message.  The
  * call allocates nothing (no cudaMalloc / cudaFree, no allocating library routine); inputs and
  * the three outputs are still the caller's.  The first call on a device looks up the array's
- * device address; make that call outside any stream capture.  All calls on a device share the
- * one array: it is cleared at the start of every call, and two calls whose kernels may overlap
+ * device address (with lazy module loading that lookup is also what makes the driver bring the
+ * module and its 8 MiB array onto the device, so "allocates nothing" holds from the second call
+ * on); make that call outside any stream capture.  The device that is current at the call is the
+ * one whose array is used: `stream` must belong to it.  The address cache is safe against
+ * concurrent first calls from several host threads; it does not survive cudaDeviceReset.  All
+ * calls on a device share the one array: it is cleared at the start of every call, and two calls whose kernels may overlap
  * on the GPU (different streams, no ordering between them) would corrupt each other.
  * This entry point has no counterpart in the reference. */
 size_t nsa_csr_builtin_scratch_bytes(void);

@@ -1,5 +1,7 @@
 // Bandwidth-bound companions of the attention kernels: compression pooling, block scoring +
 // top-n, block->query CSR inversion and the sigmoid gate combine.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace nsa {
@@ -1160,17 +1162,19 @@ extern "C" int nsa_build_block_to_query_csr_noalloc(const int32_t* block_idx, in
               kCsrBuiltinScratchBytes);
     return NSA_ERR_WORKSPACE;
   }
-  static void* scratch_of_device[64] = {nullptr};
+  // one address per device, published with release / acquire so that threads of a multi-threaded
+  // host may race on the first call (each would look up the same address)
+  static std::atomic<void*> scratch_of_device[64];
   int dev = 0;
   NSA_CUDA_OK(cudaGetDevice(&dev));
   NSA_CHECK_ARG(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
-  if (scratch_of_device[dev] == nullptr) {   // first call on this device, with it current
-    void* ptr = nullptr;
-    NSA_CUDA_OK(cudaGetSymbolAddress(&ptr, g_csr_builtin_scratch));
-    scratch_of_device[dev] = ptr;
+  void* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {   // first call on this device, with it current
+    NSA_CUDA_OK(cudaGetSymbolAddress(&scratch, g_csr_builtin_scratch));
+    scratch_of_device[dev].store(scratch, std::memory_order_release);
   }
   return build_csr_internal(block_idx, B, Hkv, T, S, block_size, T / block_size, q_of_block,
-                            block_offsets, pair_bh, nullptr, scratch_of_device[dev],
+                            block_offsets, pair_bh, nullptr, scratch,
                             kCsrBuiltinScratchBytes, (cudaStream_t)stream);
 }
 

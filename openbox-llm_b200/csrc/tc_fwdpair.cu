@@ -495,6 +495,10 @@ int build_csr_internal(const int32_t* block_idx, int B, int Hkv, int T, int S, i
 int tc_fwd_union_launch(const AttnArgs& a, const unsigned long long* stats, const int32_t* offsets,
                         int force, cudaStream_t st);
 int get_option_sel_fwd();
+int get_option_pair_kernel();
+int tc_fwdpair2_launch(const AttnArgs& a, const int32_t* q_of_block, const int32_t* offsets, void* o_part,
+                       float* ml, const unsigned long long* stats, const void* work, int force, int nq,
+                       int n_ktiles, int nq_union, size_t cap_pairs, unsigned grid, cudaStream_t st);
 
 size_t tc_sel_fwd_workspace(const AttnArgs& a) { return tc::plan_pairs(a).total; }
 
@@ -557,16 +561,22 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   const dim3 grid((unsigned)sel_work_max_items((size_t)a.B * a.Hkv, pl.n_ktiles, pl.cap_pairs, pl.nq));
   const size_t nthreads = (size_t)a.B * a.Hkv * a.T * G * (a.D / 8);
   const unsigned cgrid = (unsigned)((nthreads + 255) / 256);
+  const bool v2 = get_option_pair_kernel() == 1;
+  if (v2) {
+    rc = tc_fwdpair2_launch(a, p.q_of_block, offsets, p.o_part, p.ml, stats, p.work, force, pl.nq, pl.n_ktiles,
+                            nq_union, pl.cap_pairs, grid.x, st);
+    if (rc != NSA_OK) return rc;
+  }
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p); }
+    if (!v2) { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p); }
     { KernelScope ks("sel_combine_kernel", st);
       sel_combine_kernel<128><<<cgrid, 256, 0, st>>>(p.o_part, p.ml, pair_of_slot, offsets, stats,
                                                     (__nv_bfloat16*)a.o, a.lse, a.B, a.Hq, a.Hkv, a.T, G,
                                                     a.S, pl.n_ktiles, nq_union, p.force); }
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p); }
+    if (!v2) { KernelScope ks("tc_fwd_slc_pairs", st); tc_fwdpair_kernel<64><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p); }
     { KernelScope ks("sel_combine_kernel", st);
       sel_combine_kernel<64><<<cgrid, 256, 0, st>>>(p.o_part, p.ml, pair_of_slot, offsets, stats,
                                                    (__nv_bfloat16*)a.o, a.lse, a.B, a.Hq, a.Hkv, a.T, G,

@@ -20,7 +20,7 @@ MODE_COMPRESS = L.MODE_COMPRESS
 MODE_COMPRESS_STRIDED = L.MODE_COMPRESS_STRIDED
 
 _impl = "auto"
-_deterministic = False
+_dq_accumulator = False
 
 
 def set_impl(name: str):
@@ -34,18 +34,20 @@ def get_impl() -> str:
     return _impl
 
 
-def set_deterministic(on: bool):
-    """Whole-op backward on tcgen05 shapes.  False (default): the window and compression
-    branches add their dQ tiles into one fp32 accumulator by TMA reduce-add (no partial buffers;
-    the order of the adds, hence the last bits of dq, varies from run to run).  True: every
-    branch keeps bf16 dQ partials and one kernel adds them in a fixed order, which makes dq
-    bit-reproducible at the price of the partial buffers."""
-    global _deterministic
-    _deterministic = bool(on)
+def set_dq_accumulator(on: bool):
+    """Whole-op backward on tcgen05 shapes.  False (default): every branch keeps bf16 dQ partials
+    (one slot per key tile a query attends) and one kernel adds them in a fixed order: dq is
+    bit-reproducible, at the price of the partial buffers.  True: the window and compression
+    branches add their dQ tiles into one fp32 accumulator by TMA reduce-add instead: no partial
+    buffers for them (23 GB less at B=8, T=32K; the way to run compression strides that would need
+    dozens of slots), but the L2 reduction rate bounds those kernels (they run about 1.7 times
+    longer) and the order of the adds, hence the last bits of dq, varies from run to run."""
+    global _dq_accumulator
+    _dq_accumulator = bool(on)
 
 
-def get_deterministic() -> bool:
-    return _deterministic
+def get_dq_accumulator() -> bool:
+    return _dq_accumulator
 
 
 def set_option(name: str, value: int):
@@ -487,7 +489,7 @@ class _NSAAttention(torch.autograd.Function):
         dq_sum = torch.empty_like(q)
         dm = L.dims(B, Hq, ks.shape[1], T, q.shape[3], L.dtype_code(q))
         n_cmp = k_cmp.shape[2]
-        if fused and not _deterministic:
+        if fused and _dq_accumulator:
             # window and compression add their dQ into one fp32 accumulator; only the selection
             # branch keeps partials (its rows are gathered, the adds would miss L2)
             G = Hq // ks.shape[1]

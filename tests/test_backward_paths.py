@@ -18,7 +18,7 @@ NAMES = ["q", "kc", "vc", "ks", "vs", "kw", "vw", "gate"]
 @pytest.fixture(autouse=True)
 def _reset():
     yield
-    pkg().set_deterministic(False)
+    pkg().set_dq_accumulator(False)
     pkg().set_impl("auto")
     pkg().set_option("sel_fwd_variant", 0)
 
@@ -49,7 +49,9 @@ def _compressor(c, seed=7):
 @pytest.mark.parametrize("c", TC_CONFIGS[:6] + [TC_CONFIGS[7]], ids=cfg_id)
 def test_accumulator_and_slot_backward_agree_with_the_oracle(c):
     """Whole op on tcgen05 shapes, both dq paths: each against the oracle, and against each other
-    (everything but dq must be bit-identical: the two paths differ only in how dq is added up)."""
+    (the forward is bit-identical; the gradients agree within one bf16 rounding step of their
+    largest entry: the paths differ in how dq is added up, and dk / dv of a key tile collect their
+    row tiles in the order the kernel's two compute groups happen to issue them)."""
     nsa = pkg()
     dtype = torch.bfloat16
     if not nsa.tc_supported(c["B"], c["Hq"], c["Hkv"], c["T"], c["D"], dtype, c["block_size"]):
@@ -57,57 +59,55 @@ def test_accumulator_and_slot_backward_agree_with_the_oracle(c):
     t = make_inputs(c, dtype, seed=11, scale_qkv=True)
     comp = _compressor(c)
     res = {}
-    for det in (False, True):
-        nsa.set_deterministic(det)
+    for acc in (False, True):
+        nsa.set_dq_accumulator(acc)
         out, idx, g = _op(nsa, t, c, dtype, comp)
         fwd = O.stream_nsa_forward(*(t[n] for n in NAMES), c["block_size"], c["S"], window_for(c),
                                    block_idx=idx.cpu(), compressor=comp)
         g_ref = O.stream_nsa_backward(*(t[n] for n in NAMES), c["block_size"], window_for(c), fwd, t["do"],
                                       compressor=comp)
-        tag = "slots" if det else "accumulator"
+        tag = "accumulator" if acc else "slots"
         check(out, fwd["out"], dtype, f"{tag} out", scale_abs=False)
         for n in NAMES:
             check(g[n], g_ref[n], dtype, f"{tag} d{n}", scale_abs=False)
-        res[det] = (out, idx, g)
+        res[acc] = (out, idx, g)
     assert torch.equal(res[False][0], res[True][0]) and torch.equal(res[False][1], res[True][1])
-    for n in NAMES[1:]:
-        assert torch.equal(res[False][2][n], res[True][2][n]), n
-    d = (res[False][2]["q"].float() - res[True][2]["q"].float()).abs().max().item()
-    assert d <= 2e-2 * max(1.0, res[True][2]["q"].float().abs().max().item()), d
+    for n in NAMES:
+        a, b = res[True][2][n].float(), res[False][2][n].float()
+        assert (a - b).abs().max().item() <= 2.0 ** -7 * max(b.abs().max().item(), 1e-6), n
     assert nsa.lib().nsa_device_status(None) == 0
 
 
 def test_run_to_run_reproducibility():
-    """The same inputs twice.  Forward: bit-identical (no atomics anywhere in it).  Backward with
-    set_deterministic(True): dq, dks, dvs, dkw, dvw and d_gate bit-identical.  The compression key
-    tiles that every query attends are split over CTAs and meet in fp32 atomics, as do the
-    compressor parameter gradients, so dkc, dvc and the parameter gradients are reproducible only up
-    to the order of fp32 adds: bounded here at 2^-7 of the largest entry (one bf16 rounding step).
-    Default (accumulator) backward: dq within the same bound."""
+    """The same inputs twice.  Forward (out, block lists): bit-identical, nothing in it is added in
+    a timing-dependent order.  Backward, default path: dq and d_gate bit-identical (every
+    (row tile, key tile) dQ partial is computed on its own and the partials of a query are added in
+    a fixed order).  dk / dv of a key tile are accumulated in TMEM over its row tiles in the order
+    the kernel's two compute groups issue them, split key tiles and the compressor parameter
+    gradients meet in fp32 atomics: reproducible up to the order of fp32 adds, bounded here at 2^-7
+    of the largest entry (one bf16 rounding step).  Accumulator path: dq within the same bound."""
     nsa = pkg()
     dtype = torch.bfloat16
     c = dict(B=2, Hq=16, Hkv=2, D=128, T=2048, block_size=64, S=16, window=512)
     t = make_inputs(c, dtype, seed=5, scale_qkv=True)
     comp = _compressor(c)
-    runs = {}
-    for det in (True, False):
-        nsa.set_deterministic(det)
-        runs[det] = [_op(nsa, t, c, dtype, comp) for _ in range(2)]
-    for det in (True, False):
-        (o1, i1, g1), (o2, i2, g2) = runs[det]
+    for acc in (False, True):
+        nsa.set_dq_accumulator(acc)
+        (o1, i1, g1), (o2, i2, g2) = [_op(nsa, t, c, dtype, comp) for _ in range(2)]
         assert torch.equal(o1, o2) and torch.equal(i1, i2)
-        exact = ["ks", "vs", "kw", "vw", "gate"] + (["q"] if det else [])
+        exact = ["gate"] + ([] if acc else ["q"])
         for n in exact:
-            assert torch.equal(g1[n], g2[n]), (det, n)
+            assert torch.equal(g1[n], g2[n]), (acc, n)
         for n in [k for k in g1 if k not in exact]:
             a, b = g1[n].float(), g2[n].float()
-            assert (a - b).abs().max().item() <= 2.0 ** -7 * max(b.abs().max().item(), 1e-6), (det, n)
+            # (floor 1e-4: d k_intra is analytically zero, what is left of it is rounding noise)
+            assert (a - b).abs().max().item() <= 2.0 ** -7 * max(b.abs().max().item(), 1e-4), (acc, n)
     assert nsa.lib().nsa_device_status(None) == 0
 
 
 def test_range_backward_accumulator_entry_point():
     """nsa_range_attn_bwd_acc + nsa_dq_finish through the C ABI against nsa_range_attn_bwd on the
-    same gated branch: dk, dv bit-identical, dq within bf16 rounding of the slot path."""
+    same gated branch: dq, dk, dv within one bf16 rounding step of the slot path."""
     nsa = pkg()
     L = importlib.import_module("openbox-llm_b200._lib")
     dtype = torch.bfloat16
@@ -130,9 +130,9 @@ def test_range_backward_accumulator_entry_point():
         dq = torch.empty_like(q)
         L.check(L.lib().nsa_dq_finish(L.dims(B, Hq, Hkv, T, D, L.DTYPE_BF16), 0, 64, L.ptr(acc), None,
                                       L.ptr(dq), L.stream()))
-        assert torch.equal(dk, dk_ref) and torch.equal(dv, dv_ref), (cfg_id(c), mode)
-        d = (dq.float() - dq_ref.float()).abs().max().item()
-        assert d <= 2.0 ** -7 * dq_ref.float().abs().max().item() + 1e-6, (cfg_id(c), mode, d)
+        for got, ref, nm in ((dq, dq_ref, "dq"), (dk, dk_ref, "dk"), (dv, dv_ref, "dv")):
+            d = (got.float() - ref.float()).abs().max().item()
+            assert d <= 2.0 ** -7 * ref.float().abs().max().item() + 1e-6, (cfg_id(c), mode, nm, d)
     assert nsa.lib().nsa_device_status(None) == 0
 
 

@@ -491,8 +491,10 @@ def test_headline_shape_properties():
     for p_, x, dcmp in (("k", f["kc"], dk_cmp), ("v", f["vc"], dv_cmp)):
         ref = O.compressor_backward(x, comp[p_ + "_intra"], comp[p_ + "_logits"], comp[p_ + "_proj"], bs, dcmp)
         for name, r in zip(("intra", "logits", "proj"), ref[1:]):
+            # (d k_intra is zero analytically: intra_pos shifts every summary key by the same vector,
+            # which a softmax over the summaries does not see; only rounding noise is left of it)
             ma, rl = err(comp_d[f"{p_}_{name}"].grad, r)
-            assert rl <= 2e-2, f"8K d{p_}_{name}: rel-L2 {rl:.3e} (max-abs {ma:.3e})"
+            assert rl <= 2e-2 or ma <= 1e-4, f"8K d{p_}_{name}: rel-L2 {rl:.3e} (max-abs {ma:.3e})"
 
 
 def test_long_context_forward_shape():
@@ -538,8 +540,8 @@ def test_model_layer_shape_whole_oracle():
     for n in NAMES:
         check(grads[n], g_ref[n], dtype, "model-layer shape d" + n, scale_abs=False)
     for k in comp:
-        ma, rl = err(comp_d[k].grad, g_ref[k])
-        assert rl <= 2e-2, f"model-layer shape d{k}: rel-L2 {rl:.3e} (max-abs {ma:.3e})"
+        ma, rl = err(comp_d[k].grad, g_ref[k])       # d k_intra is analytically zero: noise on both sides
+        assert rl <= 2e-2 or ma <= 1e-4, f"model-layer shape d{k}: rel-L2 {rl:.3e} (max-abs {ma:.3e})"
 
 
 def test_module_under_activation_checkpointing():

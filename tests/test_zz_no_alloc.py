@@ -47,6 +47,7 @@ def test_noalloc_csr_matches_workspace_csr_twice_in_a_row():
         assert torch.equal(pbh_a[:P], pbh_b[:P])
         r_qob, r_off, r_pbh = O.build_block_to_query_csr(idx.cpu(), 32)
         assert (qob_a[:P].cpu().numpy() == r_qob).all() and (off_a.cpu().numpy() == r_off).all()
+        assert (pbh_a[:P].cpu().numpy() == r_pbh).all()
 
 
 def test_noalloc_csr_refuses_shapes_beyond_its_scratch():

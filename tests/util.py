@@ -97,18 +97,22 @@ def check(a, b, dtype, what, abs32=2e-3, abs16=2e-2, rel16=1e-2, scale_abs=True)
     """fp32: max-abs <= abs32 (the reference's fp32 gates are 2e-3..4e-3).
     bf16, inputs scaled as the benchmark configurations scale them (q, k, v times D^-1/2; call with
     scale_abs=False): max-abs <= abs16 = 2e-2 and relative L2 <= rel16 = 1e-2 against the fp32
-    oracle on the bf16-rounded inputs.  bf16 with unscaled N(0,1) inputs (the reference's own gate
-    inputs, where gradients reach tens): the absolute bound is taken relative to the largest
-    reference entry, max-abs <= abs16 * max(1, max|b|); the relative-L2 bound is the same."""
+    oracle on the bf16-rounded inputs.  A bf16 result cannot be closer to a reference entry x than
+    |x| * 2^-9 (round to nearest, 8 significant bits), so where the reference holds entries above
+    5.12 (dV with dO ~ N(0,1) does) the absolute bound is max(2e-2, 2^-8 * max|b|): the rounding
+    of the largest entry plus as much again.  bf16 with unscaled N(0,1) inputs (the reference's
+    own gate inputs, where gradients reach tens): the absolute bound is taken relative to the
+    largest reference entry, max-abs <= abs16 * max(1, max|b|); the relative-L2 bound is the same."""
     ma, rl = err(a, b)
     assert not torch.isnan(a.float()).any(), what + ": NaN"
     if dtype == torch.float32:
         _record(what, dtype, ma, rl, abs32)
         assert ma <= abs32, f"{what}: max-abs {ma:.3e} > {abs32} (rel-L2 {rl:.3e})"
     else:
-        mag = max(1.0, b.abs().max().item()) if scale_abs else 1.0
-        _record(what, dtype, ma, rl, abs16 * mag)
-        assert ma <= abs16 * mag, f"{what}: max-abs {ma:.3e} > {abs16 * mag:.3e} (rel-L2 {rl:.3e})"
+        bmax = b.abs().max().item() if b.numel() else 0.0
+        bound = abs16 * max(1.0, bmax) if scale_abs else max(abs16, 2.0 ** -8 * bmax)
+        _record(what, dtype, ma, rl, bound)
+        assert ma <= bound, f"{what}: max-abs {ma:.3e} > {bound:.3e} (rel-L2 {rl:.3e}, max|ref| {bmax:.3g})"
         assert rl <= rel16, f"{what}: rel-L2 {rl:.3e} > {rel16} (max-abs {ma:.3e})"
 
 
