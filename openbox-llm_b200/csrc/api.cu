@@ -58,8 +58,10 @@ void kernel_end(cudaStream_t st) {
 
 static std::atomic<int> g_opt_sel_fwd{0};
 int get_option_sel_fwd() { return g_opt_sel_fwd.load(); }
-static std::atomic<int> g_opt_pair_kernel{0};
+static std::atomic<int> g_opt_pair_kernel{1};
 int get_option_pair_kernel() { return g_opt_pair_kernel.load(); }
+static std::atomic<int> g_opt_merged{1};
+int get_option_merged_boxes() { return g_opt_merged.load(); }
 static std::atomic<int> g_opt_bwd_kernel{0};
 int get_option_bwd_kernel() { return g_opt_bwd_kernel.load(); }
 
@@ -149,6 +151,10 @@ extern "C" int nsa_set_option(const char* name, int value) {
   }
   if (name && strcmp(name, "sel_pair_kernel") == 0 && value >= 0 && value <= 1) {
     g_opt_pair_kernel.store(value);
+    return NSA_OK;
+  }
+  if (name && strcmp(name, "merged_boxes") == 0 && value >= 0 && value <= 1) {
+    g_opt_merged.store(value);
     return NSA_OK;
   }
   if (name && strcmp(name, "bwd_kernel") == 0 && value >= 0 && value <= 1) {

@@ -51,6 +51,7 @@ struct BwdArgs {
   int B, Hq, Hkv, T, Lk, G, nq;
   int kind, window, block_size;
   int n_ktiles, n_slots;
+  int merged;                  // selection: one TMA box per (query, tensor) brings both 64-column slabs
   int dq_acc_mode;             // 1: dQ tiles are added to the fp32 accumulator (window / compression)
   float scale, scale_log2;
 };
@@ -216,6 +217,9 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const uint32_t tmem = *s_tmem;
   const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
   const uint32_t colS = grp * 128, colDP = grp * 128 + 64, colDQ = grp * 128;
+  // Q / dO tiles: slab-major (8-row groups 1024 bytes apart, slabs kRows * 128 apart) or, with merged
+  // boxes, the two slabs of an 8-row group side by side (groups 2048 bytes apart)
+  const uint32_t q_slab = p.merged ? 1024u : (uint32_t)(kRows * 128), q_sbo = p.merged ? 2048u : 1024u;
 
   if (tid == 0) {
     mbar_expect_tx(bar_kv, 2 * kKVBytes);
@@ -268,7 +272,17 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       // warps of the group (a few lanes each) because one warp issues them one after another
       if (lt == 0) mbar_expect_tx(bar_g, gather_bytes);
       const int op = lane * 8 + wg;                       // op id -> (query, slab, Q or dO)
-      const int n_ops = p.nq * kSlabs * 2;
+      if (p.merged) {
+        // a box costs the TMA unit a fixed time whatever its size, and the boxes of a tile are what
+        // bounds the kernel: one box per (query, tensor) brings both slabs, laid out side by side
+        for (int o = op; o < p.nq * 2; o += kGroupThreads) {
+          const int qq = o >> 1;
+          const int tq = rowt[qq] >= 0 ? rowt[qq] : p.T;
+          tma_load_5d(((o & 1) ? sDO : sQ) + qq * (p.G / 8) * 2048, (o & 1) ? &tm_do : &tm_q, bar_g, 0, 0, 0, tq,
+                      (b * p.Hq + hkv * p.G) >> 3);
+        }
+      }
+      const int n_ops = p.merged ? 0 : p.nq * kSlabs * 2;
       for (int o = op; o < n_ops; o += kGroupThreads) {
         const int qq = o / (kSlabs * 2), k = o % (kSlabs * 2);
         const int s = k >> 1;
@@ -320,13 +334,13 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + colS, desc_at(qa, slab * (kRows * 128) + in),
+        mma_ss(tmem + colS, desc_at_sbo(qa, slab * q_slab + in, q_sbo),
                desc_at(ka, slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + colDP, desc_at(da, slab * (kRows * 128) + in),
+        mma_ss(tmem + colDP, desc_at_sbo(da, slab * q_slab + in, q_sbo),
                desc_at(va, slab * (kKeys * 128) + in), kIdescS, kk > 0);
       }
       tc_commit(bar_sp);
@@ -384,16 +398,16 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     group_sync(grp);
     if (lt == 0) {
       tc_fence_after();
-      const uint32_t qa = desc_lo_mnmajor(smem_u32(sQ), kRows * 128);
-      const uint32_t da = desc_lo_mnmajor(smem_u32(sDO), kRows * 128);
+      const uint32_t qa = desc_lo_mnmajor(smem_u32(sQ), q_slab);
+      const uint32_t da = desc_lo_mnmajor(smem_u32(sDO), q_slab);
       const uint32_t pa = desc_lo_mnmajor(smem_u32(sP), 0), dsa = desc_lo_mnmajor(smem_u32(sDS), 0);
       const uint32_t dsk = desc_lo_kmajor(smem_u32(sDS)), ka = desc_lo_mnmajor(smem_u32(sK), kKeys * 128);
 #pragma unroll
-      for (int kk = 0; kk < kRows / 16; ++kk)        // contraction over the 128 rows
-        mma_ss(tmem + kColDV, desc_at(da, kk * 2048), desc_at(pa, kk * 2048), kIdescT, 1);
+      for (int kk = 0; kk < kRows / 16; ++kk)        // contraction over the 128 rows, 16 (two 8-row groups) a step
+        mma_ss(tmem + kColDV, desc_at_sbo(da, kk * 2 * q_sbo, q_sbo), desc_at(pa, kk * 2048), kIdescT, 1);
 #pragma unroll
       for (int kk = 0; kk < kRows / 16; ++kk)
-        mma_ss(tmem + kColDK, desc_at(qa, kk * 2048), desc_at(dsa, kk * 2048), kIdescT, 1);
+        mma_ss(tmem + kColDK, desc_at_sbo(qa, kk * 2 * q_sbo, q_sbo), desc_at(dsa, kk * 2048), kIdescT, 1);
 #pragma unroll
       for (int kk = 0; kk < kKeys / 16; ++kk)        // contraction over the 64 keys
         mma_ss(tmem + colDQ, desc_at(dsk, kk * 32), desc_at(ka, kk * 2048), kIdescDQ, kk > 0);
@@ -697,10 +711,11 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
       }
     }
     const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs * 2);
-    const int n_ops = p.nq * kSlabs * 2;             // selection: (query, slab, Q or dO) boxes of a tile
+    const int per_q = p.merged ? 2 : kSlabs * 2;     // boxes per query: Q and dO, per slab unless merged
+    const int n_ops = p.nq * per_q;                  // selection: the boxes of a tile
     constexpr int kRounds = kMaxNq * kSlabs * 2 / 32;
     auto tq_of = [&](int k, int o) -> int {          // query position of box o of tile k (none: past T, zeros)
-      const int qi = (rt_begin + k) * p.nq + o / (kSlabs * 2);
+      const int qi = (rt_begin + k) * p.nq + o / per_q;
       return (o < n_ops && qi < n_q) ? ldg_s32_now(p.q_of_block + pair_base + qi) : p.T;
     };
     int tq[kRounds];
@@ -732,7 +747,10 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
           const int o = lane + 32 * r;
-          if (o < n_ops) {
+          if (o < n_ops && p.merged) {
+            tma_load_5d(((o & 1) ? sDO : sQ) + (o >> 1) * (p.G / 8) * 2048, (o & 1) ? &tm_do : &tm_q, g_full + sb,
+                        0, 0, 0, tq[r], (b * p.Hq + hkv * p.G) >> 3);
+          } else if (o < n_ops) {
             const int qq = o / (kSlabs * 2), kx = o % (kSlabs * 2);
             const int s = kx >> 1;
             if (kx & 1)
@@ -755,6 +773,7 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
       mbar_wait(bar_kv, 0, p.status, s_abort, 32);
       const uint32_t ka = desc_lo_kmajor(smem_u32(sK)), va = desc_lo_kmajor(smem_u32(sV));
       const uint32_t kb = desc_lo_mnmajor(smem_u32(sK), kKeys * 128);
+      const uint32_t q_slab = p.merged ? 1024u : (uint32_t)(kRows * 128), q_sbo = p.merged ? 2048u : 1024u;
       int next_a = 0, next_b = 0;                    // next tile for S / dP, next tile for dV / dK / dQ
       long long idle_since = clock64();
       uint32_t polls = 0;
@@ -771,13 +790,13 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
               const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-              mma_ss(colS, desc_at(qa, slab * (kRows * 128) + in), desc_at(ka, slab * (kKeys * 128) + in),
+              mma_ss(colS, desc_at_sbo(qa, slab * q_slab + in, q_sbo), desc_at(ka, slab * (kKeys * 128) + in),
                      kIdescS, kk > 0);
             }
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
               const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-              mma_ss(colDP, desc_at(da, slab * (kRows * 128) + in), desc_at(va, slab * (kKeys * 128) + in),
+              mma_ss(colDP, desc_at_sbo(da, slab * q_slab + in, q_sbo), desc_at(va, slab * (kKeys * 128) + in),
                      kIdescS, kk > 0);
             }
             tc_commit(sp_full + sb);
@@ -792,16 +811,16 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             const uint8_t* sQ = sGroup + sb * kGroupBytes;
             const uint8_t* sP = sQ + 2 * kRowTileBytes;
             const uint8_t* sDS = sP + kPBytes;
-            const uint32_t qa = desc_lo_mnmajor(smem_u32(sQ), kRows * 128);
-            const uint32_t da = desc_lo_mnmajor(smem_u32(sQ + kRowTileBytes), kRows * 128);
+            const uint32_t qa = desc_lo_mnmajor(smem_u32(sQ), q_slab);
+            const uint32_t da = desc_lo_mnmajor(smem_u32(sQ + kRowTileBytes), q_slab);
             const uint32_t pa = desc_lo_mnmajor(smem_u32(sP), 0), dsa = desc_lo_mnmajor(smem_u32(sDS), 0);
             const uint32_t dsk = desc_lo_kmajor(smem_u32(sDS));
 #pragma unroll
-            for (int kk = 0; kk < kRows / 16; ++kk)        // contraction over the 128 rows
-              mma_ss(tmem + kColDV, desc_at(da, kk * 2048), desc_at(pa, kk * 2048), kIdescT, 1);
+            for (int kk = 0; kk < kRows / 16; ++kk)        // contraction over the 128 rows, 16 a step
+              mma_ss(tmem + kColDV, desc_at_sbo(da, kk * 2 * q_sbo, q_sbo), desc_at(pa, kk * 2048), kIdescT, 1);
 #pragma unroll
             for (int kk = 0; kk < kRows / 16; ++kk)
-              mma_ss(tmem + kColDK, desc_at(qa, kk * 2048), desc_at(dsa, kk * 2048), kIdescT, 1);
+              mma_ss(tmem + kColDK, desc_at_sbo(qa, kk * 2 * q_sbo, q_sbo), desc_at(dsa, kk * 2048), kIdescT, 1);
 #pragma unroll
             for (int kk = 0; kk < kKeys / 16; ++kk)        // contraction over the 64 keys
               mma_ss(tmem + sb * 128, desc_at(dsk, kk * 32), desc_at(kb, kk * 2048), kIdescDQ, kk > 0);
@@ -1210,6 +1229,7 @@ int sel_build_worklist(const int32_t* offsets, int n_ktiles, size_t units, size_
 
 }  // namespace tc
 int get_option_bwd_kernel();   // api.cu
+int get_option_merged_boxes();
 namespace tc {
 
 static BwdPlan plan_bwd(const AttnArgs& a) {
@@ -1293,6 +1313,7 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   p.kind = a.kind; p.window = a.window; p.block_size = a.block_size;
   p.n_ktiles = pl.n_ktiles; p.n_slots = pl.n_slots;
   p.dq_acc_mode = (a.dq_acc && a.kind != 2) ? 1 : 0;
+  p.merged = (a.kind == 2 && a.D == 128 && G % 8 == 0 && get_option_merged_boxes()) ? 1 : 0;
   p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
   p.split_chunk = pl.split_chunk;
   const size_t n_kv = (size_t)a.B * a.Hkv * a.Lk * a.D;
@@ -1326,8 +1347,10 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   CUtensorMap tm_k, tm_v, tm_q, tm_do;
   int rc = make_map(&tm_k, a.k, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
   if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.Lk, a.B * a.Hkv, kKeys, 1);
-  if (rc == NSA_OK) rc = make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
-  if (rc == NSA_OK) rc = make_map_query_rows(&tm_do, a.d_o, a.D, a.T, a.B * a.Hq, G);
+  if (rc == NSA_OK) rc = p.merged ? make_map_query_both_slabs(&tm_q, a.q, a.T, a.B * a.Hq, G)
+                                  : make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
+  if (rc == NSA_OK) rc = p.merged ? make_map_query_both_slabs(&tm_do, a.d_o, a.T, a.B * a.Hq, G)
+                                  : make_map_query_rows(&tm_do, a.d_o, a.D, a.T, a.B * a.Hq, G);
   CUtensorMap tm_q_run, tm_do_run;
   if (rc == NSA_OK) rc = make_map_query_rows(&tm_q_run, a.q, a.D, a.T, a.B * a.Hq, G, pl.nq);
   if (rc == NSA_OK) rc = make_map_query_rows(&tm_do_run, a.d_o, a.D, a.T, a.B * a.Hq, G, pl.nq);

@@ -206,6 +206,22 @@ __device__ __forceinline__ uint64_t desc_at(uint32_t lo, uint32_t byte_offset) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo + (byte_offset >> 4)), "r"(kDescHi));
   return d;
 }
+// the same with another distance between 8-row groups (tiles whose 64-column slabs interleave)
+__device__ __forceinline__ uint64_t desc_at_sbo(uint32_t lo, uint32_t byte_offset, uint32_t sbo_bytes) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo + (byte_offset >> 4)),
+      "r"((sbo_bytes >> 4) | (1u << 14) | (2u << 29)));
+  return d;
+}
+// 5-D tiled load: coordinates innermost first
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) { return desc_sw128(saddr, 16, 1024); }
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t slab_bytes) {
   return desc_sw128(saddr, slab_bytes, 1024);

@@ -28,6 +28,7 @@ struct PairArgs2 {
   int* status;
   int force;                     // 0: device-side choice, 1: query-outer kernel, 2: this kernel
   int B, Hq, Hkv, T, G, nq, n_ktiles, nq_union;
+  int merged;                    // 1: one TMA box per query brings both 64-column slabs (D = 128, G % 8 == 0)
   float scale_log2;
 };
 
@@ -148,10 +149,14 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
     }
     const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs);
-    const int n_ops = p.nq * kSlabs;
+    // A TMA box costs the TMA unit a fixed time of the order of a hundred cycles whatever its size, and
+    // the boxes of a tile are what bounds this kernel: where the shape allows (`merged`), one box per
+    // query brings both column slabs, else one box per query and slab.
+    const int per_q = p.merged ? 1 : kSlabs;
+    const int n_ops = p.nq * per_q;
     // query position of this lane's boxes in tile k (a missing query reads past T: zeros)
     auto tq_of = [&](int k, int o) -> int {
-      const int qi = (item.z + k) * p.nq + o / kSlabs;
+      const int qi = (item.z + k) * p.nq + o / per_q;
       return (o < n_ops && qi < n_q) ? ldg_s32_now(p.q_of_block + pair_base + qi) : p.T;
     };
     int tq0 = tq_of(0, lane), tq1 = tq_of(0, lane + 32), tq2 = tq_of(0, lane + 64), tq3 = tq_of(0, lane + 96);
@@ -171,9 +176,14 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       for (int r = 0; r < 4; ++r) {
         const int o = lane + 32 * r;
         if (o < n_ops) {
-          const int qq = o / kSlabs, sl = o % kSlabs;
-          tma_load_3d(dst + sl * (kRows * 128) + qq * p.G * 128, &tm_q, q_full + st, sl * 64,
-                      b * p.Hq + hkv * p.G, tqs[r]);
+          if (p.merged) {
+            tma_load_5d(dst + o * (p.G / 8) * 2048, &tm_q, q_full + st, 0, 0, 0, tqs[r],
+                        (b * p.Hq + hkv * p.G) >> 3);
+          } else {
+            const int qq = o / kSlabs, sl = o % kSlabs;
+            tma_load_3d(dst + sl * (kRows * 128) + qq * p.G * 128, &tm_q, q_full + st, sl * 64,
+                        b * p.Hq + hkv * p.G, tqs[r]);
+          }
         }
       }
       tq0 = nq0; tq1 = nq1; tq2 = nq2; tq3 = nq3;
@@ -195,10 +205,13 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           tc_fence_after();
           const uint32_t qa = desc_lo_kmajor(smem_u32(sQ + st * kQBytes));
           const uint32_t colS = tmem + sb * kSlotCols;
+          // Q tile: slab-major (8-row groups 1024 bytes apart, slabs kRows * 128 apart) or, with merged
+          // boxes, the two slabs of an 8-row group side by side (groups 2048 bytes apart)
+          const uint32_t q_slab = p.merged ? 1024u : (uint32_t)(kRows * 128), q_sbo = p.merged ? 2048u : 1024u;
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-            mma_ss(colS, desc_at(qa, slab * (kRows * 128) + in), desc_at(ka, slab * (kKeys * 128) + in),
+            mma_ss(colS, desc_at_sbo(qa, slab * q_slab + in, q_sbo), desc_at(ka, slab * (kKeys * 128) + in),
                    kIdescS, kk > 0);
           }
           tc_commit(q_empty + st);     // the stage may be refilled once S has read it
@@ -370,6 +383,8 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
 }  // namespace tc
 
+int get_option_merged_boxes();   // api.cu
+
 // launched by tc_sel_fwd (tc_fwdpair.cu) in place of the lock-stepped kernel
 int tc_fwdpair2_launch(const AttnArgs& a, const int32_t* q_of_block, const int32_t* offsets, void* o_part,
                        float* ml, const unsigned long long* stats, const void* work, int force, int nq,
@@ -386,10 +401,12 @@ int tc_fwdpair2_launch(const AttnArgs& a, const int32_t* q_of_block, const int32
   p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.T = a.T; p.G = G; p.nq = nq;
   p.n_ktiles = n_ktiles; p.nq_union = nq_union;
   p.scale_log2 = a.scale * kLog2e;
+  p.merged = (a.D == 128 && G % 8 == 0 && get_option_merged_boxes()) ? 1 : 0;
   CUtensorMap tm_k, tm_v, tm_q, tm_o;
   int rc = make_map(&tm_k, a.k, a.D, a.T, a.B * a.Hkv, kKeys, 1);
   if (rc == NSA_OK) rc = make_map(&tm_v, a.v, a.D, a.T, a.B * a.Hkv, kKeys, 1);
-  if (rc == NSA_OK) rc = make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
+  if (rc == NSA_OK) rc = p.merged ? make_map_query_both_slabs(&tm_q, a.q, a.T, a.B * a.Hq, G)
+                                  : make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
   if (rc == NSA_OK) rc = make_map_partial(&tm_o, o_part, a.D, G, 1, cap_pairs ? cap_pairs : 1, 1, nq);
   if (rc != NSA_OK) return rc;
   const size_t smem = pair2_smem_bytes(a.D);

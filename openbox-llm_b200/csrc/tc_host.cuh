@@ -59,6 +59,26 @@ static inline int make_map_query_rows(CUtensorMap* m, const void* base, int D, i
   return NSA_OK;
 }
 
+// 5-D map over a [heads, T, D] bf16 tensor (D = 128, heads a multiple of 8) whose box brings ALL of one
+// query's rows in one go: 64 elements x 8 heads x 2 column slabs x 1 token x G/8 head groups.  In
+// shared memory the box is laid out [head group][slab][8 heads][128 bytes]: every (head group, slab)
+// is one 1024-byte swizzle atom, the two slabs of an 8-row group are neighbours and consecutive
+// 8-row groups are 2048 bytes apart.
+static inline int make_map_query_both_slabs(CUtensorMap* m, const void* base, int T, int heads, int G) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available"); return NSA_ERR_CUDA; }
+  const cuuint64_t row = 128 * 2;
+  cuuint64_t dims[5] = {64u, 8u, 2u, (cuuint64_t)T, (cuuint64_t)(heads / 8)};
+  cuuint64_t strides[4] = {(cuuint64_t)T * row, 128u, row, (cuuint64_t)8 * T * row};
+  cuuint32_t box[5] = {64u, 8u, 2u, 1u, (cuuint32_t)(G / 8)};
+  cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (query, both slabs) failed with %d", (int)r); return NSA_ERR_CUDA; }
+  return NSA_OK;
+}
+
 // 5-D map over a bf16 partial buffer [outer][mid][slots][G][D] for stores of boxes
 // 64 elements x G x 1 x box_mid x 1: the G rows of box_mid consecutive `mid` entries of one slot.
 static inline int make_map_partial(CUtensorMap* m, void* base, int D, int G, size_t slots, size_t mid,
