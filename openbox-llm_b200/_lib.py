@@ -85,10 +85,6 @@ def lib():
             fn = getattr(handle, name)
             fn.restype, fn.argtypes = res, args
         _lib = handle
-        if os.environ.get("NSA_B200_PAIR_KERNEL"):      # development switch between the two pair kernels
-            handle.nsa_set_option(b"sel_pair_kernel", int(os.environ["NSA_B200_PAIR_KERNEL"]))
-        if os.environ.get("NSA_B200_BWD_KERNEL"):
-            handle.nsa_set_option(b"bwd_kernel", int(os.environ["NSA_B200_BWD_KERNEL"]))
     return _lib
 
 

@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libnsa_b200.so")
-SOURCES = ["api.cu", "simt.cu", "aux.cu", "tc.cu", "tc_bwd.cu", "tc_score.cu", "tc_fwdpair.cu", "tc_fwdpair2.cu", "optim.cu"]
+SOURCES = ["api.cu", "simt.cu", "aux.cu", "tc.cu", "tc_bwd.cu", "tc_score.cu", "tc_fwdpair.cu", "tc_fwdpair_kernel.cu", "optim.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-DNSA_B200",
               "-Xptxas", "-v"]

@@ -58,12 +58,8 @@ void kernel_end(cudaStream_t st) {
 
 static std::atomic<int> g_opt_sel_fwd{0};
 int get_option_sel_fwd() { return g_opt_sel_fwd.load(); }
-static std::atomic<int> g_opt_pair_kernel{1};
-int get_option_pair_kernel() { return g_opt_pair_kernel.load(); }
 static std::atomic<int> g_opt_merged{1};
 int get_option_merged_boxes() { return g_opt_merged.load(); }
-static std::atomic<int> g_opt_bwd_kernel{0};
-int get_option_bwd_kernel() { return g_opt_bwd_kernel.load(); }
 
 static int check_dims(const NsaDims* d) {
   NSA_CHECK_ARG(d != nullptr, "dims is null");
@@ -149,16 +145,8 @@ extern "C" int nsa_set_option(const char* name, int value) {
     g_opt_sel_fwd.store(value);
     return NSA_OK;
   }
-  if (name && strcmp(name, "sel_pair_kernel") == 0 && value >= 0 && value <= 1) {
-    g_opt_pair_kernel.store(value);
-    return NSA_OK;
-  }
   if (name && strcmp(name, "merged_boxes") == 0 && value >= 0 && value <= 1) {
     g_opt_merged.store(value);
-    return NSA_OK;
-  }
-  if (name && strcmp(name, "bwd_kernel") == 0 && value >= 0 && value <= 1) {
-    g_opt_bwd_kernel.store(value);
     return NSA_OK;
   }
   set_error("unknown option or value");

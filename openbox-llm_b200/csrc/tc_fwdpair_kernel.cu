@@ -1,11 +1,14 @@
 // Selected-block attention forward, key-block outer, warp-specialised.
 //
-// Same work split as tc_fwdpair.cu (one CTA per (64-token block, chunk of its row tiles); per row
+// One CTA per (64-token block, chunk of its row tiles), launched by tc_sel_fwd (tc_fwdpair.cu); per row
 // tile S = Q K^T, p = exp2(s - m_block), O_part = P V; O_part, m and the sum of p leave per
-// (pair, head) and sel_combine_kernel merges them), but the row tiles of a CTA flow through a
-// pipeline of roles instead of two lock-stepped groups:
-//   producer warp     gathers the Q rows of tile k into a 3-stage ring (one TMA box per query and
-//                     64-column slab), three tiles ahead of the arithmetic
+// (pair, head) and sel_combine_kernel merges them.  The row tiles of a CTA flow through a
+// pipeline of roles:
+//   3 producer warps  gather the Q rows of tile k into a 3-stage ring, three tiles ahead of the
+//                     arithmetic: one TMA box per query (both 64-column slabs, where the shape
+//                     allows) or per query and slab.  A warp gets a box out every 60-100 cycles,
+//                     whatever its size, and at 32 boxes a tile that bounded the kernel; several
+//                     warps issue side by side
 //   MMA warp          one thread issues S(k) as soon as stage k has landed, then P V of tile k-1
 //   2 softmax groups  128 threads each (thread = row = TMEM lane), tiles alternate between them:
 //                     S from TMEM, row maximum, exponentials, P back to TMEM as packed bf16 (it is
@@ -18,7 +21,7 @@
 namespace nsa {
 namespace tc {
 
-struct PairArgs2 {
+struct PairArgs {
   const int32_t* q_of_block;
   const int32_t* offsets;        // [B*Hkv, n_ktiles + 1]
   __nv_bfloat16* o_part;         // [pairs, G, D]
@@ -32,12 +35,13 @@ struct PairArgs2 {
   float scale_log2;
 };
 
-constexpr int kP2Threads = 448;            // 2 x 4 softmax warps, 4 epilogue warps, producer, MMA
-constexpr int kP2QStages = 3;
+constexpr int kPairThreads = 512;            // 2 x 4 softmax warps, 4 epilogue warps, 3 producer warps, MMA warp
+constexpr int kPairProducers = 3;
+constexpr int kPairQStages = 3;
 
-__host__ __device__ inline size_t pair2_smem_bytes(int D) {
+__host__ __device__ inline size_t pair_smem_bytes(int D) {
   const size_t q = (size_t)kRows * 128 * (D / 64);
-  return (size_t)2 * kKeys * 128 * (D / 64) + kP2QStages * q + 2 * q /*staging*/ + 512 /*barriers*/ +
+  return (size_t)2 * kKeys * 128 * (D / 64) + kPairQStages * q + 2 * q /*staging*/ + 512 /*barriers*/ +
          128 * 4 /*partial-row index*/ + 1024 /*alignment slack*/;
 }
 
@@ -59,10 +63,10 @@ __device__ __forceinline__ bool named_or(int id, int threads, int pred) {
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
 template <int D>
-__global__ void __launch_bounds__(kP2Threads, 1)
-tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+__global__ void __launch_bounds__(kPairThreads, 1)
+tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_o,
-                   const PairArgs2 p) {
+                   const PairArgs p) {
   constexpr int kSlabs = D / 64;
   constexpr int kKVBytes = kKeys * 128 * kSlabs;
   constexpr int kQBytes = kRows * 128 * kSlabs;
@@ -75,8 +79,8 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sK = smem;
   uint8_t* sV = sK + kKVBytes;
-  uint8_t* sQ = sV + kKVBytes;                      // [kP2QStages][kQBytes]
-  uint8_t* sStage = sQ + kP2QStages * kQBytes;      // [2][kQBytes]
+  uint8_t* sQ = sV + kKVBytes;                      // [kPairQStages][kQBytes]
+  uint8_t* sStage = sQ + kPairQStages * kQBytes;      // [2][kQBytes]
   uint64_t* bars = (uint64_t*)(sStage + 2 * kQBytes);
   uint64_t* bar_kv = bars + 0;
   uint64_t* q_full = bars + 1;      // [3]
@@ -106,14 +110,14 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     int bad = (*(volatile int*)p.status != 0) ? 1 : 0;
-    if ((size_t)((uint8_t*)(s_prow + 128) - smem_raw) > pair2_smem_bytes(D)) {
+    if ((size_t)((uint8_t*)(s_prow + 128) - smem_raw) > pair_smem_bytes(D)) {
       atomicOr(p.status, 256);   // the shared-memory window is less aligned than assumed
       bad = 1;
     }
     *s_abort = bad;
     *s_issued = 0;
     mbar_init(bar_kv, 1);
-    for (int s = 0; s < kP2QStages; ++s) { mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); }
+    for (int s = 0; s < kPairQStages; ++s) { mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); }
     for (int s = 0; s < 2; ++s) {
       mbar_init(s_full + s, 1); mbar_init(p_full + s, 128);
       mbar_init(o_full + s, 1); mbar_init(o_empty + s, 128);
@@ -126,7 +130,7 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   __syncthreads();
   if (*s_abort) return;
   // rows past nq * G of a tile are never loaded: keep them zero in every stage
-  for (int i = tid; i < kP2QStages * kQBytes / 16; i += kP2Threads)
+  for (int i = tid; i < kPairQStages * kQBytes / 16; i += kPairThreads)
     *reinterpret_cast<uint4*>(sQ + (size_t)i * 16) = make_uint4(0, 0, 0, 0);
   fence_proxy_async();
   if (warp == 0) {
@@ -138,9 +142,10 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
 
-  if (warp == 12) {
-    // ---- producer: K / V once, then the Q rows of every tile -------------------------------
-    if (lane == 0) {
+  if (warp >= 12 && warp < 12 + kPairProducers) {
+    // ---- producers: K / V once, then the Q rows of every tile; box o of a tile goes to warp o % 3 ----
+    const int pw = warp - 12;
+    if (pw == 0 && lane == 0) {
       mbar_expect_tx(bar_kv, 2 * kKVBytes);
 #pragma unroll
       for (int s = 0; s < kSlabs; ++s) {
@@ -149,46 +154,43 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
     }
     const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs);
-    // A TMA box costs the TMA unit a fixed time of the order of a hundred cycles whatever its size, and
-    // the boxes of a tile are what bounds this kernel: where the shape allows (`merged`), one box per
-    // query brings both column slabs, else one box per query and slab.
+    // A TMA box costs its issuing warp a fixed time of the order of a hundred cycles whatever its size:
+    // where the shape allows (`merged`), one box per query brings both column slabs, else one box per
+    // query and slab.
     const int per_q = p.merged ? 1 : kSlabs;
-    const int n_ops = p.nq * per_q;
-    // query position of this lane's boxes in tile k (a missing query reads past T: zeros)
+    const int n_ops = p.nq * per_q;                  // at most 128: up to two per lane of the three warps
+    const int o0 = lane * kPairProducers + pw, o1 = o0 + 32 * kPairProducers;   // this lane's boxes
+    // query position of one of this lane's boxes in tile k (a missing query reads past T: zeros)
     auto tq_of = [&](int k, int o) -> int {
       const int qi = (item.z + k) * p.nq + o / per_q;
       return (o < n_ops && qi < n_q) ? ldg_s32_now(p.q_of_block + pair_base + qi) : p.T;
     };
-    int tq0 = tq_of(0, lane), tq1 = tq_of(0, lane + 32), tq2 = tq_of(0, lane + 64), tq3 = tq_of(0, lane + 96);
+    int tq0 = tq_of(0, o0), tq1 = tq_of(0, o1);
     for (int k = 0; k < n_tiles; ++k) {
-      const int st = k % kP2QStages;
-      mbar_wait(q_empty + st, ((k / kP2QStages) + 1) & 1, p.status, s_abort, 512);
-      const int nq0 = k + 1 < n_tiles ? tq_of(k + 1, lane) : p.T;        // next tile's positions, ahead
-      const int nq1 = k + 1 < n_tiles ? tq_of(k + 1, lane + 32) : p.T;
-      const int nq2 = k + 1 < n_tiles ? tq_of(k + 1, lane + 64) : p.T;
-      const int nq3 = k + 1 < n_tiles ? tq_of(k + 1, lane + 96) : p.T;
+      const int st = k % kPairQStages;
+      mbar_wait(q_empty + st, ((k / kPairQStages) + 1) & 1, p.status, s_abort, 512);
+      const int tn0 = k + 1 < n_tiles ? tq_of(k + 1, o0) : p.T;          // next tile's positions, ahead
+      const int tn1 = k + 1 < n_tiles ? tq_of(k + 1, o1) : p.T;
       if (__any_sync(0xffffffffu, *s_abort)) break;          // the whole warp leaves together
-      if (lane == 0) { mbar_expect_tx(q_full + st, gather_bytes); *s_issued = k + 1; }
+      if (pw == 0 && lane == 0) { mbar_expect_tx(q_full + st, gather_bytes); *s_issued = k + 1; }
       __syncwarp();
       uint8_t* dst = sQ + st * kQBytes;
-      const int tqs[4] = {tq0, tq1, tq2, tq3};
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int o = lane + 32 * r;
+      for (int r = 0; r < 2; ++r) {
+        const int o = r ? o1 : o0, tq = r ? tq1 : tq0;
         if (o < n_ops) {
           if (p.merged) {
-            tma_load_5d(dst + o * (p.G / 8) * 2048, &tm_q, q_full + st, 0, 0, 0, tqs[r],
-                        (b * p.Hq + hkv * p.G) >> 3);
+            tma_load_5d(dst + o * (p.G / 8) * 2048, &tm_q, q_full + st, 0, 0, 0, tq, (b * p.Hq + hkv * p.G) >> 3);
           } else {
             const int qq = o / kSlabs, sl = o % kSlabs;
             tma_load_3d(dst + sl * (kRows * 128) + qq * p.G * 128, &tm_q, q_full + st, sl * 64,
-                        b * p.Hq + hkv * p.G, tqs[r]);
+                        b * p.Hq + hkv * p.G, tq);
           }
         }
       }
-      tq0 = nq0; tq1 = nq1; tq2 = nq2; tq3 = nq3;
+      tq0 = tn0; tq1 = tn1;
     }
-  } else if (warp == 13) {
+  } else if (warp == 12 + kPairProducers) {
     // ---- MMA issuer ------------------------------------------------------------------------
     if (lane == 0) {
       mbar_wait(bar_kv, 0, p.status, s_abort, 32);
@@ -197,8 +199,8 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       for (int k = 0; k <= n_tiles; ++k) {
         if (*s_abort) break;
         if (k < n_tiles) {
-          const int st = k % kP2QStages, sb = k & 1;
-          mbar_wait(q_full + st, (k / kP2QStages) & 1, p.status, s_abort, 512);
+          const int st = k % kPairQStages, sb = k & 1;
+          mbar_wait(q_full + st, (k / kPairQStages) & 1, p.status, s_abort, 512);
           // the S / P columns of the slot are free once P V of tile k-2 has completed
           if (k >= 2) mbar_wait(o_full + sb, ((k >> 1) - 1) & 1, p.status, s_abort, 128);
           if (*s_abort) break;
@@ -369,10 +371,10 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   __syncthreads();
   if (*s_abort && tid == 0) {
     const int issued = *s_issued;
-    for (int k = max(0, issued - kP2QStages); k < issued; ++k) {
+    for (int k = max(0, issued - kPairQStages); k < issued; ++k) {
       // bounded: a gather that never lands was what made the CTA give up in the first place
       const long long t0 = clock64();
-      while (!mbar_try_wait(q_full + k % kP2QStages, (k / kP2QStages) & 1) &&
+      while (!mbar_try_wait(q_full + k % kPairQStages, (k / kPairQStages) & 1) &&
              clock64() - t0 < kWaitLimitCycles) {}
     }
   }
@@ -385,13 +387,13 @@ tc_fwdpair2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
 int get_option_merged_boxes();   // api.cu
 
-// launched by tc_sel_fwd (tc_fwdpair.cu) in place of the lock-stepped kernel
-int tc_fwdpair2_launch(const AttnArgs& a, const int32_t* q_of_block, const int32_t* offsets, void* o_part,
+// launched by tc_sel_fwd (tc_fwdpair.cu)
+int tc_fwdpair_launch(const AttnArgs& a, const int32_t* q_of_block, const int32_t* offsets, void* o_part,
                        float* ml, const unsigned long long* stats, const void* work, int force, int nq,
                        int n_ktiles, int nq_union, size_t cap_pairs, unsigned grid, cudaStream_t st) {
   using namespace tc;
   const int G = a.Hq / a.Hkv;
-  PairArgs2 p;
+  PairArgs p;
   p.q_of_block = q_of_block; p.offsets = offsets;
   p.o_part = (__nv_bfloat16*)o_part; p.ml = ml; p.stats = stats;
   p.work = (const SelWorkHeader*)work;
@@ -409,16 +411,16 @@ int tc_fwdpair2_launch(const AttnArgs& a, const int32_t* q_of_block, const int32
                                   : make_map_query_rows(&tm_q, a.q, a.D, a.T, a.B * a.Hq, G);
   if (rc == NSA_OK) rc = make_map_partial(&tm_o, o_part, a.D, G, 1, cap_pairs ? cap_pairs : 1, 1, nq);
   if (rc != NSA_OK) return rc;
-  const size_t smem = pair2_smem_bytes(a.D);
+  const size_t smem = pair_smem_bytes(a.D);
   KernelScope ks("tc_fwd_slc_pairs", st);
   if (a.D == 128) {
-    NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tc_fwdpair2_kernel<128><<<grid, kP2Threads, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p);
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tc_fwdpair_kernel<128><<<grid, kPairThreads, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p);
   } else {
-    NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tc_fwdpair2_kernel<64><<<grid, kP2Threads, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p);
+    NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwdpair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tc_fwdpair_kernel<64><<<grid, kPairThreads, smem, st>>>(tm_k, tm_v, tm_q, tm_o, p);
   }
-  NSA_LAUNCH_OK("tc_fwdpair2_kernel");
+  NSA_LAUNCH_OK("tc_fwdpair_kernel");
   return NSA_OK;
 }
 
