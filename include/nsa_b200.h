@@ -231,6 +231,24 @@ int nsa_topn_blocks_general(const void* q, const void* k_cmp, const float* lse_c
                             int cmp_stride, int sel_block, int n_sel, int n_init, int n_local, int impl,
                             void* stream);
 
+/* ---- projection glue ---------------------------------------------------------------------------
+ * The reference layer runs seven projections and a gate projection as eight GEMMs and brings each
+ * result to head-major layout by its own transpose + copy (nsa_model.py:192-194, 325-329, 358-359,
+ * 366-367), and the output back by another (:369).  Here the eight weights are applied as ONE GEMM
+ * whose rows [B,T,W] hold, per token, q (Hq*D), kc, vc, ks, vs, kw, vw (Hkv*D each) and the gate
+ * logits (3*Hq, padded to a multiple of 8 elements: W = nsa_fused_projection_width);
+ * nsa_split_heads turns those rows into q [B,Hq,T,D], kv [6,B,Hkv,T,D] and gate [B,Hq,T,3] in one
+ * pass, nsa_merge_heads assembles the gradient rows from dq, dkv, dgate in one pass, and
+ * nsa_swap_heads_tokens converts [B,H,T,D] <-> [B,T,H,D] (the op's output for out_proj, its upstream
+ * gradient back). */
+int nsa_fused_projection_width(int Hq, int Hkv, int D);
+int nsa_split_heads(const void* y, void* q, void* kv, void* gate, int B, int T, int Hq, int Hkv, int D,
+                    int dtype, void* stream);
+int nsa_merge_heads(const void* dq, const void* dkv, const void* dgate, void* dy, int B, int T, int Hq,
+                    int Hkv, int D, int dtype, void* stream);
+int nsa_swap_heads_tokens(const void* src, void* dst, int B, int H, int T, int D, int dtype, int to_tokens,
+                          void* stream);
+
 /* ---- gate combine ---------------------------------------------------------------------------
  * Replaces the sigmoid blend nsa_model.py:366-368 / nsa_fused_kernel.py:572-573 and its
  * autograd backward: out = sum_i sigmoid(gate[...,i]) * o_i; d_gate is float32-accumulated

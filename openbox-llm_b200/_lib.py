@@ -68,6 +68,10 @@ SIGNATURES = {
     "nsa_range_attn_bwd_acc_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
     "nsa_range_attn_bwd_acc": (_i, [_vp] * 9 + [_dp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "nsa_dq_finish": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp]),
+    "nsa_fused_projection_width": (_i, [_i, _i, _i]),
+    "nsa_split_heads": (_i, [_vp] * 4 + [_i] * 6 + [_vp]),
+    "nsa_merge_heads": (_i, [_vp] * 4 + [_i] * 6 + [_vp]),
+    "nsa_swap_heads_tokens": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
     "nsa_gate_combine_fwd": (_i, [_vp] * 5 + [_dp, _vp]),
     "nsa_gate_combine_bwd": (_i, [_vp] * 9 + [_dp, _vp]),
 }

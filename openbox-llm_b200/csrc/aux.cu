@@ -1214,6 +1214,136 @@ extern "C" int nsa_sum3(const void* a, const void* b, const void* c, void* out, 
   return NSA_OK;
 }
 
+// ---- projection glue: one pass between the fused projection's [B,T,W] rows and the head-major
+// tensors the attention kernels take ------------------------------------------------------------
+namespace nsa {
+namespace {
+// A row of the fused projection holds, for one token: q (Hq*D), then kc, vc, ks, vs, kw, vw (Hkv*D
+// each), then the gate logits (3*Hq, padded to a multiple of 8 elements).  `to_heads`: rows -> q
+// [B,Hq,T,D], kv [6][B,Hkv,T,D], gate [B,Hq,T,3]; else the other way (gradients), the padding zeroed.
+template <typename T, typename V>   // V: the 16-byte vector of T
+__global__ void split_heads_kernel(T* __restrict__ y, T* __restrict__ q, T* __restrict__ kv, T* __restrict__ gate,
+                                   int B, int Tn, int Hq, int Hkv, int D, int W, int to_heads, size_t n_vec) {
+  constexpr int kPer = 16 / (int)sizeof(T);                 // elements per vector
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const int wv = W / kPer;
+  const int col = (int)(i % wv) * kPer;
+  const size_t bt = i / wv;
+  const int t = (int)(bt % Tn), b = (int)(bt / Tn);
+  V* row = reinterpret_cast<V*>(y + bt * W + col);
+  const int n_attn = (Hq + 6 * Hkv) * D;
+  if (col < n_attn) {
+    T* dst;
+    if (col < Hq * D) {
+      const int h = col / D, d = col % D;
+      dst = q + (((size_t)b * Hq + h) * Tn + t) * D + d;
+    } else {
+      const int c2 = col - Hq * D;
+      const int which = c2 / (Hkv * D), c3 = c2 % (Hkv * D);
+      const int h = c3 / D, d = c3 % D;
+      dst = kv + ((((size_t)which * B + b) * Hkv + h) * Tn + t) * D + d;
+    }
+    if (to_heads) *reinterpret_cast<V*>(dst) = *row;
+    else *row = *reinterpret_cast<const V*>(dst);
+  } else {
+    T tmp[kPer];
+    if (to_heads) *reinterpret_cast<V*>(tmp) = *row;
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) {
+      const int c = col - n_attn + e;                       // h * 3 + branch
+      if (c < 3 * Hq) {
+        T* g = gate + ((((size_t)b * Hq + c / 3) * Tn + t) * 3 + c % 3);
+        if (to_heads) *g = tmp[e]; else tmp[e] = *g;
+      } else if (!to_heads) {
+        tmp[e] = T(0.f);
+      }
+    }
+    if (!to_heads) *row = *reinterpret_cast<const V*>(tmp);
+  }
+}
+
+// [B,H,T,D] <-> [B,T,H,D], 16 bytes per thread
+template <typename V>
+__global__ void swap_heads_tokens_kernel(const V* __restrict__ src, V* __restrict__ dst, int H, int Tn, int Dv,
+                                         int to_tokens, size_t n_vec) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;    // over dst vectors
+  if (i >= n_vec) return;
+  const int d = (int)(i % Dv);
+  const size_t r = i / Dv;
+  size_t s;
+  if (to_tokens) {                                          // dst [B,T,H,D]
+    const int h = (int)(r % H);
+    const size_t bt = r / H;
+    const int t = (int)(bt % Tn);
+    const size_t b = bt / Tn;
+    s = ((b * H + h) * Tn + t) * Dv + d;
+  } else {                                                  // dst [B,H,T,D]
+    const int t = (int)(r % Tn);
+    const size_t bh = r / Tn;
+    const int h = (int)(bh % H);
+    const size_t b = bh / H;
+    s = ((b * Tn + t) * H + h) * Dv + d;
+  }
+  dst[i] = __ldg(src + s);
+}
+}  // namespace
+}  // namespace nsa
+
+extern "C" int nsa_fused_projection_width(int Hq, int Hkv, int D) {
+  return (Hq + 6 * Hkv) * D + (3 * Hq + 7) / 8 * 8;
+}
+
+static int split_or_merge(void* y, void* q, void* kv, void* gate, int B, int T, int Hq, int Hkv, int D, int dtype,
+                          int to_heads, void* stream) {
+  NSA_CHECK_ARG(B >= 0 && T >= 0 && Hq > 0 && Hkv > 0 && D > 0 && D % 8 == 0, "bad sizes");
+  NSA_CHECK_ARG(dtype == NSA_DTYPE_BF16 || dtype == NSA_DTYPE_F32, "bad dtype %d", dtype);
+  const int W = nsa_fused_projection_width(Hq, Hkv, D);
+  const size_t rows = (size_t)B * T;
+  if (rows == 0) return NSA_OK;
+  NSA_CHECK_ARG(y && q && kv && gate, "null tensor");
+  cudaStream_t st = (cudaStream_t)stream;
+  KernelScope ks(to_heads ? "split_heads_kernel" : "merge_heads_kernel", st);
+  if (dtype == NSA_DTYPE_BF16) {
+    const size_t n = rows * (W / 8);
+    split_heads_kernel<__nv_bfloat16, uint4><<<blocks_for(n, 256), 256, 0, st>>>(
+        (__nv_bfloat16*)y, (__nv_bfloat16*)q, (__nv_bfloat16*)kv, (__nv_bfloat16*)gate, B, T, Hq, Hkv, D, W, to_heads, n);
+  } else {
+    const size_t n = rows * (W / 4);
+    split_heads_kernel<float, float4><<<blocks_for(n, 256), 256, 0, st>>>(
+        (float*)y, (float*)q, (float*)kv, (float*)gate, B, T, Hq, Hkv, D, W, to_heads, n);
+  }
+  NSA_LAUNCH_OK("split_heads_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_split_heads(const void* y, void* q, void* kv, void* gate, int B, int T, int Hq, int Hkv, int D,
+                               int dtype, void* stream) {
+  return split_or_merge(const_cast<void*>(y), q, kv, gate, B, T, Hq, Hkv, D, dtype, 1, stream);
+}
+
+extern "C" int nsa_merge_heads(const void* dq, const void* dkv, const void* dgate, void* dy, int B, int T, int Hq,
+                               int Hkv, int D, int dtype, void* stream) {
+  return split_or_merge(dy, const_cast<void*>(dq), const_cast<void*>(dkv), const_cast<void*>(dgate), B, T, Hq, Hkv,
+                        D, dtype, 0, stream);
+}
+
+extern "C" int nsa_swap_heads_tokens(const void* src, void* dst, int B, int H, int T, int D, int dtype,
+                                     int to_tokens, void* stream) {
+  NSA_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && D > 0 && D % 8 == 0, "bad sizes");
+  NSA_CHECK_ARG(dtype == NSA_DTYPE_BF16 || dtype == NSA_DTYPE_F32, "bad dtype %d", dtype);
+  const int Dv = dtype == NSA_DTYPE_BF16 ? D / 8 : D / 4;
+  const size_t n = (size_t)B * H * T * Dv;
+  if (n == 0) return NSA_OK;
+  NSA_CHECK_ARG(src && dst, "null tensor");
+  cudaStream_t st = (cudaStream_t)stream;
+  KernelScope ks("swap_heads_tokens_kernel", st);
+  swap_heads_tokens_kernel<uint4><<<blocks_for(n, 256), 256, 0, st>>>((const uint4*)src, (uint4*)dst, H, T, Dv,
+                                                                       to_tokens, n);
+  NSA_LAUNCH_OK("swap_heads_tokens_kernel");
+  return NSA_OK;
+}
+
 extern "C" int nsa_gate_combine_fwd(const void* o_cmp, const void* o_slc, const void* o_win,
                                     const void* gate_logits, void* out, const NsaDims* dims,
                                     void* stream) {

@@ -415,6 +415,86 @@ def gate_combine(o_cmp, o_slc, o_win, gate_logits):
     return _GateCombine.apply(o_cmp, o_slc, o_win, gate_logits)
 
 
+# ---------------------------------------------------------------------------------------
+# projection glue of the layer (nsa_model.py:192-194, 325-329, 358-359, 366-369)
+# ---------------------------------------------------------------------------------------
+def fused_projection_width(Hq, Hkv, D):
+    """Row width of the fused projection: q, six K/V projections, 3*Hq gate logits padded to 8."""
+    return int(L.lib().nsa_fused_projection_width(Hq, Hkv, D))
+
+
+@L.on_device
+def _split_heads_launch(y, q, kv, gate, Hq, Hkv, D, merge):
+    B, T = y.shape[0], y.shape[1]
+    fn = L.lib().nsa_merge_heads if merge else L.lib().nsa_split_heads
+    if merge:
+        L.check(fn(L.ptr(q), L.ptr(kv), L.ptr(gate), L.ptr(y), B, T, Hq, Hkv, D, L.dtype_code(y), L.stream()))
+    else:
+        L.check(fn(L.ptr(y), L.ptr(q), L.ptr(kv), L.ptr(gate), B, T, Hq, Hkv, D, L.dtype_code(y), L.stream()))
+
+
+class _SplitHeads(torch.autograd.Function):
+    """Rows [B,T,W] of the fused projection -> q [B,Hq,T,D], kv [6,B,Hkv,T,D] (kc, vc, ks, vs, kw,
+    vw), gate logits [B,Hq,T,3], in one pass; backward assembles the gradient rows in one pass."""
+
+    @staticmethod
+    def forward(ctx, y, Hq, Hkv, D):
+        B, T, W = y.shape
+        assert W == fused_projection_width(Hq, Hkv, D), "row width does not match the head counts"
+        y = y.contiguous()
+        q = torch.empty(B, Hq, T, D, device=y.device, dtype=y.dtype)
+        kv = torch.empty(6, B, Hkv, T, D, device=y.device, dtype=y.dtype)
+        gate = torch.empty(B, Hq, T, 3, device=y.device, dtype=y.dtype)
+        _split_heads_launch(y, q, kv, gate, Hq, Hkv, D, False)
+        ctx.cfg = (Hq, Hkv, D, W)
+        return q, kv, gate
+
+    @staticmethod
+    def backward(ctx, dq, dkv, dgate):
+        Hq, Hkv, D, W = ctx.cfg
+        B, _, T, _ = dq.shape
+        dq, dkv, dgate = dq.contiguous(), dkv.contiguous(), dgate.contiguous()
+        dy = torch.empty(B, T, W, device=dq.device, dtype=dq.dtype)
+        _split_heads_launch(dy, dq, dkv, dgate, Hq, Hkv, D, True)
+        return dy, None, None, None
+
+
+def split_heads(y, Hq, Hkv, D):
+    return _SplitHeads.apply(y, Hq, Hkv, D)
+
+
+@L.on_device
+def _swap_heads_tokens(x, to_tokens):
+    if to_tokens:
+        B, H, T, D = x.shape
+        out = torch.empty(B, T, H, D, device=x.device, dtype=x.dtype)
+    else:
+        B, T, H, D = x.shape
+        out = torch.empty(B, H, T, D, device=x.device, dtype=x.dtype)
+    L.check(L.lib().nsa_swap_heads_tokens(L.ptr(x), L.ptr(out), B, H, T, D, L.dtype_code(x), int(to_tokens),
+                                          L.stream()))
+    return out
+
+
+class _HeadsToTokens(torch.autograd.Function):
+    """[B,H,T,D] -> [B,T,H*D] (what out_proj reads, nsa_model.py:369); backward the other way."""
+
+    @staticmethod
+    def forward(ctx, x):
+        ctx.D = x.shape[3]
+        out = _swap_heads_tokens(x.contiguous(), True)
+        return out.view(out.shape[0], out.shape[1], -1)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        B, T, HD = d_out.shape
+        return _swap_heads_tokens(d_out.contiguous().view(B, T, HD // ctx.D, ctx.D), False)
+
+
+def heads_to_tokens(x):
+    return _HeadsToTokens.apply(x)
+
+
 def nsa_fused_forward(q, kc, vc, ks, vs, kw, vw, gate_logits, block_idx, block_size, window):
     """nsa_fused_kernel.py:560-573: the three branches with a given block_idx, mean pooling."""
     k_cmp = block_mean_pool(kc, block_size)

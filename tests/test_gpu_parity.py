@@ -729,3 +729,50 @@ def test_metric_shape_properties():
         assert grads[n].float().abs().max().item() > 0, n
     for k, v in comp_d.items():
         assert torch.isfinite(v.grad).all() and v.grad.abs().max().item() > 0, k
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_fused_projection_glue(dtype):
+    """The layer with one GEMM for the eight projections and one pass to / from head-major layout
+    (nsa_split_heads, nsa_merge_heads, nsa_swap_heads_tokens) against the same layer with the
+    reference's eight separate projections and transposes (nsa_model.py:325-329, 358-359, 366-369):
+    same state_dict, same output, same gradients."""
+    import importlib
+    M = importlib.import_module("openbox-llm_b200.module")
+    nsa = pkg()
+    torch.manual_seed(3)
+    kw = dict(d_model=192, n_q_heads=6, n_kv_heads=2, block_size=64, n_selected_blocks=3, window=100)
+    a = M.NSAAttentionB200(**kw, fused_projection=True).cuda()
+    b = M.NSAAttentionB200(**kw, fused_projection=False).cuda()
+    b.load_state_dict(a.state_dict())
+    assert set(a.state_dict()) == set(b.state_dict())
+    x = torch.randn(2, 320, 192, device="cuda")
+    dy = torch.randn(2, 320, 192, device="cuda")
+    xs = [x.clone().requires_grad_(True) for _ in range(2)]
+    outs = []
+    for m, xi in zip((a, b), xs):
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=dtype == torch.bfloat16):
+            y = m(xi)
+        y.float().backward(dy)
+        outs.append(y.float())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (outs[0] - outs[1]).abs().max().item() <= tol * max(1.0, outs[1].abs().max().item())
+    assert (xs[0].grad - xs[1].grad).abs().max().item() <= tol * max(1.0, xs[1].grad.abs().max().item())
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert p.grad is not None and q.grad is not None, n
+        d = (p.grad - q.grad).abs().max().item()
+        assert d <= tol * max(1.0, q.grad.abs().max().item()), (n, d)
+    # the raw passes: split is a permutation of the row, merge its inverse with the padding zeroed
+    Hq, Hkv, D = 6, 2, 32
+    W = nsa.ops.fused_projection_width(Hq, Hkv, D)
+    yrow = torch.randn(2, 50, W, device="cuda").to(dtype)
+    q, kv, gate = nsa.ops.split_heads(yrow, Hq, Hkv, D)
+    n_attn = (Hq + 6 * Hkv) * D
+    assert torch.equal(q, yrow[..., :Hq * D].view(2, 50, Hq, D).transpose(1, 2))
+    for i in range(6):
+        seg = yrow[..., Hq * D + i * Hkv * D: Hq * D + (i + 1) * Hkv * D]
+        assert torch.equal(kv[i], seg.view(2, 50, Hkv, D).transpose(1, 2)), i
+    assert torch.equal(gate, yrow[..., n_attn:n_attn + 3 * Hq].view(2, 50, Hq, 3).transpose(1, 2))
+    t = nsa.ops.heads_to_tokens(q)
+    assert torch.equal(t, q.transpose(1, 2).reshape(2, 50, Hq * D))
+    assert nsa.lib().nsa_device_status(None) == 0
