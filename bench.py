@@ -46,6 +46,9 @@ WORKLOADS = {
     # the single-kv-head 8K shape (16 query heads share one kv head)
     "c2_t8k": dict(B=4, T=8192, Hq=16, Hkv=1, D=128, block_size=64, n_sel=16, window=512),
     "tiny": dict(B=1, T=2048, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
+    # a quarter-length, quarter-batch cut of c4_t32k (same heads, so the same bytes per unit and token):
+    # the case counter captures are taken on (inputs above the 126 MB L2, a few GB on the device)
+    "c4_t16k_b2": dict(B=2, T=16384, Hq=16, Hkv=2, D=128, block_size=64, n_sel=16, window=512),
     # forward only at long context, 64 query / 4 kv heads (value = forward tokens/s)
     "c3_t16k_fwd": dict(B=1, T=16384, Hq=64, Hkv=4, D=128, block_size=64, n_sel=16, window=512, fwd_only=True),
     "c3_t32k_fwd": dict(B=1, T=32768, Hq=64, Hkv=4, D=128, block_size=64, n_sel=16, window=512, fwd_only=True),
@@ -646,9 +649,18 @@ def main_leg(args, name, w, rank, world, dev, dist, nsa, L):
     n_pairs = counts["sel_pairs"]
     full = n_loc * G * T_ * D * 2                          # one [units,G,T,D] bf16 tensor
     row = G * D * 2                                        # the G head rows of one query
+    t1 = torch.arange(T_)
+    win_slots = int(((t1 >> 6) - (torch.clamp(t1 - w["window"] + 1, min=0) >> 6) + 1).sum().item())
+    cl_ = w.get("cmp_len") or w["block_size"]
+    cs_ = w.get("cmp_stride") or cl_
+    n_sum_ = (T_ - cl_) // cs_ + 1 if T_ >= cl_ else 0
+    cmp_slots = int(((torch.clamp((t1 + 1 - cl_) // cs_ + 1, min=0, max=n_sum_) + 63) // 64).sum().item())
+    # the dQ reduction reads every partial row once (selection: one per pair; window / compression: one
+    # per key tile a query attends, or the fp32 accumulator instead) and writes dq
+    range_part = 2 * full if nsa.get_dq_accumulator() else n_loc * (win_slots + cmp_slots) * row
     bytes_tab = {
         "sel_combine_kernel": n_pairs * (row + G * 12) + n_loc * T_ * S_ * 4 + full + n_loc * G * T_ * 4,
-        "dq_reduce3": n_pairs * row + n_loc * T_ * S_ * 4 + 2 * full + full,   # partials, fp32 accumulator, dq
+        "dq_reduce3": n_pairs * row + n_loc * T_ * S_ * 4 + range_part + full,
         "gate_fwd_kernel": 4 * full, "gate_bwd_rows_kernel": 4 * full, "sum3_kernel": 4 * full,
     }
     traffic = load_traffic()
