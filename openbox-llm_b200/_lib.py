@@ -89,6 +89,10 @@ def lib():
             fn = getattr(handle, name)
             fn.restype, fn.argtypes = res, args
         _lib = handle
+        # tuning switches from the environment: NSA_B200_OPTIONS="name=value,name=value" (nsa_set_option)
+        for item in filter(None, os.environ.get("NSA_B200_OPTIONS", "").split(",")):
+            name, _, value = item.partition("=")
+            check(handle.nsa_set_option(name.strip().encode(), int(value)))
     return _lib
 
 

@@ -58,6 +58,8 @@ void kernel_end(cudaStream_t st) {
 
 static std::atomic<int> g_opt_sel_fwd{0};
 int get_option_sel_fwd() { return g_opt_sel_fwd.load(); }
+static std::atomic<int> g_opt_bwd_kernel{1};
+int get_option_bwd_kernel() { return g_opt_bwd_kernel.load(); }
 static std::atomic<int> g_opt_merged{1};
 int get_option_merged_boxes() { return g_opt_merged.load(); }
 
@@ -143,6 +145,10 @@ extern "C" long long nsa_launch_count(void) { return g_launches.load(); }
 extern "C" int nsa_set_option(const char* name, int value) {
   if (name && strcmp(name, "sel_fwd_variant") == 0 && value >= 0 && value <= 2) {
     g_opt_sel_fwd.store(value);
+    return NSA_OK;
+  }
+  if (name && strcmp(name, "bwd_kernel") == 0 && value >= 0 && value <= 1) {
+    g_opt_bwd_kernel.store(value);
     return NSA_OK;
   }
   if (name && strcmp(name, "merged_boxes") == 0 && value >= 0 && value <= 1) {

@@ -554,6 +554,489 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   if (tid < 32) tmem_dealloc(tmem, kTmemCols);
 }
 
+// ---- the same backward with the issuing taken out of the compute groups ---------------------------
+// Two row tiles are in flight (shared memory holds no more: Q, dO, P, dS of a tile are 96 KB), one
+// per slot.  Three producer warps refill a slot's Q / dO the moment its MMAs are done; one thread
+// issues whichever batch of MMAs is ready next (S / dP of the tile that has landed, or dV / dK / dQ
+// of the tile whose probabilities are written); each slot has a compute group of 256 threads (two
+// warps per TMEM lane quadrant, half of the key columns each) that turns S / dP into P / dS and,
+// while the slot's next tile is on its way, moves the tile's dQ from TMEM to the staging tile and
+// stores it.  Each hand-over is an mbarrier with a bounded wait.  The tensor pipe needs about 2.9 k
+// cycles per row tile (80-100 cycles per MMA instruction: their shared-memory operands, not the
+// arithmetic); the aim of this arrangement is to keep it fed.
+constexpr int kB2Threads = 640;   // 2 x 8 compute warps, 3 producer warps, MMA warp
+constexpr int kB2Producers = 3;
+constexpr int kB2Compute = 16;    // compute warps
+
+__device__ __forceinline__ bool named_or_b(int id, int threads, int pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"(pred)
+      : "memory");
+  return out != 0;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kB2Threads, 1)
+tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+               const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+               const __grid_constant__ CUtensorMap tm_q_run, const __grid_constant__ CUtensorMap tm_do_run,
+               const __grid_constant__ CUtensorMap tm_dq, const BwdArgs p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kKVBytes = kKeys * 128 * kSlabs;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColDV = 256, kColDK = 320;   // slot s: S at 128 s, dP at 128 s + 64, dQ over both
+  constexpr uint32_t kIdescS = idesc_bf16(128, kKeys, 0, 0);
+  constexpr uint32_t kIdescT = idesc_bf16(128, kKeys, 1, 1);
+  constexpr uint32_t kIdescDQ = idesc_bf16(128, D, 0, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + kKVBytes;
+  uint8_t* sGroup = sV + kKVBytes;
+  uint64_t* bars = (uint64_t*)(sGroup + 2 * kGroupBytes);
+  uint64_t* bar_kv = bars + 0;
+  uint64_t* g_full = bars + 1;       // [2] Q / dO of the slot have landed
+  uint64_t* sp_full = bars + 3;      // [2] S / dP of the slot are in TMEM
+  uint64_t* pds_full = bars + 5;     // [2] P / dS of the slot are in shared memory (128 arrivals)
+  uint64_t* acc_full = bars + 7;     // [2] dV / dK / dQ MMAs of the slot are done
+  uint64_t* dq_read = bars + 9;      // [2] dQ of the slot has left TMEM (128 arrivals)
+  uint64_t* bar_drain = bars + 11;
+  uint32_t* s_tmem = (uint32_t*)(bars + 12);
+  volatile int* s_abort = (volatile int*)(s_tmem + 1);
+  uint32_t* s_prow = (uint32_t*)(s_tmem + 4);        // [2][128] partial row of each tile row (ragged tile), per slot
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  int4 item = make_int4((int)blockIdx.y, (int)blockIdx.x, 0, 1);
+  if (p.kind == 2) {                                 // selection: one work item per CTA
+    if ((int)blockIdx.x >= p.work->n_items) return;
+    item = reinterpret_cast<const int4*>(p.work + 1)[blockIdx.x];
+  }
+  const int j = item.y;                              // key tile
+  const int bh = item.x;
+  const int b = bh / p.Hkv, hkv = bh % p.Hkv;
+  const int key0 = j * kKeys;
+
+  // ---- the queries that attend this key tile ---------------------------------------------
+  int t_lo = 0, n_q = 0, pair_base = 0;
+  if (p.kind == 0) {
+    t_lo = key0;
+    n_q = min(p.T - 1, key0 + kKeys - 1 + p.window - 1) - t_lo + 1;
+  } else if (p.kind == 1) {
+    t_lo = key0 * p.window + p.block_size - 1;       // first query that sees summary key0 (window: the stride)
+    n_q = p.T - t_lo;
+  } else {
+    pair_base = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j);
+    n_q = __ldg(p.offsets + (size_t)bh * (p.n_ktiles + 1) + j + 1) - pair_base;
+  }
+  n_q = max(n_q, 0);
+  const int n_rt_all = (n_q + p.nq - 1) / p.nq;
+  const int chunk = p.kind == 2 ? kSelChunkTiles : ((int)gridDim.z > 1 ? p.split_chunk : n_rt_all);
+  const int rt_begin = p.kind == 2 ? item.z : (int)blockIdx.z * chunk;
+  const int rt_end = min(n_rt_all, rt_begin + chunk);
+  const bool split = p.kind == 2 ? item.w > 1 : gridDim.z > 1;
+  const int n_tiles = rt_end - rt_begin;
+
+  if (n_tiles <= 0) {
+    if (!split && n_rt_all == 0) {   // nobody attends these keys: their gradients are zero
+      for (int i = tid; i < kKeys * D / 8; i += blockDim.x) {
+        const int key = key0 + i / (D / 8);
+        if (key < p.Lk) {
+          const size_t off = ((size_t)bh * p.Lk + key) * D + (i % (D / 8)) * 8;
+          *reinterpret_cast<uint4*>(p.dk + off) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(p.dv + off) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    int bad = (*(volatile int*)p.status != 0) ? 1 : 0;
+    if ((size_t)((uint8_t*)(s_prow + 256) - smem_raw) > bwd_smem_bytes(D)) {
+      atomicOr(p.status, 256);   // the shared-memory window is less aligned than assumed
+      bad = 1;
+    }
+    *s_abort = bad;
+    mbar_init(bar_kv, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(g_full + s, 1); mbar_init(sp_full + s, 1); mbar_init(pds_full + s, 256);
+      mbar_init(acc_full + s, 1); mbar_init(dq_read + s, 256);
+    }
+    mbar_init(bar_drain, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_do); prefetch_tensormap(&tm_dq);
+  }
+  __syncthreads();
+  if (*s_abort) return;
+  // Rows past nq * G of a tile (and, for D = 64, the second slab) are never loaded: keep them 0.
+  for (int i = tid; i < 2 * 2 * kRowTileBytes / 16; i += kB2Threads) {
+    const int buf = i / (kRowTileBytes / 16), o16 = i % (kRowTileBytes / 16);
+    uint8_t* base = sGroup + (buf >> 1) * kGroupBytes + (buf & 1) * kRowTileBytes;
+    *reinterpret_cast<uint4*>(base + o16 * 16) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async();
+  if (warp == 0) {
+    tmem_alloc(s_tmem, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  // dK^T / dV^T start at zero so that every MMA into them accumulates
+  if (warp < 4) {
+    uint32_t z[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) z[c] = 0u;
+    const uint32_t lb = tmem + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) tmem_st32(lb + kColDV + cc * 32, z);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (warp >= kB2Compute && warp < kB2Compute + kB2Producers) {
+    // ---- producers: K / V once, then Q and dO of every tile.  A warp gets a TMA box out every
+    // 60-100 cycles whatever its size, so the boxes of a tile are dealt out over three warps
+    // (box o to warp o % 3) and, where the shape allows, one box brings both column slabs ---------
+    const int pw = warp - kB2Compute;
+    if (pw == 0 && lane == 0) {
+      mbar_expect_tx(bar_kv, 2 * kKVBytes);
+#pragma unroll
+      for (int s = 0; s < kSlabs; ++s) {
+        tma_load_3d(sK + s * (kKeys * 128), &tm_k, bar_kv, s * 64, key0, bh);
+        tma_load_3d(sV + s * (kKeys * 128), &tm_v, bar_kv, s * 64, key0, bh);
+      }
+    }
+    const uint32_t gather_bytes = (uint32_t)(p.nq * p.G * 128 * kSlabs * 2);
+    const int per_q = p.merged ? 2 : kSlabs * 2;     // boxes per query: Q and dO, per slab unless merged
+    const int n_ops = p.nq * per_q;                  // selection: the boxes of a tile
+    constexpr int kRounds = (kMaxNq * kSlabs * 2 + 32 * kB2Producers - 1) / (32 * kB2Producers);
+    auto box_of = [&](int r) -> int { return (r * 32 + lane) * kB2Producers + pw; };
+    auto tq_of = [&](int k, int o) -> int {          // query position of box o of tile k (none: past T, zeros)
+      const int qi = (rt_begin + k) * p.nq + o / per_q;
+      return (o < n_ops && qi < n_q) ? ldg_s32_now(p.q_of_block + pair_base + qi) : p.T;
+    };
+    int tq[kRounds];
+    if (p.kind == 2) {
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) tq[r] = tq_of(0, box_of(r));
+    }
+    for (int k = 0; k < n_tiles; ++k) {
+      const int sb = k & 1;
+      // the slot's Q / dO are free once the dV / dK / dQ MMAs of tile k-2 are done
+      if (k >= 2) mbar_wait(acc_full + sb, ((k >> 1) - 1) & 1, p.status, s_abort, 128);
+      if (__any_sync(0xffffffffu, *s_abort)) break;           // the whole warp leaves together
+      uint8_t* sQ = sGroup + sb * kGroupBytes;
+      uint8_t* sDO = sQ + kRowTileBytes;
+      if (pw == 0 && lane == 0) mbar_expect_tx(g_full + sb, gather_bytes);
+      __syncwarp();
+      if (p.kind != 2) {
+        // window / compression: the tile's queries are consecutive tokens, one box per slab
+        if (pw == 0 && lane == 0) {
+          const int qi = (rt_begin + k) * p.nq;
+          const int t0 = qi < n_q ? t_lo + qi : p.T;
+#pragma unroll
+          for (int s = 0; s < kSlabs; ++s) {
+            tma_load_3d(sQ + s * (kRows * 128), &tm_q_run, g_full + sb, s * 64, b * p.Hq + hkv * p.G, t0);
+            tma_load_3d(sDO + s * (kRows * 128), &tm_do_run, g_full + sb, s * 64, b * p.Hq + hkv * p.G, t0);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+          const int o = box_of(r);
+          if (o < n_ops && p.merged) {
+            tma_load_5d(((o & 1) ? sDO : sQ) + (o >> 1) * (p.G / 8) * 2048, (o & 1) ? &tm_do : &tm_q, g_full + sb,
+                        0, 0, 0, tq[r], (b * p.Hq + hkv * p.G) >> 3);
+          } else if (o < n_ops) {
+            const int qq = o / (kSlabs * 2), kx = o % (kSlabs * 2);
+            const int s = kx >> 1;
+            if (kx & 1)
+              tma_load_3d(sDO + s * (kRows * 128) + qq * p.G * 128, &tm_do, g_full + sb, s * 64,
+                          b * p.Hq + hkv * p.G, tq[r]);
+            else
+              tma_load_3d(sQ + s * (kRows * 128) + qq * p.G * 128, &tm_q, g_full + sb, s * 64,
+                          b * p.Hq + hkv * p.G, tq[r]);
+          }
+        }
+        if (k + 1 < n_tiles) {
+#pragma unroll
+          for (int r = 0; r < kRounds; ++r) tq[r] = tq_of(k + 1, box_of(r));
+        }
+      }
+    }
+  } else if (warp == kB2Compute + kB2Producers) {
+    // ---- MMA issuer: whichever batch is ready next ---------------------------------------------
+    if (lane == 0) {
+      mbar_wait(bar_kv, 0, p.status, s_abort, 32);
+      const uint32_t ka = desc_lo_kmajor(smem_u32(sK)), va = desc_lo_kmajor(smem_u32(sV));
+      const uint32_t kb = desc_lo_mnmajor(smem_u32(sK), kKeys * 128);
+      const uint32_t q_slab = p.merged ? 1024u : (uint32_t)(kRows * 128), q_sbo = p.merged ? 2048u : 1024u;
+      int next_a = 0, next_b = 0;                    // next tile for S / dP, next tile for dV / dK / dQ
+      long long idle_since = clock64();
+      uint32_t polls = 0;
+      while (next_b < n_tiles) {
+        bool progressed = false;
+        if (next_a < n_tiles) {
+          const int k = next_a, sb = k & 1, u = k >> 1;
+          // Q / dO have landed; dQ of tile k-2, which lies over the slot's S / dP columns, has been read
+          if (mbar_try_wait(g_full + sb, u & 1) && (k < 2 || mbar_try_wait(dq_read + sb, (u - 1) & 1))) {
+            tc_fence_after();
+            const uint8_t* sQ = sGroup + sb * kGroupBytes;
+            const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), da = desc_lo_kmajor(smem_u32(sQ + kRowTileBytes));
+            const uint32_t colS = tmem + sb * 128, colDP = colS + 64;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+              mma_ss(colS, desc_at_sbo(qa, slab * q_slab + in, q_sbo), desc_at(ka, slab * (kKeys * 128) + in),
+                     kIdescS, kk > 0);
+            }
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+              mma_ss(colDP, desc_at_sbo(da, slab * q_slab + in, q_sbo), desc_at(va, slab * (kKeys * 128) + in),
+                     kIdescS, kk > 0);
+            }
+            tc_commit(sp_full + sb);
+            ++next_a;
+            progressed = true;
+          }
+        }
+        if (next_b < next_a) {
+          const int k = next_b, sb = k & 1, u = k >> 1;
+          if (mbar_try_wait(pds_full + sb, u & 1)) {
+            tc_fence_after();
+            const uint8_t* sQ = sGroup + sb * kGroupBytes;
+            const uint8_t* sP = sQ + 2 * kRowTileBytes;
+            const uint8_t* sDS = sP + kPBytes;
+            const uint32_t qa = desc_lo_mnmajor(smem_u32(sQ), q_slab);
+            const uint32_t da = desc_lo_mnmajor(smem_u32(sQ + kRowTileBytes), q_slab);
+            const uint32_t pa = desc_lo_mnmajor(smem_u32(sP), 0), dsa = desc_lo_mnmajor(smem_u32(sDS), 0);
+            const uint32_t dsk = desc_lo_kmajor(smem_u32(sDS));
+#pragma unroll
+            for (int kk = 0; kk < kRows / 16; ++kk)        // contraction over the 128 rows, 16 a step
+              mma_ss(tmem + kColDV, desc_at_sbo(da, kk * 2 * q_sbo, q_sbo), desc_at(pa, kk * 2048), kIdescT, 1);
+#pragma unroll
+            for (int kk = 0; kk < kRows / 16; ++kk)
+              mma_ss(tmem + kColDK, desc_at_sbo(qa, kk * 2 * q_sbo, q_sbo), desc_at(dsa, kk * 2048), kIdescT, 1);
+#pragma unroll
+            for (int kk = 0; kk < kKeys / 16; ++kk)        // contraction over the 64 keys
+              mma_ss(tmem + sb * 128, desc_at(dsk, kk * 32), desc_at(kb, kk * 2048), kIdescDQ, kk > 0);
+            tc_commit(acc_full + sb);
+            ++next_b;
+            progressed = true;
+          }
+        }
+        if (progressed) {
+          idle_since = clock64();
+        } else if ((++polls & 0xffu) == 0) {
+          if (*s_abort) break;
+          if (*(volatile int*)p.status != 0) { *s_abort = 1; break; }
+          if (clock64() - idle_since > kWaitLimitCycles) { atomicOr(p.status, 2048); *s_abort = 1; break; }
+        }
+      }
+      // the tensor pipe is idle before TMEM is read for dK / dV and given back, whatever happened
+      tc_commit(bar_drain);
+      mbar_wait(bar_drain, 0, p.status, s_abort, 4096);
+    }
+  } else if (warp < kB2Compute) {
+    // ---- compute group of slot sb: S, dP -> P, dS; then the tile's dQ out -----------------------------
+    const int sb = warp >> 3, wg = warp & 7, lt = (warp & 7) * 32 + lane;
+    const int quad = wg & 3, half = wg >> 2;           // TMEM lane quadrant, key-column half
+    const int row = quad * 32 + lane;
+    const int ql = row / p.G, g = row % p.G;
+    const int head = hkv * p.G + g;
+    const bool row_slot_ok = ql < p.nq;
+    uint8_t* sP = sGroup + sb * kGroupBytes + 2 * kRowTileBytes;
+    uint8_t* sDS = sP + kPBytes;
+    uint32_t* s_prow_g = s_prow + sb * 128;
+    const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + sb * 128;
+    auto row_query = [&](int k) -> int {
+      const int qi = (rt_begin + k) * p.nq + ql;
+      if (!row_slot_ok || qi >= n_q) return -1;
+      if (p.kind == 2) return ldg_s32_now(p.q_of_block + pair_base + qi);
+      return t_lo + qi;
+    };
+    auto row_index = [&](int t) -> size_t { return (size_t)(b * p.Hq + head) * p.T + t; };
+    int t_cur = sb < n_tiles ? row_query(sb) : -1;
+    int t_nxt = sb + 2 < n_tiles ? row_query(sb + 2) : -1;
+    float lse_cur = 0.f, delta_cur = 0.f, gate_cur = 1.f;
+    if (t_cur >= 0) {
+      lse_cur = __ldg(p.lse + row_index(t_cur));
+      delta_cur = __ldg(p.delta + row_index(t_cur));
+      if (p.row_scale) gate_cur = __ldg(p.row_scale + row_index(t_cur));
+    }
+    for (int k = sb; k < n_tiles; k += 2) {
+      const int u = k >> 1, i = rt_begin + k;
+      const int t_nn = (k + 4 < n_tiles) ? row_query(k + 4) : -1;
+      float lse_nxt = 0.f, delta_nxt = 0.f, gate_nxt = 1.f;
+      if (t_nxt >= 0) {
+        lse_nxt = ldg_f32_now(p.lse + row_index(t_nxt));
+        delta_nxt = ldg_f32_now(p.delta + row_index(t_nxt));
+        if (p.row_scale) gate_nxt = ldg_f32_now(p.row_scale + row_index(t_nxt));
+      }
+      int lo = 0, hi = -1;                           // valid key columns of this row: one range [lo, hi]
+      if (t_cur >= 0) {
+        if (p.kind == 0) {
+          lo = max(0, t_cur - p.window + 1 - key0);
+          hi = min(kKeys - 1, t_cur - key0);
+        } else if (p.kind == 1) {
+          hi = min(kKeys - 1, cmp_visible(t_cur, p.block_size, p.window, p.Lk) - 1 - key0);
+        } else {
+          hi = min(kKeys - 1, min(t_cur, p.T - 1) - key0);
+        }
+      }
+      const float lse2 = lse_cur * kLog2e;
+      // dS = scale * gate * p * (dP - delta): the constant factors folded once per row
+      const float dscale = p.scale, ddelta = delta_cur * p.scale;
+      mbar_wait(sp_full + sb, u & 1, p.status, s_abort, 64);
+      // the P / dS tiles double as the dQ staging tile: this group's store of tile k-2 has read it
+      if (lt == 0) bulk_wait_read();
+      if (named_or_b(1 + sb, 256, *s_abort)) break;            // the whole group leaves together
+      tc_fence_after();
+      {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(lane_base + half * 32, rs);
+        tmem_ld32(lane_base + 64 + half * 32, rp);
+        tmem_wait_ld();
+        uint32_t pp[16], pd[16];
+#pragma unroll
+        for (int c2 = 0; c2 < 16; ++c2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = half * 32 + c2 * 2 + e;
+            const bool ok = (c >= lo) && (c <= hi);
+            // gate * p: the branch's dO is gate * dO, so dV takes (gate p)^T dO and
+            // dS = scale * gate * p * (dO.v - dO.o)
+            const float pr = ok ? gate_cur * ex2(__uint_as_float(rs[c2 * 2 + e]) * p.scale_log2 - lse2) : 0.f;
+            pv[e] = pr;
+            dv[e] = pr * fmaf(__uint_as_float(rp[c2 * 2 + e]), dscale, -ddelta);
+          }
+          pp[c2] = pack_bf16(pv[0], pv[1]);
+          pd[c2] = pack_bf16(dv[0], dv[1]);
+        }
+        const uint32_t p_row = smem_u32(sP) + row * 128, ds_row = smem_u32(sDS) + row * 128;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint32_t chunk16 = (uint32_t)((half * 4 + k4) ^ (row & 7)) << 4;
+          st_shared_v4(p_row + chunk16, pp[k4 * 4], pp[k4 * 4 + 1], pp[k4 * 4 + 2], pp[k4 * 4 + 3]);
+          st_shared_v4(ds_row + chunk16, pd[k4 * 4], pd[k4 * 4 + 1], pd[k4 * 4 + 2], pd[k4 * 4 + 3]);
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pds_full + sb);
+      // ---- the tile's dQ: TMEM -> bf16 -> staging tile (the P / dS region, free once the MMAs are
+      // done) -> partial buffer, while the producers fetch the slot's next tile
+      mbar_wait(acc_full + sb, u & 1, p.status, s_abort, 128);
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {          // this thread's half of the D columns
+        const int col0 = half * (D / 2) + cc * 32;
+        uint32_t r32[32];
+        tmem_ld32(lane_base + col0, r32);
+        tmem_wait_ld();
+        if (cc == D / 64 - 1) {            // dQ is in registers: S / dP of the slot's next tile may land
+          tc_fence_before();
+          mbar_arrive(dq_read + sb);
+        }
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const uint32_t chunk = (uint32_t)((col0 >> 3) + v4);
+          st_shared_v4(smem_u32(sP) + (chunk >> 3) * (kRows * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 0]), __uint_as_float(r32[v4 * 8 + 1])),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 2]), __uint_as_float(r32[v4 * 8 + 3])),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 4]), __uint_as_float(r32[v4 * 8 + 5])),
+                       pack_bf16(__uint_as_float(r32[v4 * 8 + 6]), __uint_as_float(r32[v4 * 8 + 7])));
+        }
+      }
+      const bool full_tile = (i + 1) * p.nq <= n_q;
+      if (!full_tile && half == 0) {
+        uint32_t prow = 0xffffffffu;
+        const int qi = i * p.nq + ql;
+        if (row_slot_ok && qi < n_q) {
+          if (p.kind == 2) {
+            prow = (uint32_t)((size_t)(pair_base + qi) * p.G + g);
+          } else {
+            const int slot = p.kind == 0 ? j % p.n_slots : j;
+            prow = (uint32_t)((((size_t)bh * p.T + t_lo + qi) * p.n_slots + slot) * p.G + g);
+          }
+        }
+        s_prow_g[row] = prow;
+      }
+      fence_proxy_async();
+      if (named_or_b(1 + sb, 256, *s_abort)) break;
+      if (full_tile) {
+        // its rows are consecutive in the partial buffer: one TMA store per slab
+        if (lt == 0) {
+          const int slot = p.kind == 2 ? 0 : (p.kind == 0 ? j % p.n_slots : j);
+          const int mid = p.kind == 2 ? pair_base + i * p.nq : t_lo + i * p.nq;
+          const int outer = p.kind == 2 ? 0 : bh;
+#pragma unroll
+          for (int sl = 0; sl < kSlabs; ++sl)
+            tma_store_5d(&tm_dq, sP + sl * (kRows * 128), sl * 64, 0, slot, mid, outer);
+          bulk_commit();
+        }
+      } else {   // the ragged last tile: 16 lanes write the 256 (D = 128) or 128 bytes of one row
+        constexpr int kChunks = D / 8;
+        constexpr int kRowsPerPass = 256 / kChunks;
+        const int c = lt % kChunks;
+        for (int r = lt / kChunks; r < kRows; r += kRowsPerPass) {
+          const uint32_t prow = s_prow_g[r];
+          if (prow != 0xffffffffu) {
+            const uint4 v = *reinterpret_cast<const uint4*>(sP + (c >> 3) * (kRows * 128) + r * 128 +
+                                                            (((c & 7) ^ (r & 7)) << 4));
+            *reinterpret_cast<uint4*>(p.dq_part + (size_t)prow * D + c * 8) = v;
+          }
+        }
+      }
+      t_cur = t_nxt; t_nxt = t_nn; lse_cur = lse_nxt; delta_cur = delta_nxt; gate_cur = gate_nxt;
+    }
+    if (lt == 0) bulk_wait_all();
+  }
+
+  // ---- dK^T, dV^T: lane = d, column = key; compute group 0 writes dV, group 1 writes dK ----------
+  __syncthreads();           // the MMA thread has seen the tensor pipe drain (bar_drain)
+  tc_fence_after();
+  if (warp < kB2Compute && ((warp >> 2) & 1) == 0 && !*s_abort) {
+    const int grp = warp >> 3, quad = warp & 3;
+    const uint32_t col = grp == 0 ? kColDV : kColDK;
+    const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+    const int d = quad * 32 + lane;
+#pragma unroll
+    for (int hc = 0; hc < 2; ++hc) {
+      uint32_t r32[32];
+      tmem_ld32(lane_base + col + hc * 32, r32);
+      tmem_wait_ld();
+      if (d < D) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int key = key0 + hc * 32 + c;
+          if (key < p.Lk) {
+            const size_t o = ((size_t)bh * p.Lk + key) * D + d;
+            if (split) atomicAdd((grp == 0 ? p.dv_acc : p.dk_acc) + o, __uint_as_float(r32[c]));
+            else (grp == 0 ? p.dv : p.dk)[o] = __float2bfloat16_rn(__uint_as_float(r32[c]));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
 // delta[b,h,t] = sum_d dO * O (fp32), one warp per row
 __global__ void delta_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o,
                              float* __restrict__ delta, size_t rows, int D) {
@@ -744,6 +1227,7 @@ int sel_build_worklist(const int32_t* offsets, int n_ktiles, size_t units, size_
 
 }  // namespace tc
 int get_option_merged_boxes();   // api.cu
+int get_option_bwd_kernel();
 namespace tc {
 
 static BwdPlan plan_bwd(const AttnArgs& a) {
@@ -882,7 +1366,16 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   dim3 grid(pl.n_ktiles, a.B * a.Hkv, pl.n_splits);
   if (a.kind == 2)
     grid = dim3((unsigned)sel_work_max_items((size_t)a.B * a.Hkv, pl.n_ktiles, pl.cap_pairs, pl.nq));
-  if (a.D == 128) {
+  if (get_option_bwd_kernel() == 1 && !p.dq_acc_mode) {       // compute groups relieved of the issuing
+    KernelScope ks(branch_name(kBwdNames, a.kind), st);
+    if (a.D == 128) {
+      NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      tc_bwd2_kernel<128><<<grid, kB2Threads, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, p);
+    } else {
+      NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      tc_bwd2_kernel<64><<<grid, kB2Threads, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, p);
+    }
+  } else if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope ks(branch_name(kBwdNames, a.kind), st);
     tc_bwd_kernel<128><<<grid, 512, smem, st>>>(tm_k, tm_v, tm_q, tm_do, tm_q_run, tm_do_run, tm_dq, tm_dqacc, p);
