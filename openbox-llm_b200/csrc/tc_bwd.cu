@@ -604,9 +604,10 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
   uint64_t* sp_full = bars + 3;      // [2] S / dP of the slot are in TMEM
   uint64_t* pds_full = bars + 5;     // [2] P / dS of the slot are in shared memory (128 arrivals)
   uint64_t* acc_full = bars + 7;     // [2] dV / dK / dQ MMAs of the slot are done
-  uint64_t* dq_read = bars + 9;      // [2] dQ of the slot has left TMEM (128 arrivals)
+  uint64_t* dq_read = bars + 9;      // [2] dQ of the slot has left TMEM (256 arrivals)
+  uint64_t* qdo_free = bars + 13;    // [2] the dV / dK MMAs of the slot are done: Q / dO may be refilled
   uint64_t* bar_drain = bars + 11;
-  uint32_t* s_tmem = (uint32_t*)(bars + 12);
+  uint32_t* s_tmem = (uint32_t*)(bars + 16);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
   uint32_t* s_prow = (uint32_t*)(s_tmem + 4);        // [2][128] partial row of each tile row (ragged tile), per slot
 
@@ -666,7 +667,7 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     mbar_init(bar_kv, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(g_full + s, 1); mbar_init(sp_full + s, 1); mbar_init(pds_full + s, 256);
-      mbar_init(acc_full + s, 1); mbar_init(dq_read + s, 256);
+      mbar_init(acc_full + s, 1); mbar_init(dq_read + s, 256); mbar_init(qdo_free + s, 1);
     }
     mbar_init(bar_drain, 1);
     fence_barrier_init();
@@ -733,8 +734,8 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     }
     for (int k = 0; k < n_tiles; ++k) {
       const int sb = k & 1;
-      // the slot's Q / dO are free once the dV / dK / dQ MMAs of tile k-2 are done
-      if (k >= 2) mbar_wait(acc_full + sb, ((k >> 1) - 1) & 1, p.status, s_abort, 128);
+      // the slot's Q / dO are free once the dV / dK MMAs of tile k-2 are done (dQ reads dS and K only)
+      if (k >= 2) mbar_wait(qdo_free + sb, ((k >> 1) - 1) & 1, p.status, s_abort, 128);
       if (__any_sync(0xffffffffu, *s_abort)) break;           // the whole warp leaves together
       uint8_t* sQ = sGroup + sb * kGroupBytes;
       uint8_t* sDO = sQ + kRowTileBytes;
@@ -829,6 +830,7 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
             for (int kk = 0; kk < kRows / 16; ++kk)
               mma_ss(tmem + kColDK, desc_at_sbo(qa, kk * 2 * q_sbo, q_sbo), desc_at(dsa, kk * 2048), kIdescT, 1);
+            tc_commit(qdo_free + sb);
 #pragma unroll
             for (int kk = 0; kk < kKeys / 16; ++kk)        // contraction over the 64 keys
               mma_ss(tmem + sb * 128, desc_at(dsk, kk * 32), desc_at(kb, kk * 2048), kIdescDQ, kk > 0);
@@ -896,9 +898,12 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
           hi = min(kKeys - 1, min(t_cur, p.T - 1) - key0);
         }
       }
-      const float lse2 = lse_cur * kLog2e;
-      // dS = scale * gate * p * (dP - delta): the constant factors folded once per row
+      // gate * p = 2^(s * scale * log2e - lse * log2e + log2(gate)): the branch's dO is gate * dO, so dV takes
+      // (gate p)^T dO; dS = scale * gate * p * (dP - delta), the constant factors folded once per row
+      const float lse2 = lse_cur * kLog2e - __log2f(gate_cur);
       const float dscale = p.scale, ddelta = delta_cur * p.scale;
+      // every column of this thread's half is attended (the usual case away from the diagonal)?
+      const bool all_cols = lo <= half * 32 && hi >= half * 32 + 31;
       mbar_wait(sp_full + sb, u & 1, p.status, s_abort, 64);
       // the P / dS tiles double as the dQ staging tile: this group's store of tile k-2 has read it
       if (lt == 0) bulk_wait_read();
@@ -910,21 +915,30 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         tmem_ld32(lane_base + 64 + half * 32, rp);
         tmem_wait_ld();
         uint32_t pp[16], pd[16];
+        if (__all_sync(0xffffffffu, all_cols)) {
 #pragma unroll
-        for (int c2 = 0; c2 < 16; ++c2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int c = half * 32 + c2 * 2 + e;
-            const bool ok = (c >= lo) && (c <= hi);
-            // gate * p: the branch's dO is gate * dO, so dV takes (gate p)^T dO and
-            // dS = scale * gate * p * (dO.v - dO.o)
-            const float pr = ok ? gate_cur * ex2(__uint_as_float(rs[c2 * 2 + e]) * p.scale_log2 - lse2) : 0.f;
-            pv[e] = pr;
-            dv[e] = pr * fmaf(__uint_as_float(rp[c2 * 2 + e]), dscale, -ddelta);
+          for (int c2 = 0; c2 < 16; ++c2) {
+            const float p0 = ex2(fmaf(__uint_as_float(rs[c2 * 2]), p.scale_log2, -lse2));
+            const float p1 = ex2(fmaf(__uint_as_float(rs[c2 * 2 + 1]), p.scale_log2, -lse2));
+            pp[c2] = pack_bf16(p0, p1);
+            pd[c2] = pack_bf16(p0 * fmaf(__uint_as_float(rp[c2 * 2]), dscale, -ddelta),
+                               p1 * fmaf(__uint_as_float(rp[c2 * 2 + 1]), dscale, -ddelta));
           }
-          pp[c2] = pack_bf16(pv[0], pv[1]);
-          pd[c2] = pack_bf16(dv[0], dv[1]);
+        } else {
+#pragma unroll
+          for (int c2 = 0; c2 < 16; ++c2) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int c = half * 32 + c2 * 2 + e;
+              const bool ok = (c >= lo) && (c <= hi);
+              const float pr = ok ? ex2(fmaf(__uint_as_float(rs[c2 * 2 + e]), p.scale_log2, -lse2)) : 0.f;
+              pv[e] = pr;
+              dv[e] = pr * fmaf(__uint_as_float(rp[c2 * 2 + e]), dscale, -ddelta);
+            }
+            pp[c2] = pack_bf16(pv[0], pv[1]);
+            pd[c2] = pack_bf16(dv[0], dv[1]);
+          }
         }
         const uint32_t p_row = smem_u32(sP) + row * 128, ds_row = smem_u32(sDS) + row * 128;
 #pragma unroll
