@@ -294,7 +294,12 @@ int nsa_profile_summary(char* buf, size_t cap);
 /* Tuning switches.  "sel_fwd_variant": 0 = the selection forward picks, on the device, between
  * its query-outer kernel (cheap when neighbouring queries share blocks) and its block-outer
  * kernel (cheap when they do not); 1 / 2 force one of them.  No counterpart in the reference
- * beyond its USE_FSA_FWD module flag (nsa_selection_kernel.py:48). */
+ * beyond its USE_FSA_FWD module flag (nsa_selection_kernel.py:48).
+ * "debug_starve_load" (0 / 1, tests only): with 1 the tcgen05 window / compression / query-outer
+ * forward kernel never sends the load of its second V tile, so that CTA's bounded wait runs out
+ * after about a second: it raises the status word, waits for what it has in flight, gives its
+ * tensor memory back and returns without writing.  This is how the give-up path is exercised
+ * without faulting or hanging anything. */
 int nsa_set_option(const char* name, int value);
 
 /* Error word of the current device, raised by a kernel whose bounded wait ran out (0 = none).

@@ -62,6 +62,8 @@ static std::atomic<int> g_opt_bwd_kernel{1};
 int get_option_bwd_kernel() { return g_opt_bwd_kernel.load(); }
 static std::atomic<int> g_opt_merged{1};
 int get_option_merged_boxes() { return g_opt_merged.load(); }
+static std::atomic<int> g_opt_starve{0};
+int get_option_debug_starve_load() { return g_opt_starve.load(); }
 
 static int check_dims(const NsaDims* d) {
   NSA_CHECK_ARG(d != nullptr, "dims is null");
@@ -153,6 +155,10 @@ extern "C" int nsa_set_option(const char* name, int value) {
   }
   if (name && strcmp(name, "merged_boxes") == 0 && value >= 0 && value <= 1) {
     g_opt_merged.store(value);
+    return NSA_OK;
+  }
+  if (name && strcmp(name, "debug_starve_load") == 0 && value >= 0 && value <= 1) {
+    g_opt_starve.store(value);
     return NSA_OK;
   }
   set_error("unknown option or value");

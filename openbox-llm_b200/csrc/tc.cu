@@ -30,6 +30,7 @@ struct FwdArgs {
   const unsigned long long* stats;   // selection: statistics for the variant choice (may be null)
   const int32_t* offsets;            // selection: CSR offsets (pair count at the end)
   int force;
+  int debug_starve;          // test only: the V load of the second key tile is never sent
   int n_qtiles, nb_sel;      // nb_sel = ceil(T / 64) blocks a selection list may name
   int nw;                    // 32-bit membership words per block = max(1, nq / 32)
   float scale_log2;
@@ -71,6 +72,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint64_t* bar_v = bars + 3;   // [2]
   uint64_t* bar_s = bars + 5;
   uint64_t* bar_o = bars + 6;
+  uint64_t* bar_drain = bars + 7;   // an aborted CTA waits here for its last MMAs
   uint32_t* s_tmem = (uint32_t*)(bars + 8);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
   int* s_ntiles = (int*)(s_tmem + 2);
@@ -99,6 +101,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(bar_v + 0, 1); mbar_init(bar_v + 1, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
+    mbar_init(bar_drain, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
   }
@@ -154,6 +157,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   float m_used = -INFINITY, l_sum = 0.f;
   uint32_t tmem = 0;
+  bool aborted = false;
+  // thread 0: K / V tiles whose load was issued, and whose arrival was seen (the rest is what an
+  // aborted CTA still has to wait for)
+  int k_loaded = 0, k_seen = 0, v_loaded = 0, v_seen = 0;
+  bool q_seen = false;
 
   if (n_tiles > 0) {
     // ---- TMEM ---------------------------------------------------------------------------
@@ -177,13 +185,16 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
       for (int s = 0; s < kSlabs; ++s)
         tma_load_3d(sK + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_k, bar, s * 64, key0_of(i), bh);
+      k_loaded = i + 1;
     };
     auto load_v = [&](int i) {
       uint64_t* bar = bar_v + (i & 1);
+      if (p.debug_starve && i == 1) return;   // test only: this tile's wait has to run out
       mbar_expect_tx(bar, L::kKVBytes);
 #pragma unroll
       for (int s = 0; s < kSlabs; ++s)
         tma_load_3d(sV + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_v, bar, s * 64, key0_of(i), bh);
+      v_loaded = i + 1;
     };
     auto issue_s = [&](int i) {   // S = Q K^T for tile i
       const uint32_t qa = desc_lo_kmajor(smem_u32(sQ));
@@ -213,17 +224,17 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       load_k(0);
       load_v(0);
       if (n_tiles > 1) { load_k(1); load_v(1); }
-      mbar_wait(bar_q, 0, p.status, s_abort, 1);
-      mbar_wait(bar_k, 0, p.status, s_abort, 2);
+      q_seen = mbar_wait(bar_q, 0, p.status, s_abort, 1);
+      if (mbar_wait(bar_k, 0, p.status, s_abort, 2)) k_seen = 1;
       tc_fence_after();
-      issue_s(0);
+      if (!*s_abort) issue_s(0);
     }
 
     for (int i = 0; i < n_tiles; ++i) {
       const int key0 = key0_of(i);
       mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
       tc_fence_after();
-      if (tid == 0 && i + 2 < n_tiles) load_k(i + 2);   // the K stage of tile i is free again
+      if (tid == 0 && i + 2 < n_tiles && !*s_abort) load_k(i + 2);   // the K stage of tile i is free again
       __syncwarp();
 
       uint32_t r[64];
@@ -283,7 +294,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (i > 0) {                            // P and O are free once PV of tile i-1 is done
         mbar_wait(bar_o, (i - 1) & 1, p.status, s_abort, 8);
         tc_fence_after();
-        if (tid == 0 && i + 1 < n_tiles && i + 1 >= 2) load_v(i + 1);
+        if (tid == 0 && i + 1 < n_tiles && i + 1 >= 2 && !*s_abort) load_v(i + 1);
         __syncwarp();
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
@@ -301,19 +312,41 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tmem_st32(lane_base + kColP, pk);
       tmem_wait_st();
       tc_fence_before();
-      __syncthreads();
+      // one decision for the whole CTA: after a given-up wait nothing more is issued
+      if (__syncthreads_or(*s_abort)) { aborted = true; break; }
       if (tid == 0) {
         tc_fence_after();
-        mbar_wait(bar_v + (i & 1), (i >> 1) & 1, p.status, s_abort, 16);
-        issue_pv(i);
-        if (i + 1 < n_tiles) {
-          mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
-          issue_s(i + 1);
+        if (mbar_wait(bar_v + (i & 1), (i >> 1) & 1, p.status, s_abort, 16)) {
+          v_seen = i + 1;
+          issue_pv(i);
+          if (i + 1 < n_tiles && mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2)) {
+            k_seen = i + 2;
+            issue_s(i + 1);
+          }
         }
       }
     }
-    mbar_wait(bar_o, (n_tiles - 1) & 1, p.status, s_abort, 8);
-    tc_fence_after();
+    if (!aborted) {
+      mbar_wait(bar_o, (n_tiles - 1) & 1, p.status, s_abort, 8);
+      tc_fence_after();
+      aborted = __syncthreads_or(*s_abort) != 0;
+    }
+    if (aborted) {
+      // Give-up path: no output is written.  Thread 0 waits (bounded) for the loads that are still
+      // on their way into this CTA's shared memory and for the MMAs already issued, then the
+      // tensor memory goes back.
+      if (tid == 0) {
+        if (!q_seen) mbar_wait_drain(bar_q, 0);
+        for (int j = k_seen; j < k_loaded; ++j) mbar_wait_drain(bar_k + (j & 1), (j >> 1) & 1);
+        for (int j = v_seen; j < v_loaded; ++j) mbar_wait_drain(bar_v + (j & 1), (j >> 1) & 1);
+        tc_commit(bar_drain);
+        mbar_wait_drain(bar_drain, 0);
+      }
+      tc_fence_before();
+      __syncthreads();
+      if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+      return;
+    }
     __syncwarp();
   }
 
@@ -371,11 +404,14 @@ bool tc_shape_ok(const NsaDims& d, int block_size) {
   return true;
 }
 
+int get_option_debug_starve_load();   // api.cu
+
 static int launch_fwd(const AttnArgs& a, const unsigned long long* stats, const int32_t* offsets,
                       int force, cudaStream_t st) {
   using namespace tc;
   FwdArgs p;
   p.stats = stats; p.offsets = offsets; p.force = force;
+  p.debug_starve = get_option_debug_starve_load();
   p.block_idx = a.block_idx;
   p.o = (__nv_bfloat16*)a.o;
   p.lse = a.lse;

@@ -85,6 +85,18 @@ __host__ __device__ inline size_t bwd_smem_bytes(int D) {
 __device__ __forceinline__ void group_sync(int group) {
   asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kGroupThreads) : "memory");
 }
+// Named barrier that also tells every thread whether any of them brought a non-zero `pred`: the
+// way a group of warps decides together to leave after a given-up wait.
+__device__ __forceinline__ bool named_or_b(int id, int threads, int pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"(pred)
+      : "memory");
+  return out != 0;
+}
 
 // Two compute groups of 256 threads share the key tile and the dK^T / dV^T accumulators and
 // take alternate row tiles, so that one group's MMAs and memory waits overlap the other
@@ -132,6 +144,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint64_t* bar_sp = bars + 1 + 3 * grp;
   uint64_t* bar_acc = bars + 2 + 3 * grp;
   uint64_t* bar_g = bars + 3 + 3 * grp;
+  uint64_t* bar_drain = bars + 7 + 2 * grp;
   int* s_rowt = s_rowt_all + grp * 2 * kMaxNq;
   uint32_t* s_prow = s_prow_all + grp * 128;
 
@@ -192,6 +205,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     // S / dP ready (bars 1 and 4) = the MMAs have completed and the previous tile's dQ store
     // has left the staging tile, which is the P / dS tile: two arrivals
     for (int k = 0; k <= 6; ++k) mbar_init(bars + k, (k == 1 || k == 4) ? 2 : 1);
+    mbar_init(bars + 7, 1); mbar_init(bars + 9, 1);   // per group: an aborted CTA waits here for its last MMAs
     fence_barrier_init();
     prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
     prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_do);
@@ -309,10 +323,12 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (p.row_scale) gate_cur = __ldg(p.row_scale + row_index(t_cur));
   }
   int buf = 0;
+  bool g_pending = false;     // a gather of this group is on its way and its arrival has not been seen
   if (i < rt_end) {
     if (g == 0 && half == 0 && row_slot_ok) s_rowt[ql] = t_cur;
     group_sync(grp);
     gather(s_rowt);
+    g_pending = true;
   }
   uint32_t phase = 0;
   for (; i < rt_end; i += 2, phase ^= 1, buf ^= 1) {
@@ -325,8 +341,10 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     // query positions of this group's next tile, for the gather issued further down
     if (g == 0 && half == 0 && row_slot_ok) s_rowt[(buf ^ 1) * kMaxNq + ql] = t_nxt;
-    mbar_wait(bar_g, phase, p.status, s_abort, 512);
-    group_sync(grp);       // also: the staging tile of the previous iteration has been read
+    if (mbar_wait(bar_g, phase, p.status, s_abort, 512)) g_pending = false;
+    // also: the staging tile of the previous iteration has been read.  One decision for the whole
+    // group: after a given-up wait it issues and writes nothing more
+    if (named_or_b(grp + 1, kGroupThreads, *s_abort)) break;
     if (lt == 0) {
       tc_fence_after();
       const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), da = desc_lo_kmajor(smem_u32(sDO));
@@ -434,7 +452,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       // other two (D = 128) over the dO tile, whose refill therefore waits until the reduction has
       // read them; Q is refilled at once.
       constexpr bool kTwoStep = D > 64;
-      if (i + 2 < rt_end) gather(s_rowt + (buf ^ 1) * kMaxNq, kTwoStep ? 1 : 0);
+      if (i + 2 < rt_end) { gather(s_rowt + (buf ^ 1) * kMaxNq, kTwoStep ? 1 : 0); g_pending = true; }
       __syncwarp();
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) {          // this thread's half of the D columns
@@ -469,7 +487,7 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
     } else {
       // the row tiles are free again: fetch this group's next tile
-      if (i + 2 < rt_end) gather(s_rowt + (buf ^ 1) * kMaxNq);
+      if (i + 2 < rt_end) { gather(s_rowt + (buf ^ 1) * kMaxNq); g_pending = true; }
       __syncwarp();
       // dQ: TMEM -> bf16 -> staging tile (the P / dS region): one slab of 128-byte rows per 64
       // columns, 16-byte chunks XOR row, which is the layout of a 128B-swizzled TMA box
@@ -524,9 +542,23 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   }
 
   if (lt == 0) bulk_wait_all();
-  // ---- dK^T, dV^T: lane = d, column = key; group 0 writes dV, group 1 writes dK ---------------
   tc_fence_before();
-  __syncthreads();
+  if (__syncthreads_or(*s_abort)) {
+    // Give-up path: dK / dV are not written.  Each group's issuing thread waits (bounded) for the
+    // gather still on its way into shared memory and for the MMAs it has issued; then the tensor
+    // memory goes back.
+    if (lt == 0) {
+      if (grp == 0) mbar_wait_drain(bar_kv, 0);
+      if (g_pending) mbar_wait_drain(bar_g, phase);
+      tc_commit(bar_drain);
+      mbar_wait_drain(bar_drain, 0);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid < 32) tmem_dealloc(tmem, kTmemCols);
+    return;
+  }
+  // ---- dK^T, dV^T: lane = d, column = key; group 0 writes dV, group 1 writes dK ---------------
   tc_fence_after();
   if (half == 0) {
     const uint32_t col = grp == 0 ? kColDV : kColDK;
@@ -567,17 +599,6 @@ tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 constexpr int kB2Threads = 640;   // 2 x 8 compute warps, 3 producer warps, MMA warp
 constexpr int kB2Producers = 3;
 constexpr int kB2Compute = 16;    // compute warps
-
-__device__ __forceinline__ bool named_or_b(int id, int threads, int pred) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\t"
-      "bar.red.or.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(out)
-      : "r"(id), "r"(threads), "r"(pred)
-      : "memory");
-  return out != 0;
-}
 
 template <int D>
 __global__ void __launch_bounds__(kB2Threads, 1)
@@ -732,6 +753,7 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
       for (int r = 0; r < kRounds; ++r) tq[r] = tq_of(0, box_of(r));
     }
+    int issued = 0;                                  // tiles whose loads this warp has sent off
     for (int k = 0; k < n_tiles; ++k) {
       const int sb = k & 1;
       // the slot's Q / dO are free once the dV / dK MMAs of tile k-2 are done (dQ reads dS and K only)
@@ -775,6 +797,13 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
           for (int r = 0; r < kRounds; ++r) tq[r] = tq_of(k + 1, box_of(r));
         }
       }
+      issued = k + 1;
+    }
+    if (*s_abort && pw == 0 && lane == 0) {
+      // give-up path: the loads still on their way into this CTA's shared memory land (bounded
+      // wait on the last phase of each slot) before the CTA ends
+      mbar_wait_drain(bar_kv, 0);
+      for (int k = max(0, issued - 2); k < issued; ++k) mbar_wait_drain(g_full + (k & 1), (k >> 1) & 1);
     }
   } else if (warp == kB2Compute + kB2Producers) {
     // ---- MMA issuer: whichever batch is ready next ---------------------------------------------
@@ -849,7 +878,7 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
       }
       // the tensor pipe is idle before TMEM is read for dK / dV and given back, whatever happened
       tc_commit(bar_drain);
-      mbar_wait(bar_drain, 0, p.status, s_abort, 4096);
+      if (!mbar_wait(bar_drain, 0, p.status, s_abort, 4096)) mbar_wait_drain(bar_drain, 0);
     }
   } else if (warp < kB2Compute) {
     // ---- compute group of slot sb: S, dP -> P, dS; then the tile's dQ out -----------------------------

@@ -51,23 +51,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  When the limit runs out the kernel raises the device status word, marks the
 // CTA as aborted and every later wait of the CTA returns at once, so the grid drains; other
 // CTAs notice the status word the next time one of their waits is slow.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* status,
+// Returns true when the phase completed, false when the wait was given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status,
                                           volatile int* s_abort, int code) {
-  if (*s_abort) return;
-  if (mbar_try_wait(bar, parity)) return;
+  if (*s_abort) return false;
+  if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 0xffu) == 0) {
-      if (*s_abort) return;
-      if (*(volatile int*)status != 0) { *s_abort = 1; return; }
+      if (*s_abort) return false;
+      if (*(volatile int*)status != 0) { *s_abort = 1; return false; }
       if (clock64() - start > kWaitLimitCycles) {
         atomicOr(status, code);
         *s_abort = 1;
-        return;
+        return false;
       }
     }
   }
+  return true;
+}
+
+// Wait of an aborted CTA for something of its own that is still in flight (a TMA load into its
+// shared memory, MMAs reading it) before it gives the memory back: bounded like every other wait,
+// and not cut short by the abort flag.
+constexpr long long kDrainLimitCycles = 20000000LL;   // about ten milliseconds
+__device__ __forceinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity))
+    if (clock64() - start > kDrainLimitCycles) return false;
+  return true;
 }
 
 // ---- selection work list -----------------------------------------------------------------------

@@ -235,7 +235,7 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       }
       // the tensor pipe is idle before TMEM is given back, whatever happened above
       tc_commit(bar_drain);
-      mbar_wait(bar_drain, 0, p.status, s_abort, 2048);
+      if (!mbar_wait(bar_drain, 0, p.status, s_abort, 2048)) mbar_wait_drain(bar_drain, 0);
     }
   } else if (warp < 8) {
     // ---- softmax group `sb` ------------------------------------------------------------------
@@ -373,9 +373,7 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const int issued = *s_issued;
     for (int k = max(0, issued - kPairQStages); k < issued; ++k) {
       // bounded: a gather that never lands was what made the CTA give up in the first place
-      const long long t0 = clock64();
-      while (!mbar_try_wait(q_full + k % kPairQStages, (k / kPairQStages) & 1) &&
-             clock64() - t0 < kWaitLimitCycles) {}
+      mbar_wait_drain(q_full + k % kPairQStages, (k / kPairQStages) & 1);
     }
   }
   tc_fence_before();

@@ -25,21 +25,8 @@ struct ScoreArgs {
   // blocks of sel_block = r * stride tokens; overlap: block_size == 2 * stride; imp_out has imp_cols columns
   int stride, sel_block, r, overlap, imp_cols;
   float scale_log2;
-#ifdef NSA_TRACE
-  long long* trace;
-#endif
 };
 
-#ifdef NSA_TRACE
-extern "C" long long* nsa_trace_buffer();
-#define SC_STAMP(k)                                                                         \
-  do {                                                                                      \
-    if (p.trace && blockIdx.x == 100 && blockIdx.y == 0 && tid == 33 && i < 8)               \
-      p.trace[i * 12 + (k)] = clock64();                                                    \
-  } while (0)
-#else
-#define SC_STAMP(k) do {} while (0)
-#endif
 
 __host__ __device__ inline size_t score_smem_bytes(int D, int nq) {
   return (size_t)(kRows * 128 + 2 * kKeys * 128) * (D / 64) + (size_t)kRows * kKeys * 4 +
@@ -65,7 +52,8 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_q = bars + 0;
   uint64_t* bar_k = bars + 1;   // [2]
   uint64_t* bar_s = bars + 3;
-  uint32_t* s_tmem = (uint32_t*)(bars + 4);
+  uint64_t* bar_drain = bars + 4;   // an aborted CTA waits here for its last MMAs
+  uint32_t* s_tmem = (uint32_t*)(bars + 5);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -83,6 +71,7 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar_q, 1);
     mbar_init(bar_k + 0, 1); mbar_init(bar_k + 1, 1);
     mbar_init(bar_s, 1);
+    mbar_init(bar_drain, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k);
   }
@@ -111,6 +100,9 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   for (int k = 0; k < kList; ++k) { lv[k] = -1.f; li[k] = -1; }
 
   uint32_t tmem = 0;
+  bool aborted = false;
+  int k_loaded = 0, k_seen = 0;   // thread 0: K tiles whose load was issued / whose arrival was seen
+  bool q_seen = false;
   if (n_tiles > 0) {
     if (warp == 0) {
       tmem_alloc(s_tmem, kTmemCols);
@@ -129,6 +121,7 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int s = 0; s < kSlabs; ++s)
         tma_load_3d(sK + (i & 1) * kKBytes + s * (kKeys * 128), &tm_k, bar, s * 64, i * kKeys, bh);
+      k_loaded = i + 1;
     };
     auto issue_s = [&](int i) {
       const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), ka = desc_lo_kmajor(smem_u32(sK + (i & 1) * kKBytes));
@@ -147,19 +140,17 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_3d(sQ + s * (kRows * 128), &tm_q, bar_q, s * 64, t0, b * p.Hq + hkv * p.G);
       load_k(0);
       if (n_tiles > 1) load_k(1);
-      mbar_wait(bar_q, 0, p.status, s_abort, 1);
-      mbar_wait(bar_k, 0, p.status, s_abort, 2);
+      q_seen = mbar_wait(bar_q, 0, p.status, s_abort, 1);
+      if (mbar_wait(bar_k, 0, p.status, s_abort, 2)) k_seen = 1;
       tc_fence_after();
-      issue_s(0);
+      if (!*s_abort) issue_s(0);
     }
 
     for (int i = 0; i < n_tiles; ++i) {
       const int key0 = i * kKeys;
-      SC_STAMP(0);
-      mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
-      SC_STAMP(1);
+      const bool s_ok = mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
       tc_fence_after();
-      if (tid == 0 && i + 2 < n_tiles) load_k(i + 2);
+      if (tid == 0 && i + 2 < n_tiles && s_ok) load_k(i + 2);
       __syncwarp();
       uint32_t r[64];
       tmem_ld32(lane_base, r);
@@ -178,13 +169,15 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // 16-byte chunk index XOR row: a warp's stores spread over the banks
         dst[c4 ^ (tid & 15)] = v;
       }
-      SC_STAMP(2);
-      __syncthreads();                         // all of S is read, all of P is in shared memory
-      SC_STAMP(3);
+      // all of S is read, all of P is in shared memory; one decision for the whole CTA: after a
+      // given-up wait nothing more is issued or written
+      if (__syncthreads_or(*s_abort)) { aborted = true; break; }
       if (tid == 0 && i + 1 < n_tiles) {
         tc_fence_after();
-        mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
-        issue_s(i + 1);
+        if (mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2)) {
+          k_seen = i + 2;
+          issue_s(i + 1);
+        }
       }
       // group sums: importance[ql][c] = sum over heads, ascending; four columns per thread
       for (int e = tid; e < p.nq * (kKeys / 4); e += 128) {
@@ -205,9 +198,7 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (key0 + c4 * 4 + e < p.n_blk) out[e] = (c4 * 4 + e <= hq) ? vals[e] : 0.f;
         }
       }
-      SC_STAMP(4);
       __syncthreads();
-      SC_STAMP(5);
       // top-16 update: this thread scans its share of the query's 64 candidates
       {
         const int hq = my_t < p.T ? min(kKeys - 1, min(p.n_blk, (my_t + 1) / p.block_size) - 1 - key0) : -1;
@@ -234,9 +225,23 @@ tc_score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-      SC_STAMP(6);
       __syncthreads();                         // sP / sImp are rewritten by the next tile
-      SC_STAMP(7);
+    }
+    if (!aborted) aborted = __syncthreads_or(*s_abort) != 0;
+    if (aborted) {
+      // Give-up path: no list is written.  Thread 0 waits (bounded) for the loads still on their
+      // way into this CTA's shared memory and for the MMAs already issued, then the tensor memory
+      // goes back.
+      if (tid == 0) {
+        if (!q_seen) mbar_wait_drain(bar_q, 0);
+        for (int j = k_seen; j < k_loaded; ++j) mbar_wait_drain(bar_k + (j & 1), (j >> 1) & 1);
+        tc_commit(bar_drain);
+        mbar_wait_drain(bar_drain, 0);
+      }
+      tc_fence_before();
+      __syncthreads();
+      if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+      return;
     }
     tc_fence_before();
     __syncthreads();
@@ -296,7 +301,8 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   uint64_t* bar_q = bars + 0;
   uint64_t* bar_k = bars + 1;   // [2]
   uint64_t* bar_s = bars + 3;
-  uint32_t* s_tmem = (uint32_t*)(bars + 4);
+  uint64_t* bar_drain = bars + 4;   // an aborted CTA waits here for its last MMAs
+  uint32_t* s_tmem = (uint32_t*)(bars + 5);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -314,6 +320,7 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     mbar_init(bar_q, 1);
     mbar_init(bar_k + 0, 1); mbar_init(bar_k + 1, 1);
     mbar_init(bar_s, 1);
+    mbar_init(bar_drain, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k);
   }
@@ -341,6 +348,9 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
+    bool aborted = false;
+    int k_loaded = 0, k_seen = 0;   // thread 0: K tiles whose load was issued / whose arrival was seen
+    bool q_seen = false;
     const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
     const float lse2 = row_ok ? __ldg(p.lse + (size_t)(b * p.Hq + hkv * p.G + g) * p.T + t) * kLog2e : 0.f;
     const int n_vis = t < p.T ? cmp_visible(t, p.block_size, p.stride, p.n_blk) : 0;   // summaries query t sees
@@ -353,6 +363,7 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
       for (int sl = 0; sl < kSlabs; ++sl)
         tma_load_3d(sK + (i & 1) * kKBytes + sl * (kKeys * 128), &tm_k, bar, sl * 64, i * kKeys, bh);
+      k_loaded = i + 1;
     };
     auto issue_s = [&](int i) {
       const uint32_t qa = desc_lo_kmajor(smem_u32(sQ)), ka = desc_lo_kmajor(smem_u32(sK + (i & 1) * kKBytes));
@@ -371,10 +382,10 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tma_load_3d(sQ + sl * (kRows * 128), &tm_q, bar_q, sl * 64, b * p.Hq + hkv * p.G, t0);
       load_k(0);
       if (n_tiles > 1) load_k(1);
-      mbar_wait(bar_q, 0, p.status, s_abort, 1);
-      mbar_wait(bar_k, 0, p.status, s_abort, 2);
+      q_seen = mbar_wait(bar_q, 0, p.status, s_abort, 1);
+      if (mbar_wait(bar_k, 0, p.status, s_abort, 2)) k_seen = 1;
       tc_fence_after();
-      issue_s(0);
+      if (!*s_abort) issue_s(0);
     }
 
     for (int i = 0; i < n_tiles; ++i) {
@@ -394,13 +405,17 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int c = 0; c < 64; ++c)
           v[c] = (c <= hi) ? ex2(__uint_as_float(r[c]) * p.scale_log2 - lse2) : 0.f;
       }
-      __syncthreads();                         // every thread has read S: the next MMA may overwrite it
+      // every thread has read S: the next MMA may overwrite it; one decision for the whole CTA:
+      // after a given-up wait nothing more is issued or written
+      if (__syncthreads_or(*s_abort)) { aborted = true; break; }
       if (tid == 0) {
         if (i + 2 < n_tiles) load_k(i + 2);    // stage i & 1 was read by the MMA that just completed
         if (i + 1 < n_tiles) {
           tc_fence_after();
-          mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
-          issue_s(i + 1);
+          if (mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2)) {
+            k_seen = i + 2;
+            issue_s(i + 1);
+          }
         }
       }
       __syncwarp();
@@ -459,6 +474,22 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (cv > lv[0]) { lv[0] = cv; li[0] = cj; }
         }
       }
+    }
+    if (!aborted) aborted = __syncthreads_or(*s_abort) != 0;
+    if (aborted) {
+      // Give-up path: no list is written.  Thread 0 waits (bounded) for the loads still on their
+      // way into this CTA's shared memory and for the MMAs already issued, then the tensor memory
+      // goes back.
+      if (tid == 0) {
+        if (!q_seen) mbar_wait_drain(bar_q, 0);
+        for (int j = k_seen; j < k_loaded; ++j) mbar_wait_drain(bar_k + (j & 1), (j >> 1) & 1);
+        tc_commit(bar_drain);
+        mbar_wait_drain(bar_drain, 0);
+      }
+      tc_fence_before();
+      __syncthreads();
+      if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+      return;
     }
     tc_fence_before();
     __syncthreads();
@@ -546,9 +577,6 @@ int tc_topn(const void* q, const void* k_cmp, const float* lse, int32_t* block_i
   p.overlap = block_size / stride - 1; p.imp_cols = imp_cols;
   p.n_qtiles = (d.T + p.nq - 1) / p.nq;
   p.scale_log2 = kLog2e / sqrtf((float)d.D);
-#ifdef NSA_TRACE
-  p.trace = nsa_trace_buffer();
-#endif
   if (p.Gp == 4 || p.Gp == 8 || p.Gp == 16) {
     int rc = NSA_ERR_UNSUPPORTED;
     if (d.D == 128) rc = p.Gp == 4 ? launch_score_lanes<128, 4>(q, k_cmp, d, n_blk, p, st)

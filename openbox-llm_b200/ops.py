@@ -74,12 +74,14 @@ def _check_qkv(q, k, v):
 # raw launch wrappers
 # ---------------------------------------------------------------------------------------
 @L.on_device
-def range_attn_forward(q, k, v, mode, window, block_size):
-    """o, lse of the window (mode 0) or compression (mode 1) branch."""
+def range_attn_forward(q, k, v, mode, window, block_size, out=None):
+    """o, lse of the window (mode 0) or compression (mode 1) branch.  `out` = (o, lse) makes the
+    kernel write into existing contiguous tensors (the whole op keeps its three branches' outputs
+    and statistics in one tensor each)."""
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    o = torch.empty_like(q)
-    lse = torch.empty(B, Hq, T, device=q.device, dtype=torch.float32)
+    o, lse = out if out is not None else (
+        torch.empty_like(q), torch.empty(B, Hq, T, device=q.device, dtype=torch.float32))
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
     L.check(L.lib().nsa_range_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse), d,
                                        k.shape[2], mode, int(window), int(block_size),
@@ -126,16 +128,17 @@ def range_attn_backward_acc(q, k, v, o, lse, do, mode, window, block_size, row_s
 
 
 @L.on_device
-def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False):
-    """nsa_selection_kernel.py:175-213.  q [B,Hq,T,D], k/v [B,Hkv,T,D], block_idx [B,Hkv,T,S]."""
+def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False, out=None):
+    """nsa_selection_kernel.py:175-213.  q [B,Hq,T,D], k/v [B,Hkv,T,D], block_idx [B,Hkv,T,S].
+    `out` = (o, lse): write into existing contiguous tensors (not in the reference's signature)."""
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     S = block_idx.shape[-1]
     assert block_idx.shape[:3] == (B, Hkv, T)
     assert block_size >= 16, "block_size must be >= 16 (tl.dot inner dim)"
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     idx = block_idx.to(torch.int32).contiguous()
-    o = torch.empty_like(q)
-    lse = torch.empty(B, Hq, T, device=q.device, dtype=torch.float32)
+    o, lse = out if out is not None else (
+        torch.empty_like(q), torch.empty(B, Hq, T, device=q.device, dtype=torch.float32))
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
     nws = L.lib().nsa_selection_fwd_workspace_bytes(d, S, block_size, L.IMPL[_impl])
     ws = L.workspace(nws, q.device)
@@ -525,18 +528,22 @@ class _NSAAttention(torch.autograd.Function):
             cp = []
             k_cmp = _mean_pool_fwd(kc, block_size)
             v_cmp = _mean_pool_fwd(vc, block_size)
-        o_cmp, lse_cmp = range_attn_forward(q, k_cmp, v_cmp, MODE_COMPRESS_STRIDED, cs, cl)
+        # the three branches' outputs and softmax statistics live in one tensor each
+        q = q.contiguous()
+        o3 = torch.empty((3,) + tuple(q.shape), device=q.device, dtype=q.dtype)
+        lse3 = torch.empty((3,) + tuple(q.shape[:3]), device=q.device, dtype=torch.float32)
+        o_cmp, lse_cmp = range_attn_forward(q, k_cmp, v_cmp, MODE_COMPRESS_STRIDED, cs, cl, out=(o3[0], lse3[0]))
         if block_idx is None:
             block_idx = topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, n_init_blocks=n_init,
                                     n_local_blocks=n_local, cmp_len=cl, cmp_stride=cs)
         else:
             block_idx = block_idx.to(torch.int32).contiguous()
-        o_slc, lse_slc = selection_forward_triton(q, ks, vs, block_idx, block_size, return_lse=True)
-        o_win, lse_win = range_attn_forward(q, kw, vw, MODE_WINDOW, window, 0)
+        o_slc, _ = selection_forward_triton(q, ks, vs, block_idx, block_size, return_lse=True,
+                                            out=(o3[1], lse3[1]))
+        o_win, _ = range_attn_forward(q, kw, vw, MODE_WINDOW, window, 0, out=(o3[2], lse3[2]))
         gate = gate_logits.to(q.dtype).contiguous()
         out = _gate_fwd(o_cmp, o_slc, o_win, gate)
-        ctx.save_for_backward(q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o_cmp, o_slc, o_win,
-                              lse_cmp, lse_slc, lse_win, block_idx, *cp)
+        ctx.save_for_backward(q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o3, lse3, block_idx, *cp)
         ctx.cfg = (block_size, window, learned, gate_logits.dtype,
                    tuple(t.dtype for t in (k_intra, k_logits, k_proj, v_intra, v_logits, v_proj))
                    if learned else None, cl, cs)
@@ -548,8 +555,8 @@ class _NSAAttention(torch.autograd.Function):
     @staticmethod
     @L.on_device
     def backward(ctx, d_out, _d_idx):
-        (q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o_cmp, o_slc, o_win,
-         lse_cmp, lse_slc, lse_win, block_idx, *cp) = ctx.saved_tensors
+        (q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o3, lse3, block_idx, *cp) = ctx.saved_tensors
+        (o_cmp, o_slc, o_win), (lse_cmp, lse_slc, lse_win) = o3, lse3
         block_size, window, learned, gate_dtype, pdt, cl, cs = ctx.cfg
         T = q.shape[2]
         # gate backward as per-row statistics; the branch kernels apply the gate factor themselves

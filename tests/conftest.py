@@ -22,6 +22,28 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(autouse=True)
+def _library_state_does_not_leak(request):
+    """Every GPU test starts from the library's defaults: kernel choice, options and dq path are
+    process-wide settings, and the device status word is sticky until it is read.  With this reset
+    no test depends on the order of collection (test_zz_no_alloc.py is named to run last only so
+    that the fixed scratch array it uses is first touched after every other kernel has run)."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import importlib
+    import torch
+    if not torch.cuda.is_available():
+        return
+    nsa = importlib.import_module("openbox-llm_b200")
+    nsa.set_impl("auto")
+    nsa.set_dq_accumulator(False)
+    for name, value in (("sel_fwd_variant", 0), ("merged_boxes", 1), ("bwd_kernel", 1),
+                        ("debug_starve_load", 0)):
+        nsa.set_option(name, value)
+    nsa.lib().nsa_device_status(None)          # reading clears the word
+
+
 def pytest_terminal_summary(terminalreporter):
     """The worst measured error of each kind of tensor over the session, next to its bound."""
     try:

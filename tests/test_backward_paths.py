@@ -21,6 +21,7 @@ def _reset():
     pkg().set_dq_accumulator(False)
     pkg().set_impl("auto")
     pkg().set_option("sel_fwd_variant", 0)
+    pkg().set_option("debug_starve_load", 0)
 
 
 def _op(nsa, t, c, dtype, comp=None, idx=None):
@@ -179,3 +180,51 @@ def test_status_word_give_up_path_from_the_host():
     with pytest.raises(L.NsaError):
         step.check_status()
     assert lib.nsa_device_status(None) == 0
+
+
+def test_wait_that_runs_out_gives_up_and_leaves_the_context_usable():
+    """A bounded device wait made to run out, in the one form that faults and hangs nothing: with the
+    test-only option the forward kernel never sends one of its loads, so the CTAs that need it spin
+    for their limit (about a second, all at the same time), raise the status word, wait for what
+    they have in flight, give their tensor memory back and return without writing.  The launch and
+    the synchronisation succeed, the status word names the wait, rows of CTAs that never needed the
+    missing load are correct, all others are untouched, and the next call is correct."""
+    nsa = pkg()
+    L = importlib.import_module("openbox-llm_b200._lib")
+    lib = L.lib()
+    dtype = torch.bfloat16
+    B, Hq, Hkv, T, D, W = 1, 16, 1, 256, 128, 128
+    g = torch.Generator().manual_seed(21)
+    q = (torch.randn(B, Hq, T, D, generator=g) * D ** -0.5).to(dtype).cuda()
+    k = (torch.randn(B, Hkv, T, D, generator=g) * D ** -0.5).to(dtype).cuda()
+    v = torch.randn(B, Hkv, T, D, generator=g).to(dtype).cuda()
+    d = L.dims(B, Hq, Hkv, T, D, L.DTYPE_BF16)
+
+    def launch(o, lse):
+        return lib.nsa_range_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse), d, T,
+                                      L.MODE_WINDOW, W, 0, L.IMPL["tc"], L.stream())
+
+    o_ok, lse_ok = torch.empty_like(q), torch.empty(B, Hq, T, device="cuda")
+    assert launch(o_ok, lse_ok) == 0 and lib.nsa_device_status(None) == 0
+    canary = 1.5
+    o = torch.full_like(q, canary)
+    lse = torch.full((B, Hq, T), canary, device="cuda")
+    nsa.set_option("debug_starve_load", 1)
+    try:
+        assert launch(o, lse) == 0
+        torch.cuda.synchronize()                       # returns: the waits are bounded
+    finally:
+        nsa.set_option("debug_starve_load", 0)
+    status = lib.nsa_device_status(None)               # reads and clears
+    # the V-tile wait (16) starves; the waits behind it (S ready 4, O ready 8) start at the same
+    # moment in other threads and may be the first to reach the limit
+    assert status != 0 and (status & ~(4 | 8 | 16)) == 0, f"status word {status:#x}"
+    assert lib.nsa_device_status(None) == 0
+    # queries 0..63 see one key tile only: their CTAs finished before anything ran out
+    assert torch.equal(o[:, :, :64], o_ok[:, :, :64]) and torch.equal(lse[:, :, :64], lse_ok[:, :, :64])
+    # every CTA that needed the second tile gave up and wrote nothing
+    assert (o[:, :, 64:].float() == canary).all() and (lse[:, :, 64:] == canary).all()
+    assert launch(o, lse) == 0
+    torch.cuda.synchronize()
+    assert lib.nsa_device_status(None) == 0
+    assert torch.equal(o, o_ok) and torch.equal(lse, lse_ok)

@@ -82,11 +82,10 @@ def _same_training(a, b, lr, steps):
     """Two replicas trained on the same batches by two implementations of one step.  Kernels that
     accumulate with fp32 atomics make the gradients differ in the last bits from run to run, and
     Adam turns a gradient whose sign is noise into a step of +-lr either way: single entries may
-    drift by up to 2 * lr per step, the bulk may not."""
+    drift by up to 2 * lr per step (no bound on the maximum can fail, so none is asserted), the
+    bulk may not."""
     for (n, p), q in zip(a.named_parameters(), b.parameters()):
-        d = (p - q).abs()
-        assert d.max().item() <= 2.5 * lr * steps, n
-        assert d.mean().item() <= 0.05 * lr * steps, n
+        assert (p - q).abs().mean().item() <= 0.05 * lr * steps, n
 
 
 @pytest.mark.gpu
@@ -147,9 +146,44 @@ def test_training_step_matches_the_reference_recipe():
 
 @pytest.mark.gpu
 def test_graph_replay_gives_the_eager_step():
-    """Forward + backward replayed from a CUDA graph: the same losses and parameters as the eager
-    step on the same batches (the attention kernels, their work lists and device-side choices all
-    run inside the capture)."""
+    """Forward + backward replayed from a CUDA graph against the eager step on the same batches
+    (the attention kernels, their work lists and device-side choices all run inside the capture).
+    With lr = 0 the two replicas keep identical parameters, so every step compares the loss and the
+    flat gradient of one and the same function: what may differ is the order of fp32 atomic adds
+    and of the dK / dV accumulation, nothing else."""
+    M = importlib.import_module("openbox-llm_b200.model")
+    torch.manual_seed(0)
+    kw = dict(vocab_size=512, d_model=128, n_layers=2, n_q_heads=4, n_kv_heads=2, max_seq_len=256,
+              block_size=64, n_selected_blocks=2, window=64)
+    a = M.NSATransformerB200(**kw).cuda()
+    b = copy.deepcopy(a)
+    sa = DP.DataParallelStep(a, lr=0.0, use_graph=True, graph_warmup=2)
+    sb = DP.DataParallelStep(b, lr=0.0)
+    g = torch.Generator().manual_seed(2)
+    worst = 0.0
+    for i in range(6):
+        idx = torch.randint(0, 512, (2, 256), generator=g).cuda()
+        tgt = torch.randint(0, 512, (2, 256), generator=g).cuda()
+        la, lb = float(sa.step(idx, tgt)), float(sb.step(idx, tgt))
+        assert abs(la - lb) <= 1e-5 * max(1.0, abs(lb)), (i, la, lb)
+        ga, gb = sa.flat.grad.float(), sb.flat.grad.float()
+        rel = ((ga - gb).norm() / gb.norm().clamp_min(1e-12)).item()
+        worst = max(worst, rel)
+        assert rel <= 1e-3, (i, rel)
+        assert (ga - gb).abs().max().item() <= 1e-3 * gb.abs().max().item(), i
+    assert sa.graph is not None
+    for p, q in zip(a.parameters(), b.parameters()):
+        assert torch.equal(p, q)
+    print(f"graph vs eager: worst relative L2 of the flat gradient {worst:.2e}")
+    lib = importlib.import_module("openbox-llm_b200._lib").lib()
+    assert lib.nsa_device_status(None) == 0
+
+
+@pytest.mark.gpu
+def test_graph_replay_trains_like_the_eager_step():
+    """Six optimizer steps, graph against eager: the losses stay together (parameters are not
+    compared entry by entry: Adam turns a gradient entry whose sign is rounding noise into a step of
+    +-lr either way, so single entries may part while the function does not)."""
     M = importlib.import_module("openbox-llm_b200.model")
     torch.manual_seed(0)
     kw = dict(vocab_size=512, d_model=128, n_layers=2, n_q_heads=4, n_kv_heads=2, max_seq_len=256,
@@ -164,7 +198,46 @@ def test_graph_replay_gives_the_eager_step():
         tgt = torch.randint(0, 512, (2, 256), generator=g).cuda()
         la, lb = float(sa.step(idx, tgt)), float(sb.step(idx, tgt))
         assert abs(la - lb) <= 2e-3 * max(1.0, abs(lb)), (i, la, lb)
-    assert sa.graph is not None
-    _same_training(a, b, 1e-3, 6)
-    lib = importlib.import_module("openbox-llm_b200._lib").lib()
-    assert lib.nsa_device_status(None) == 0
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert (p - q).abs().mean().item() <= 0.05 * 1e-3 * 6, n
+
+
+@pytest.mark.gpu
+def test_model_against_the_reference_transformer():
+    """NSATransformerB200 against the reference's own NSATransformer(attn_impl="ref") (pure torch,
+    nsa_model.py:455-506) holding the same state_dict: one forward + backward under bf16 autocast on
+    one batch, loss and every parameter gradient.  Bounds: the reference's own model-level gate
+    (test_integration.py: loss 5e-2, gradients 8e-2 max-abs in bf16)."""
+    MR = importlib.import_module("oracle.make_ref")
+    if not MR.available():
+        pytest.skip("oracle/_ref holds no copy of the reference modules (python oracle/make_ref.py)")
+    MR.import_path()
+    ref_mod = importlib.import_module("nsa_model")
+    M = importlib.import_module("openbox-llm_b200.model")
+    torch.manual_seed(0)
+    kw = dict(vocab_size=512, d_model=128, n_layers=2, n_q_heads=4, n_kv_heads=2, max_seq_len=256,
+              block_size=64, n_selected_blocks=2, window=64)
+    ref = ref_mod.NSATransformer(attn_type="nsa", attn_impl="ref", **kw).cuda()
+    ours = M.NSATransformerB200(**kw).cuda()
+    missing = ours.load_state_dict(ref.state_dict(), strict=True)
+    assert not missing.missing_keys and not missing.unexpected_keys
+    g = torch.Generator().manual_seed(3)
+    idx = torch.randint(0, 512, (2, 256), generator=g).cuda()
+    tgt = torch.randint(0, 512, (2, 256), generator=g).cuda()
+    grads = []
+    for m in (ref, ours):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            _, loss = m(idx, tgt)
+        m.zero_grad(set_to_none=True)
+        loss.backward()
+        grads.append((float(loss.detach()), {n: p.grad.float() for n, p in m.named_parameters() if p.grad is not None}))
+    (lr_, gr), (lo, go) = grads
+    assert abs(lr_ - lo) <= 5e-2, (lr_, lo)
+    assert set(gr) == set(go)
+    worst = max(((gr[n] - go[n]).abs().max().item(), n) for n in gr)
+    assert worst[0] <= 8e-2, worst
+    # and in relative L2 over all parameters, which the reference's gate does not ask for
+    num = sum(((gr[n] - go[n]) ** 2).sum().item() for n in gr) ** 0.5
+    den = sum((gr[n] ** 2).sum().item() for n in gr) ** 0.5
+    assert num <= 5e-2 * den, (num, den)
+    print(f"model vs reference: loss {lr_:.5f} / {lo:.5f}, worst gradient max-abs {worst[0]:.2e} ({worst[1]}), rel-L2 {num / den:.2e}")
