@@ -215,10 +215,12 @@ def test_wait_that_runs_out_gives_up_and_leaves_the_context_usable():
         torch.cuda.synchronize()                       # returns: the waits are bounded
     finally:
         nsa.set_option("debug_starve_load", 0)
-    status = lib.nsa_device_status(None)               # reads and clears
+    assert lib.nsa_device_status(None) == -5           # NSA_ERR_DEVICE_WAIT; reads and clears
+    msg = lib.nsa_last_error().decode()
+    status = int(msg[msg.index("0x"):].rstrip(")"), 16)
     # the V-tile wait (16) starves; the waits behind it (S ready 4, O ready 8) start at the same
     # moment in other threads and may be the first to reach the limit
-    assert status != 0 and (status & ~(4 | 8 | 16)) == 0, f"status word {status:#x}"
+    assert status != 0 and (status & ~(4 | 8 | 16)) == 0, msg
     assert lib.nsa_device_status(None) == 0
     # queries 0..63 see one key tile only: their CTAs finished before anything ran out
     assert torch.equal(o[:, :, :64], o_ok[:, :, :64]) and torch.equal(lse[:, :, :64], lse_ok[:, :, :64])
