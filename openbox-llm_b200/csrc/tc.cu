@@ -50,14 +50,25 @@ __host__ __device__ inline size_t fwd_smem_bytes(int D, int nb_sel, int nw, int 
   return fixed + extra + 1024 /*alignment slack*/;
 }
 
+// 192 threads in roles.  Warps 0-3 (thread = row = TMEM lane) own the softmax; warp 4 sends the
+// TMA loads; warp 5 issues the MMAs.  With the issuing on a softmax warp, as an earlier version
+// had it, every tile waited for that warp to get its TMA boxes and a dozen MMAs out between its
+// own exponentials.  The Q tile is copied into tensor memory once per CTA, so S = Q K^T takes its
+// A operand from there (an MMA of 128 x 64 x 16 that fetches both operands from shared memory is
+// bound by that fetch, not by its arithmetic).  Two CTAs per SM.
+constexpr int kFwdThreads = 192;
+constexpr int kFwdSoftmax = 128;
+
 template <int D>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(kFwdThreads, 2)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const FwdArgs p) {
   using L = FwdSmem<D>;
   constexpr int kSlabs = L::kSlabs;
   constexpr uint32_t kTmemCols = 256;
-  constexpr uint32_t kColO = 0, kColS = 128, kColP = 192;
+  // O in columns 0-127, S in 128-191 (P, bf16, is written over its first 32 columns by the thread
+  // that read the row), the Q tile (bf16, D / 2 columns) in 192-255
+  constexpr uint32_t kColO = 0, kColS = 128, kColQ = 192;
   constexpr uint32_t kIdescQK = idesc_bf16(128, kKeys, 0, 0);
   constexpr uint32_t kIdescPV = idesc_bf16(128, D, 0, 1);
 
@@ -67,13 +78,17 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint8_t* sK = sQ + L::kQBytes;
   uint8_t* sV = sK + 2 * L::kKVBytes;
   uint64_t* bars = (uint64_t*)(sV + 2 * L::kKVBytes);
-  uint64_t* bar_q = bars + 0;
-  uint64_t* bar_k = bars + 1;   // [2]
-  uint64_t* bar_v = bars + 3;   // [2]
-  uint64_t* bar_s = bars + 5;
-  uint64_t* bar_o = bars + 6;
-  uint64_t* bar_drain = bars + 7;   // an aborted CTA waits here for its last MMAs
-  uint32_t* s_tmem = (uint32_t*)(bars + 8);
+  uint64_t* bar_q = bars + 0;        // Q tile landed (TMA bytes)
+  uint64_t* bar_k = bars + 1;        // [2] K stage landed
+  uint64_t* bar_v = bars + 3;        // [2] V stage landed
+  uint64_t* k_free = bars + 5;       // [2] the S MMA that read the stage is done
+  uint64_t* v_free = bars + 7;       // [2] the PV MMA that read the stage is done
+  uint64_t* bar_s = bars + 9;        // S of a tile is in tensor memory
+  uint64_t* bar_p = bars + 10;       // the 128 rows of P are written (and S is read)
+  uint64_t* bar_o = bars + 11;       // PV of a tile is done
+  uint64_t* bar_qt = bars + 12;      // the 128 rows of Q are in tensor memory
+  uint64_t* bar_drain = bars + 13;   // an aborted CTA waits here for its last MMAs
+  uint32_t* s_tmem = (uint32_t*)(bars + 14);
   volatile int* s_abort = (volatile int*)(s_tmem + 1);
   int* s_ntiles = (int*)(s_tmem + 2);
   int* s_scan = (int*)(s_tmem + 4);                 // [129]
@@ -83,24 +98,27 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (p.kind == 2 && p.stats != nullptr &&
       prefer_pairs(p.stats, p.offsets, p.B * p.Hkv, p.nb_sel, p.nq, p.force))
     return;   // the block-outer variant serves this call: leave before anything is set up
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qtile = p.n_qtiles - 1 - (int)blockIdx.x;   // long rows first
   const int bh = blockIdx.y;
   const int b = bh / p.Hkv, hkv = bh % p.Hkv;
   const int t0 = qtile * p.nq;
   const int t_last = min(p.T - 1, t0 + p.nq - 1);
-  const int g = tid / p.nq, ql = tid % p.nq;
+  // softmax threads: row of the tile = thread index
+  const int row = tid & (kFwdSoftmax - 1);
+  const int g = row / p.nq, ql = row % p.nq;
   const int t = t0 + ql;
-  const bool row_ok = (g < p.G) && (t < p.T);
+  const bool row_ok = tid < kFwdSoftmax && (g < p.G) && (t < p.T);
   const int head = hkv * p.G + g;
 
   if (tid == 0) {
     *s_abort = (*(volatile int*)p.status != 0) ? 1 : 0;
     mbar_init(bar_q, 1);
-    mbar_init(bar_k + 0, 1); mbar_init(bar_k + 1, 1);
-    mbar_init(bar_v + 0, 1); mbar_init(bar_v + 1, 1);
+    for (int k = 1; k <= 8; ++k) mbar_init(bars + k, 1);
     mbar_init(bar_s, 1);
+    mbar_init(bar_p, kFwdSoftmax);
     mbar_init(bar_o, 1);
+    mbar_init(bar_qt, kFwdSoftmax);
     mbar_init(bar_drain, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
@@ -118,26 +136,26 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     n_tiles = hi_last < 0 ? 0 : hi_last / kKeys + 1;
   } else {
     const int nmem = p.nb_sel * p.nw;
-    for (int i = tid; i < nmem; i += 128) s_member[i] = 0u;
+    for (int i = tid; i < nmem; i += kFwdThreads) s_member[i] = 0u;
     __syncthreads();
     const int32_t* idx = p.block_idx + ((size_t)bh * p.T + t0) * p.S;
     const int n_entries = (t_last - t0 + 1) * p.S;
-    for (int e = tid; e < n_entries; e += 128) {
+    for (int e = tid; e < n_entries; e += kFwdThreads) {
       const int q_local = e / p.S;
       const int blk = __ldg(idx + e);
       if (blk >= 0 && blk < p.nb_sel && blk * kKeys <= t0 + q_local)
         atomicOr(&s_member[blk * p.nw + (q_local >> 5)], 1u << (q_local & 31));
     }
     __syncthreads();
-    const int per = (p.nb_sel + 127) / 128;
-    const int j0 = tid * per, j1 = min(p.nb_sel, j0 + per);
+    const int per = (p.nb_sel + 127) / 128;       // the first 128 threads scan `per` blocks each
+    const int j0 = tid < 128 ? tid * per : p.nb_sel, j1 = min(p.nb_sel, j0 + per);
     int cnt = 0;
     for (int j = j0; j < j1; ++j) {
       uint32_t any = 0;
       for (int w = 0; w < p.nw; ++w) any |= s_member[j * p.nw + w];
       cnt += any != 0;
     }
-    s_scan[tid + 1] = cnt;
+    if (tid < 128) s_scan[tid + 1] = cnt;
     __syncthreads();
     if (tid == 0) {
       s_scan[0] = 0;
@@ -145,7 +163,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       *s_ntiles = s_scan[128];
     }
     __syncthreads();
-    int pos = s_scan[tid];
+    int pos = tid < 128 ? s_scan[tid] : 0;
     for (int j = j0; j < j1; ++j) {
       uint32_t any = 0;
       for (int w = 0; w < p.nw; ++w) any |= s_member[j * p.nw + w];
@@ -156,67 +174,53 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
 
   float m_used = -INFINITY, l_sum = 0.f;
-  uint32_t tmem = 0;
-  bool aborted = false;
-  // thread 0: K / V tiles whose load was issued, and whose arrival was seen (the rest is what an
-  // aborted CTA still has to wait for)
-  int k_loaded = 0, k_seen = 0, v_loaded = 0, v_seen = 0;
-  bool q_seen = false;
-
-  if (n_tiles > 0) {
-    // ---- TMEM ---------------------------------------------------------------------------
-    if (warp == 0) {
-      tmem_alloc(s_tmem, kTmemCols);
-      tmem_relinquish();
+  __nv_bfloat16* orow = p.o + ((size_t)(b * p.Hq + head) * p.T + t) * D;
+  if (n_tiles == 0) {                       // (uniform over the CTA) rows without a key: zeros
+    if (row_ok) {
+      uint4* dst = reinterpret_cast<uint4*>(orow);
+#pragma unroll
+      for (int v4 = 0; v4 < D / 8; ++v4) dst[v4] = make_uint4(0, 0, 0, 0);
+      p.lse[(size_t)(b * p.Hq + head) * p.T + t] = kLseEmpty;
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    tmem = *s_tmem;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    return;
+  }
 
-    auto key0_of = [&](int i) -> int {
-      if (p.kind == 2) return (int)s_tiles[i] * kKeys;
-      return first_key + i * kKeys;
-    };
-    auto load_k = [&](int i) {
-      uint64_t* bar = bar_k + (i & 1);
-      mbar_expect_tx(bar, L::kKVBytes);
-#pragma unroll
-      for (int s = 0; s < kSlabs; ++s)
-        tma_load_3d(sK + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_k, bar, s * 64, key0_of(i), bh);
-      k_loaded = i + 1;
-    };
-    auto load_v = [&](int i) {
-      uint64_t* bar = bar_v + (i & 1);
-      if (p.debug_starve && i == 1) return;   // test only: this tile's wait has to run out
-      mbar_expect_tx(bar, L::kKVBytes);
-#pragma unroll
-      for (int s = 0; s < kSlabs; ++s)
-        tma_load_3d(sV + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_v, bar, s * 64, key0_of(i), bh);
-      v_loaded = i + 1;
-    };
-    auto issue_s = [&](int i) {   // S = Q K^T for tile i
-      const uint32_t qa = desc_lo_kmajor(smem_u32(sQ));
-      const uint32_t ka = desc_lo_kmajor(smem_u32(sK + (i & 1) * L::kKVBytes));
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
-        mma_ss(tmem + kColS, desc_at(qa, slab * (kRows * 128) + in),
-               desc_at(ka, slab * (kKeys * 128) + in), kIdescQK, kk > 0);
-      }
-      tc_commit(bar_s);
-    };
-    auto issue_pv = [&](int i) {  // O (+)= P V for tile i
-      const uint32_t va = desc_lo_mnmajor(smem_u32(sV + (i & 1) * L::kKVBytes), kKeys * 128);
-#pragma unroll
-      for (int kk = 0; kk < kKeys / 16; ++kk)
-        mma_ts(tmem + kColO, tmem + kColP + kk * 8, desc_at(va, kk * 2048), kIdescPV,
-               (i > 0) || (kk > 0));
-      tc_commit(bar_o);
-    };
+  // ---- TMEM ---------------------------------------------------------------------------
+  if (warp == 0) {
+    tmem_alloc(s_tmem, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+  auto key0_of = [&](int i) -> int {
+    if (p.kind == 2) return (int)s_tiles[i] * kKeys;
+    return first_key + i * kKeys;
+  };
+  int last_k[2] = {-1, -1}, last_v[2] = {-1, -1};   // producer: last tile sent into each stage
 
-    if (tid == 0) {
+  if (warp == 4) {
+    // ---- producer -------------------------------------------------------------------------
+    if (lane == 0) {
+      auto load_k = [&](int i) {
+        uint64_t* bar = bar_k + (i & 1);
+        mbar_expect_tx(bar, L::kKVBytes);
+#pragma unroll
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(sK + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_k, bar, s * 64, key0_of(i), bh);
+        last_k[i & 1] = i;
+      };
+      auto load_v = [&](int i) {
+        uint64_t* bar = bar_v + (i & 1);
+        if (p.debug_starve && i == 1) return;   // test only: this tile's wait has to run out
+        mbar_expect_tx(bar, L::kKVBytes);
+#pragma unroll
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(sV + (i & 1) * L::kKVBytes + s * (kKeys * 128), &tm_v, bar, s * 64, key0_of(i), bh);
+        last_v[i & 1] = i;
+      };
       mbar_expect_tx(bar_q, L::kQBytes);
 #pragma unroll
       for (int s = 0; s < kSlabs; ++s)
@@ -224,19 +228,83 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       load_k(0);
       load_v(0);
       if (n_tiles > 1) { load_k(1); load_v(1); }
-      q_seen = mbar_wait(bar_q, 0, p.status, s_abort, 1);
-      if (mbar_wait(bar_k, 0, p.status, s_abort, 2)) k_seen = 1;
-      tc_fence_after();
-      if (!*s_abort) issue_s(0);
+      for (int i = 0; i + 2 < n_tiles; ++i) {
+        // stage i & 1 is free once the MMAs of tile i that read it are done (a barrier per stage:
+        // its next completion needs the very load that waits here, so no phase can be missed)
+        if (!mbar_wait(k_free + (i & 1), (i >> 1) & 1, p.status, s_abort, 0x4000)) break;
+        load_k(i + 2);
+        if (!mbar_wait(v_free + (i & 1), (i >> 1) & 1, p.status, s_abort, 0x4000)) break;
+        load_v(i + 2);
+      }
     }
-
+  } else if (warp == 5) {
+    // ---- MMA issuer ------------------------------------------------------------------------
+    if (lane == 0) {
+      auto issue_s = [&](int i) {   // S = Q K^T for tile i, Q from tensor memory
+        const uint32_t ka = desc_lo_kmajor(smem_u32(sK + (i & 1) * L::kKVBytes));
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t slab = kk >> 2, in = (kk & 3) * 32;
+          mma_ts(tmem + kColS, tmem + kColQ + kk * 8, desc_at(ka, slab * (kKeys * 128) + in), kIdescQK, kk > 0);
+        }
+        tc_commit(bar_s);
+        tc_commit(k_free + (i & 1));
+      };
+      auto issue_pv = [&](int i) {  // O (+)= P V for tile i
+        const uint32_t va = desc_lo_mnmajor(smem_u32(sV + (i & 1) * L::kKVBytes), kKeys * 128);
+#pragma unroll
+        for (int kk = 0; kk < kKeys / 16; ++kk)
+          mma_ts(tmem + kColO, tmem + kColS + kk * 8, desc_at(va, kk * 2048), kIdescPV, (i > 0) || (kk > 0));
+        tc_commit(bar_o);
+        tc_commit(v_free + (i & 1));
+      };
+      bool ok = mbar_wait(bar_qt, 0, p.status, s_abort, 0x8000) &&
+                mbar_wait(bar_k, 0, p.status, s_abort, 2);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int i = 0; ok && i < n_tiles; ++i) {
+        ok = mbar_wait(bar_p, i & 1, p.status, s_abort, 0x2000) &&
+             mbar_wait(bar_v + (i & 1), (i >> 1) & 1, p.status, s_abort, 16);
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv(i);
+        if (i + 1 < n_tiles) {
+          // S of the next tile overwrites P of this one: the tensor pipe keeps the order
+          ok = mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2);
+          if (ok) issue_s(i + 1);
+        }
+      }
+      // the tensor pipe is idle before tensor memory is read for the output and given back
+      tc_commit(bar_drain);
+      if (!mbar_wait(bar_drain, 0, p.status, s_abort, 0x1000)) mbar_wait_drain(bar_drain, 0);
+    }
+  } else {
+    // ---- softmax: thread = row ---------------------------------------------------------------
+    // Q: shared memory -> tensor memory, every thread its row
+    bool ok = mbar_wait(bar_q, 0, p.status, s_abort, 1);
+    {
+#pragma unroll
+      for (int sl = 0; sl < kSlabs; ++sl) {
+        const uint8_t* src = sQ + sl * (kRows * 128) + row * 128;
+        uint32_t qv[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 u = *reinterpret_cast<const uint4*>(src + ((c ^ (row & 7)) << 4));
+          qv[4 * c + 0] = u.x; qv[4 * c + 1] = u.y; qv[4 * c + 2] = u.z; qv[4 * c + 3] = u.w;
+        }
+        tmem_st32(lane_base + kColQ + sl * 32, qv);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_qt);
+    }
     for (int i = 0; i < n_tiles; ++i) {
       const int key0 = key0_of(i);
-      mbar_wait(bar_s, i & 1, p.status, s_abort, 4);
+      ok = mbar_wait(bar_s, i & 1, p.status, s_abort, 4) && ok;
+      if (!__all_sync(0xffffffffu, ok)) break;              // the whole warp leaves together
       tc_fence_after();
-      if (tid == 0 && i + 2 < n_tiles && !*s_abort) load_k(i + 2);   // the K stage of tile i is free again
-      __syncwarp();
-
       uint32_t r[64];
       tmem_ld32(lane_base + kColS, r);
       tmem_ld32(lane_base + kColS + 32, r + 32);
@@ -291,70 +359,55 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       l_sum += psum;
 
-      if (i > 0) {                            // P and O are free once PV of tile i-1 is done
-        mbar_wait(bar_o, (i - 1) & 1, p.status, s_abort, 8);
+      // O may be touched once PV of tile i-1 is done; only a warp that has to rescale waits for it
+      if (i > 0 && __any_sync(0xffffffffu, rescale)) {
+        ok = mbar_wait(bar_o, (i - 1) & 1, p.status, s_abort, 8);
+        if (!__all_sync(0xffffffffu, ok)) break;
         tc_fence_after();
-        if (tid == 0 && i + 1 < n_tiles && i + 1 >= 2 && !*s_abort) load_v(i + 1);
-        __syncwarp();
-        if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t o32[32];
-            tmem_ld32(lane_base + kColO + cc * 32, o32);
-            tmem_wait_ld();
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t o32[32];
+          tmem_ld32(lane_base + kColO + cc * 32, o32);
+          tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o32[c] = __float_as_uint(__uint_as_float(o32[c]) * alpha);
-            tmem_st32(lane_base + kColO + cc * 32, o32);
-          }
+          for (int c = 0; c < 32; ++c) o32[c] = __float_as_uint(__uint_as_float(o32[c]) * alpha);
+          tmem_st32(lane_base + kColO + cc * 32, o32);
         }
       }
-      __syncwarp();
-      tmem_st32(lane_base + kColP, pk);
+      tmem_st32(lane_base + kColS, pk);        // over the S columns this thread has just read
       tmem_wait_st();
       tc_fence_before();
-      // one decision for the whole CTA: after a given-up wait nothing more is issued
-      if (__syncthreads_or(*s_abort)) { aborted = true; break; }
-      if (tid == 0) {
-        tc_fence_after();
-        if (mbar_wait(bar_v + (i & 1), (i >> 1) & 1, p.status, s_abort, 16)) {
-          v_seen = i + 1;
-          issue_pv(i);
-          if (i + 1 < n_tiles && mbar_wait(bar_k + ((i + 1) & 1), ((i + 1) >> 1) & 1, p.status, s_abort, 2)) {
-            k_seen = i + 2;
-            issue_s(i + 1);
-          }
-        }
+      mbar_arrive(bar_p);
+    }
+    // the last PV
+    if (__all_sync(0xffffffffu, ok)) mbar_wait(bar_o, (n_tiles - 1) & 1, p.status, s_abort, 8);
+  }
+
+  // ---- teardown -------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*s_abort) {
+    // Give-up path: no output is written.  The producer waits (bounded) for the loads still on
+    // their way into this CTA's shared memory; the MMA thread has waited for the tensor pipe
+    // above; then the tensor memory goes back.
+    if (warp == 4 && lane == 0) {
+      mbar_wait_drain(bar_q, 0);
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+        if (last_k[st] >= 0) mbar_wait_drain(bar_k + st, (last_k[st] >> 1) & 1);
+        if (last_v[st] >= 0) mbar_wait_drain(bar_v + st, (last_v[st] >> 1) & 1);
       }
     }
-    if (!aborted) {
-      mbar_wait(bar_o, (n_tiles - 1) & 1, p.status, s_abort, 8);
-      tc_fence_after();
-      aborted = __syncthreads_or(*s_abort) != 0;
-    }
-    if (aborted) {
-      // Give-up path: no output is written.  Thread 0 waits (bounded) for the loads that are still
-      // on their way into this CTA's shared memory and for the MMAs already issued, then the
-      // tensor memory goes back.
-      if (tid == 0) {
-        if (!q_seen) mbar_wait_drain(bar_q, 0);
-        for (int j = k_seen; j < k_loaded; ++j) mbar_wait_drain(bar_k + (j & 1), (j >> 1) & 1);
-        for (int j = v_seen; j < v_loaded; ++j) mbar_wait_drain(bar_v + (j & 1), (j >> 1) & 1);
-        tc_commit(bar_drain);
-        mbar_wait_drain(bar_drain, 0);
-      }
-      tc_fence_before();
-      __syncthreads();
-      if (warp == 0) tmem_dealloc(tmem, kTmemCols);
-      return;
-    }
-    __syncwarp();
+    if (warp == 5 && lane == 0) mbar_wait_drain(bar_drain, 0);
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+    return;
   }
 
   // ---- epilogue ---------------------------------------------------------------------------
-  const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-  __nv_bfloat16* orow = p.o + ((size_t)(b * p.Hq + head) * p.T + t) * D;
-  if (n_tiles > 0) {
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  if (tid < kFwdSoftmax) {
+    const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
 #pragma unroll
     for (int cc = 0; cc < D / 32; ++cc) {
       uint32_t o32[32];
@@ -373,17 +426,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
     }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
-  } else if (row_ok) {
-    uint4* dst = reinterpret_cast<uint4*>(orow);
-#pragma unroll
-    for (int v4 = 0; v4 < D / 8; ++v4) dst[v4] = make_uint4(0, 0, 0, 0);
+    if (row_ok)
+      p.lse[(size_t)(b * p.Hq + head) * p.T + t] =
+          l_sum > 0.f ? (m_used + log2f(l_sum)) * kLn2 : kLseEmpty;
   }
-  if (row_ok)
-    p.lse[(size_t)(b * p.Hq + head) * p.T + t] =
-        l_sum > 0.f ? (m_used + log2f(l_sum)) * kLn2 : kLseEmpty;
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
 static const char* const kFwdNames[3] = {"tc_fwd_win", "tc_fwd_cmp", "tc_fwd_slc"};
@@ -435,10 +484,10 @@ static int launch_fwd(const AttnArgs& a, const unsigned long long* stats, const 
   dim3 grid(p.n_qtiles, a.B * a.Hkv);
   if (a.D == 128) {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks(branch_name(kFwdNames, a.kind), st); tc_fwd_kernel<128><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p); }
+    { KernelScope ks(branch_name(kFwdNames, a.kind), st); tc_fwd_kernel<128><<<grid, kFwdThreads, smem, st>>>(tm_q, tm_k, tm_v, p); }
   } else {
     NSA_CUDA_OK(cudaFuncSetAttribute(tc_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    { KernelScope ks(branch_name(kFwdNames, a.kind), st); tc_fwd_kernel<64><<<grid, 128, smem, st>>>(tm_q, tm_k, tm_v, p); }
+    { KernelScope ks(branch_name(kFwdNames, a.kind), st); tc_fwd_kernel<64><<<grid, kFwdThreads, smem, st>>>(tm_q, tm_k, tm_v, p); }
   }
   NSA_LAUNCH_OK("tc_fwd_kernel");
   return NSA_OK;

@@ -449,6 +449,12 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         carry = __shfl_sync(0xffffffffu, v[PER - 1], (threadIdx.x & 31 & ~(GP - 1)) + GP - 1);
       }
       float* out = (p.imp_out && t < p.T) ? p.imp_out + ((size_t)bh * p.T + t) * p.imp_cols : nullptr;
+      // A candidate below entry 16 / GP (counted from 1) of every one of the query's GP lists has
+      // at least 16 entries ahead of it, so it cannot reach the merged top 16 and need not enter a
+      // list; the bound only rises while the tile is scanned.
+      float tau = lv[kList / GP - 1];
+#pragma unroll
+      for (int o = 1; o < GP; o <<= 1) tau = fminf(tau, __shfl_xor_sync(0xffffffffu, tau, o));
       float accb = 0.f;
 #pragma unroll
       for (int k = 0; k < PER; ++k) {
@@ -463,7 +469,7 @@ tc_score_lanes_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (cj < p.n_init) cv = kForcedInit - (float)cj;
           else if (cj > my_cur - p.n_local) cv = kForcedLocal - (float)(my_cur - cj);
         }
-        if (cv > lv[kList - 1]) {              // beats the list's last entry (empty slots hold -1)
+        if (cv > lv[kList - 1] && cv >= tau) {   // beats the list's last entry (empty slots hold -1)
 #pragma unroll
           for (int r = kList - 1; r >= 1; --r) {   // strict '>' keeps earlier (lower) indices ahead
             const bool up = cv > lv[r - 1];
