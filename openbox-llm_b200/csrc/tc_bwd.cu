@@ -1155,44 +1155,62 @@ struct Reduce3Args {
   int B, Hq, Hkv, T, G;
 };
 
-template <int D>
+// One thread adds up 8 columns of a query's dQ for HG heads (g, g + G / HG, ...): the heads of a
+// query share the partial rows, so their index loads and address arithmetic are paid once.  The
+// kernel moves 32 GB at the benchmark shape and was held back by its instruction count, not by
+// memory, when every thread served a single head.
+template <int D, int HG>
 __global__ void dq_reduce3_kernel(const Reduce3Args a) {
   constexpr int kVec = D / 8;
+  const int Gp = a.G / HG;                               // head groups per query
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const size_t total = (size_t)a.B * a.Hkv * a.T * a.G * kVec;
+  const size_t total = (size_t)a.B * a.Hkv * a.T * Gp * kVec;
   if (gid >= total) return;
   const int v = (int)(gid % kVec);
-  const int g = (int)((gid / kVec) % a.G);
-  const int t = (int)((gid / ((size_t)kVec * a.G)) % a.T);
-  const size_t bh = gid / ((size_t)kVec * a.G * a.T);
-  float acc[8];
+  const int g = (int)((gid / kVec) % Gp);
+  const int t = (int)((gid / ((size_t)kVec * Gp)) % a.T);
+  const size_t bh = gid / ((size_t)kVec * Gp * a.T);
+  float acc[HG][8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int h = 0; h < HG; ++h)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+  const size_t row_elems = (size_t)a.G * D;              // elements of one partial row (all heads)
+  const size_t in_row = (size_t)g * D + v * 8;           // this thread's first head inside a row
+  const size_t head_step = (size_t)Gp * D;               // to its next head
   // eight partial rows per trip: their loads are issued before the first is added
   constexpr int kTrip = 8;
   auto add_rows = [&](const __nv_bfloat16* part, const long long (&rows)[kTrip]) {
-    uint4 u[kTrip];
-#pragma unroll
-    for (int k = 0; k < kTrip; ++k)
-      u[k] = rows[k] >= 0 ? __ldg(reinterpret_cast<const uint4*>(part + ((size_t)rows[k] * a.G + g) * D + v * 8))
-                          : make_uint4(0u, 0u, 0u, 0u);
+    uint4 u[kTrip][HG];
 #pragma unroll
     for (int k = 0; k < kTrip; ++k) {
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[k]);
+      const __nv_bfloat16* src = part + (size_t)(rows[k] >= 0 ? rows[k] : 0) * row_elems + in_row;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h[e]);
-        acc[2 * e] += f.x;
-        acc[2 * e + 1] += f.y;
-      }
+      for (int h = 0; h < HG; ++h)
+        u[k][h] = rows[k] >= 0 ? __ldg(reinterpret_cast<const uint4*>(src + h * head_step))
+                               : make_uint4(0u, 0u, 0u, 0u);
     }
+#pragma unroll
+    for (int k = 0; k < kTrip; ++k)
+#pragma unroll
+      for (int h = 0; h < HG; ++h) {
+        const uint32_t w[4] = {u[k][h].x, u[k][h].y, u[k][h].z, u[k][h].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {                    // bf16 -> fp32 is a shift
+          acc[h][2 * e] += __uint_as_float(w[e] << 16);
+          acc[h][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
   };
   const long long qrow = (long long)(bh * a.T + t);
   if (a.acc) {
-    const float4* src = reinterpret_cast<const float4*>(a.acc + ((size_t)qrow * a.G + g) * D + v * 8);
-    const float4 lo = __ldg(src), hi = __ldg(src + 1);
-    acc[0] = lo.x; acc[1] = lo.y; acc[2] = lo.z; acc[3] = lo.w;
-    acc[4] = hi.x; acc[5] = hi.y; acc[6] = hi.z; acc[7] = hi.w;
+#pragma unroll
+    for (int h = 0; h < HG; ++h) {
+      const float4* src = reinterpret_cast<const float4*>(a.acc + (size_t)qrow * row_elems + in_row + h * head_step);
+      const float4 lo = __ldg(src), hi = __ldg(src + 1);
+      acc[h][0] = lo.x; acc[h][1] = lo.y; acc[h][2] = lo.z; acc[h][3] = lo.w;
+      acc[h][4] = hi.x; acc[h][5] = hi.y; acc[h][6] = hi.z; acc[h][7] = hi.w;
+    }
   }
   if (a.part_slc) {
     const int32_t* ps = a.pair_of_slot + (size_t)qrow * a.S;
@@ -1223,10 +1241,13 @@ __global__ void dq_reduce3_kernel(const Reduce3Args a) {
     }
   }
   const int b = (int)(bh / a.Hkv), hkv = (int)(bh % a.Hkv);
-  uint4 u;
-  u.x = pack_bf16(acc[0], acc[1]); u.y = pack_bf16(acc[2], acc[3]);
-  u.z = pack_bf16(acc[4], acc[5]); u.w = pack_bf16(acc[6], acc[7]);
-  *reinterpret_cast<uint4*>(a.dq + (((size_t)b * a.Hq + hkv * a.G + g) * a.T + t) * D + v * 8) = u;
+#pragma unroll
+  for (int h = 0; h < HG; ++h) {
+    uint4 u;
+    u.x = pack_bf16(acc[h][0], acc[h][1]); u.y = pack_bf16(acc[h][2], acc[h][3]);
+    u.z = pack_bf16(acc[h][4], acc[h][5]); u.w = pack_bf16(acc[h][6], acc[h][7]);
+    *reinterpret_cast<uint4*>(a.dq + (((size_t)b * a.Hq + hkv * a.G + g + h * Gp) * a.T + t) * D + v * 8) = u;
+  }
 }
 
 // Selection blocks whose row tiles were split over several work items collect dK / dV in the fp32
@@ -1491,12 +1512,18 @@ int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int cmp_len, int cmp_stride,
     r.part_win = (const __nv_bfloat16*)((const char*)ws_win + pl.off_part);
     r.slots_win = pl.n_slots;
   }
-  const size_t nthreads = (size_t)r.B * r.Hkv * r.T * r.G * (base.D / 8);
+  const int hg = r.G % 2 == 0 ? 2 : 1;                    // heads of a query served by one thread
+  const size_t nthreads = (size_t)r.B * r.Hkv * r.T * (r.G / hg) * (base.D / 8);
   if (nthreads == 0) return NSA_OK;
   const unsigned grid = (unsigned)((nthreads + 255) / 256);
   KernelScope ks("dq_reduce3", st);
-  if (base.D == 128) dq_reduce3_kernel<128><<<grid, 256, 0, st>>>(r);
-  else dq_reduce3_kernel<64><<<grid, 256, 0, st>>>(r);
+  if (base.D == 128) {
+    if (hg == 2) dq_reduce3_kernel<128, 2><<<grid, 256, 0, st>>>(r);
+    else dq_reduce3_kernel<128, 1><<<grid, 256, 0, st>>>(r);
+  } else {
+    if (hg == 2) dq_reduce3_kernel<64, 2><<<grid, 256, 0, st>>>(r);
+    else dq_reduce3_kernel<64, 1><<<grid, 256, 0, st>>>(r);
+  }
   NSA_LAUNCH_OK("dq_reduce3_kernel");
   return NSA_OK;
 }

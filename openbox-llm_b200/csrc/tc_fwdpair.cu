@@ -51,8 +51,9 @@ __global__ void sel_combine_kernel(const __nv_bfloat16* __restrict__ o_part, con
       m[j] = -INFINITY; l[j] = 0.f; u[j] = make_uint4(0u, 0u, 0u, 0u);
       if (pr[j] >= 0) {
         const size_t prow = (size_t)pr[j] * G + g;
-        m[j] = __ldg(ml + prow * 3);
-        l[j] = __ldg(ml + prow * 3 + 1) + __ldg(ml + prow * 3 + 2);
+        const float2 st = __ldg(reinterpret_cast<const float2*>(ml + prow * 2));
+        m[j] = st.x;
+        l[j] = st.y;
         u[j] = __ldg(reinterpret_cast<const uint4*>(o_part + prow * D + v * 8));
       }
     }
@@ -66,12 +67,11 @@ __global__ void sel_combine_kernel(const __nv_bfloat16* __restrict__ o_part, con
     for (int j = 0; j < 4; ++j) {
       const float w = ex2(m[j] - Mn);                       // absent slot: 0
       L = fmaf(w, l[j], L);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[j]);
+      const uint32_t h[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h[e]);
-        acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
-        acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
+      for (int e = 0; e < 4; ++e) {                         // bf16 -> fp32 is a shift
+        acc[2 * e] = fmaf(w, __uint_as_float(h[e] << 16), acc[2 * e]);
+        acc[2 * e + 1] = fmaf(w, __uint_as_float(h[e] & 0xffff0000u), acc[2 * e + 1]);
       }
     }
     M = Mn;
@@ -192,7 +192,7 @@ static PairPlan plan_pairs(const AttnArgs& a) {
   size_t off = 0;
   pl.off_stats = off; off += 256;
   pl.off_part = off; off += align_up(pl.cap_pairs * G * a.D * 2, 256);
-  pl.off_ml = off; off += align_up(pl.cap_pairs * G * 3 * 4, 256);
+  pl.off_ml = off; off += align_up(pl.cap_pairs * G * 2 * 4, 256);
   pl.off_csr_ws = off; off += align_up(nsa_csr_workspace_bytes(a.B, a.Hkv, pl.n_ktiles * kKeys, a.S, kKeys), 256);
   pl.off_qob = off; off += align_up(pl.cap_pairs * 4, 256);
   pl.off_pbh = off; off += align_up(pl.cap_pairs * 4, 256);

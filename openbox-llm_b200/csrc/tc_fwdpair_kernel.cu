@@ -25,7 +25,7 @@ struct PairArgs {
   const int32_t* q_of_block;
   const int32_t* offsets;        // [B*Hkv, n_ktiles + 1]
   __nv_bfloat16* o_part;         // [pairs, G, D]
-  float* ml;                     // [pairs, G, 3]: m, sum of p, 0
+  float* ml;                     // [pairs, G, 2]: the row maximum m and the sum of p
   const unsigned long long* stats;
   const SelWorkHeader* work;     // n_items, then int4 items {bh, block, first row tile, chunks of the block}
   int* status;
@@ -292,9 +292,7 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       mbar_arrive(p_full + sb);
       if (t_cur >= 0) {
         const size_t prow = (size_t)(pair_base + (item.z + k) * p.nq + ql) * p.G + g;
-        p.ml[prow * 3] = mx;
-        p.ml[prow * 3 + 1] = lsum;
-        p.ml[prow * 3 + 2] = 0.f;
+        *reinterpret_cast<float2*>(p.ml + prow * 2) = make_float2(mx, lsum);
       }
       t_cur = t_nxt;
     }
