@@ -98,6 +98,26 @@ int nsa_selection_bwd(const void* q, const void* k, const void* v, const int32_t
                       const float* row_scale, const float* row_dot,
                       void* workspace, size_t workspace_bytes, int impl, void* stream);
 
+/* The tcgen05 selection kernels walk the block list block by block: CSR (nsa_fsa.py:14-64), the
+ * (query, slot) -> pair map and a work list, which nsa_selection_fwd and nsa_selection_bwd each
+ * build inside their workspace.  A caller that runs both on one block list (every training step)
+ * can build them once into a buffer of nsa_selection_plan_bytes bytes (0: shape not served by the
+ * tcgen05 kernels) and hand it to the *_planned forms, which copy it into place instead of
+ * building.  The reference builds its CSR once per forward and once per backward
+ * (nsa_selection_kernel.py:199-201, nsa_selection_backward.py:356-358); no counterpart for the
+ * reuse. */
+size_t nsa_selection_plan_bytes(const NsaDims* dims, int S, int block_size);
+int nsa_selection_plan_build(const int32_t* block_idx, const NsaDims* dims, int S, int block_size,
+                             void* plan, size_t plan_bytes, void* stream);
+int nsa_selection_fwd_planned(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                              void* o, float* lse, const NsaDims* dims, int S, int block_size,
+                              void* workspace, size_t workspace_bytes, const void* plan, void* stream);
+int nsa_selection_bwd_planned(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                              const void* o, const float* lse, const void* d_o,
+                              void* dq, void* dk, void* dv, const NsaDims* dims, int S, int block_size,
+                              const float* row_scale, const float* row_dot,
+                              void* workspace, size_t workspace_bytes, const void* plan, void* stream);
+
 /* dq of the whole op in one pass (no counterpart in the reference, which adds the three branch
  * gradients with torch).  When the tcgen05 kernels serve a backward call (nsa_tc_supported) its
  * `dq` argument may be NULL: the branch's bf16 dQ partials then stay in the call's workspace, and

@@ -45,6 +45,10 @@ SIGNATURES = {
     "nsa_selection_fwd": (_i, [_vp] * 6 + [_dp, _i, _i, _vp, _sz, _i, _vp]),
     "nsa_selection_bwd_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
     "nsa_selection_bwd": (_i, [_vp] * 10 + [_dp, _i, _i, _vp, _vp, _vp, _sz, _i, _vp]),
+    "nsa_selection_plan_bytes": (_sz, [_dp, _i, _i]),
+    "nsa_selection_plan_build": (_i, [_vp, _dp, _i, _i, _vp, _sz, _vp]),
+    "nsa_selection_fwd_planned": (_i, [_vp] * 6 + [_dp, _i, _i, _vp, _sz, _vp, _vp]),
+    "nsa_selection_bwd_planned": (_i, [_vp] * 10 + [_dp, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp]),
     "nsa_csr_workspace_bytes": (_sz, [_i] * 5),
     "nsa_build_block_to_query_csr": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "nsa_csr_builtin_scratch_bytes": (_sz, []),

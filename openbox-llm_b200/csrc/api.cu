@@ -355,10 +355,32 @@ static int check_sel(const NsaDims* dims, int S, int block_size) {
   return NSA_OK;
 }
 
+static int selection_fwd_impl(const void* q, const void* k, const void* v,
+                              const int32_t* block_idx, void* o, float* lse, const NsaDims* dims,
+                              int S, int block_size, void* workspace, size_t workspace_bytes,
+                              int impl, const void* plan, void* stream);
+
 extern "C" int nsa_selection_fwd(const void* q, const void* k, const void* v,
                                  const int32_t* block_idx, void* o, float* lse, const NsaDims* dims,
                                  int S, int block_size, void* workspace, size_t workspace_bytes,
                                  int impl, void* stream) {
+  return selection_fwd_impl(q, k, v, block_idx, o, lse, dims, S, block_size, workspace, workspace_bytes, impl,
+                            nullptr, stream);
+}
+
+extern "C" int nsa_selection_fwd_planned(const void* q, const void* k, const void* v,
+                                         const int32_t* block_idx, void* o, float* lse, const NsaDims* dims,
+                                         int S, int block_size, void* workspace, size_t workspace_bytes,
+                                         const void* plan, void* stream) {
+  NSA_CHECK_ARG(plan, "null plan");
+  return selection_fwd_impl(q, k, v, block_idx, o, lse, dims, S, block_size, workspace, workspace_bytes,
+                            NSA_IMPL_TC, plan, stream);
+}
+
+static int selection_fwd_impl(const void* q, const void* k, const void* v,
+                              const int32_t* block_idx, void* o, float* lse, const NsaDims* dims,
+                              int S, int block_size, void* workspace, size_t workspace_bytes,
+                              int impl, const void* plan, void* stream) {
   int rc = check_sel(dims, S, block_size);
   if (rc != NSA_OK) return rc;
   const size_t rows = (size_t)dims->B * dims->Hq * dims->T;
@@ -367,10 +389,31 @@ extern "C" int nsa_selection_fwd(const void* q, const void* k, const void* v,
   AttnArgs a = base_args(dims, dims->T);
   a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse; a.block_idx = block_idx;
   a.kind = 2; a.S = S; a.block_size = block_size;
+  a.sel_plan = plan;
   if (use_tc(dims, block_size, impl, &rc) && S > 0)
     return tc_sel_fwd(a, workspace, workspace_bytes, (cudaStream_t)stream);
   if (rc != NSA_OK) return rc;
   return simt_attn_fwd(a, dims->dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t nsa_selection_plan_bytes(const NsaDims* dims, int S, int block_size) {
+  if (check_sel(dims, S, block_size) != NSA_OK || S <= 0) return 0;
+  int rc;
+  if (!use_tc(dims, block_size, NSA_IMPL_AUTO, &rc)) return 0;
+  AttnArgs a = base_args(dims, dims->T);
+  a.kind = 2; a.S = S; a.block_size = block_size;
+  return tc_sel_plan_bytes(a);
+}
+
+extern "C" int nsa_selection_plan_build(const int32_t* block_idx, const NsaDims* dims, int S, int block_size,
+                                        void* plan, size_t plan_bytes, void* stream) {
+  int rc = check_sel(dims, S, block_size);
+  if (rc != NSA_OK) return rc;
+  NSA_CHECK_ARG(S > 0 && block_idx && plan, "null block_idx or plan");
+  NSA_CHECK_ARG(use_tc(dims, block_size, NSA_IMPL_AUTO, &rc), "a selection plan needs a shape the tcgen05 kernels serve");
+  AttnArgs a = base_args(dims, dims->T);
+  a.block_idx = block_idx; a.kind = 2; a.S = S; a.block_size = block_size;
+  return tc_sel_plan_build(a, plan, plan_bytes, (cudaStream_t)stream);
 }
 
 extern "C" size_t nsa_selection_bwd_workspace_bytes(const NsaDims* dims, int S, int block_size,
@@ -386,11 +429,36 @@ extern "C" size_t nsa_selection_bwd_workspace_bytes(const NsaDims* dims, int S, 
   return need;
 }
 
+static int selection_bwd_impl(const void* q, const void* k, const void* v,
+                              const int32_t* block_idx, const void* o, const float* lse,
+                              const void* d_o, void* dq, void* dk, void* dv, const NsaDims* dims,
+                              int S, int block_size, const float* row_scale, const float* row_dot,
+                              void* workspace, size_t workspace_bytes, int impl, const void* plan, void* stream);
+
 extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
                                  const int32_t* block_idx, const void* o, const float* lse,
                                  const void* d_o, void* dq, void* dk, void* dv, const NsaDims* dims,
                                  int S, int block_size, const float* row_scale, const float* row_dot,
                                  void* workspace, size_t workspace_bytes, int impl, void* stream) {
+  return selection_bwd_impl(q, k, v, block_idx, o, lse, d_o, dq, dk, dv, dims, S, block_size, row_scale, row_dot,
+                            workspace, workspace_bytes, impl, nullptr, stream);
+}
+
+extern "C" int nsa_selection_bwd_planned(const void* q, const void* k, const void* v,
+                                         const int32_t* block_idx, const void* o, const float* lse,
+                                         const void* d_o, void* dq, void* dk, void* dv, const NsaDims* dims,
+                                         int S, int block_size, const float* row_scale, const float* row_dot,
+                                         void* workspace, size_t workspace_bytes, const void* plan, void* stream) {
+  NSA_CHECK_ARG(plan, "null plan");
+  return selection_bwd_impl(q, k, v, block_idx, o, lse, d_o, dq, dk, dv, dims, S, block_size, row_scale, row_dot,
+                            workspace, workspace_bytes, NSA_IMPL_TC, plan, stream);
+}
+
+static int selection_bwd_impl(const void* q, const void* k, const void* v,
+                              const int32_t* block_idx, const void* o, const float* lse,
+                              const void* d_o, void* dq, void* dk, void* dv, const NsaDims* dims,
+                              int S, int block_size, const float* row_scale, const float* row_dot,
+                              void* workspace, size_t workspace_bytes, int impl, const void* plan, void* stream) {
   int rc = check_sel(dims, S, block_size);
   if (rc != NSA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
@@ -406,6 +474,7 @@ extern "C" int nsa_selection_bwd(const void* q, const void* k, const void* v,
   if (use_tc(dims, block_size, impl, &rc) && S > 0) {
     a.dk_acc = (float*)dk;
     a.dv_acc = (float*)dv;
+    a.sel_plan = plan;
     return tc_attn_bwd(a, workspace, workspace_bytes, st);
   }
   if (rc != NSA_OK) return rc;

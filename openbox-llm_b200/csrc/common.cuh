@@ -99,6 +99,7 @@ struct AttnArgs {
   const void* d_o; void* dq; float* dk_acc; float* dv_acc;   // backward
   const float* row_scale; const float* row_dot;   // backward of a gated branch (may be null)
   float* dq_acc;     // tcgen05 window / compression backward: fp32 accumulator [B*Hkv][T][G][D] that takes dQ (or null)
+  const void* sel_plan;   // tcgen05 selection: CSR + pair map + work list built earlier (tc_sel_plan_build), or null
   int B, Hq, Hkv, T, Lk, D, S;
   int kind;          // 0 window, 1 compress, 2 selection
   int window, block_size;
@@ -113,6 +114,8 @@ bool tc_shape_ok(const NsaDims& d, int block_size);
 int tc_attn_fwd(const AttnArgs& a, cudaStream_t st);
 size_t tc_sel_fwd_workspace(const AttnArgs& a);
 int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
+size_t tc_sel_plan_bytes(const AttnArgs& a);
+int tc_sel_plan_build(const AttnArgs& a, void* plan, size_t plan_bytes, cudaStream_t st);
 size_t tc_attn_bwd_workspace(const AttnArgs& a);
 int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_dq_reduce3(const AttnArgs& base, int Lk_cmp, int cmp_len, int cmp_stride, int S, int block_size,

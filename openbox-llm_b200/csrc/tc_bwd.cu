@@ -1282,9 +1282,12 @@ struct BwdPlan {
   size_t off_acc;
   size_t cap_pairs;          // selection: pairs the CSR may hold
   size_t off_delta, off_part, off_csr_ws, off_qob, off_off, off_pbh, off_pos, off_work, total;
+  size_t sel_region_bytes;   // selection: bytes from off_qob to the end of the work list
 };
 
-size_t sel_work_max_items(size_t units, int n_ktiles, size_t cap_pairs, int nq);   // tc_fwdpair.cu
+struct SelRegion { size_t qob, pbh, off, pos, work, total; };                     // tc_fwdpair.cu
+SelRegion sel_region(size_t units, int n_ktiles, size_t cap_pairs, int nq);
+size_t sel_work_max_items(size_t units, int n_ktiles, size_t cap_pairs, int nq);
 size_t sel_work_bytes(size_t units, int n_ktiles, size_t cap_pairs, int nq);
 int sel_build_worklist(const int32_t* offsets, int n_ktiles, size_t units, size_t cap_pairs, int nq,
                        void* work, cudaStream_t st);
@@ -1316,11 +1319,11 @@ static BwdPlan plan_bwd(const AttnArgs& a) {
   pl.off_csr_ws = pl.off_qob = pl.off_off = pl.off_pbh = pl.off_pos = off;
   if (a.kind == 2) {
     pl.off_csr_ws = off; off += align_up(nsa_csr_workspace_bytes(a.B, a.Hkv, pl.n_ktiles * kKeys, a.S, kKeys), 256);
-    pl.off_qob = off; off += align_up(pl.cap_pairs * 4, 256);
-    pl.off_pbh = off; off += align_up(pl.cap_pairs * 4, 256);
-    pl.off_off = off; off += align_up(units * (pl.n_ktiles + 1) * 4, 256);
-    pl.off_pos = off; off += align_up(pl.cap_pairs * 4, 256);
-    pl.off_work = off; off += align_up(sel_work_bytes(units, pl.n_ktiles, pl.cap_pairs, pl.nq), 256);
+    const SelRegion r = sel_region(units, pl.n_ktiles, pl.cap_pairs, pl.nq);   // same layout as the forward's
+    pl.off_qob = off + r.qob; pl.off_pbh = off + r.pbh; pl.off_off = off + r.off;
+    pl.off_pos = off + r.pos; pl.off_work = off + r.work;
+    pl.sel_region_bytes = r.total;
+    off += r.total;
   }
   // compression: a few key tiles are attended by (almost) every query; split their row tiles
   pl.n_splits = 1;
@@ -1394,13 +1397,17 @@ int tc_attn_bwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   NSA_LAUNCH_OK("delta_kernel");
   int32_t* pair_of_slot = (int32_t*)(base + pl.off_pos);
   if (a.kind == 2) {
-    int rc = build_csr_internal(a.block_idx, a.B, a.Hkv, a.T, a.S, kKeys, pl.n_ktiles,
-                                (int32_t*)(base + pl.off_qob), (int32_t*)(base + pl.off_off),
-                                (int32_t*)(base + pl.off_pbh), pair_of_slot, base + pl.off_csr_ws,
-                                pl.off_qob - pl.off_csr_ws, st);
-    if (rc != NSA_OK) return rc;
-    rc = sel_build_worklist(p.offsets, pl.n_ktiles, (size_t)a.B * a.Hkv, pl.cap_pairs, pl.nq, base + pl.off_work, st);
-    if (rc != NSA_OK) return rc;
+    if (a.sel_plan) {      // built earlier for this block list: one copy instead of the build
+      NSA_CUDA_OK(cudaMemcpyAsync(base + pl.off_qob, a.sel_plan, pl.sel_region_bytes, cudaMemcpyDeviceToDevice, st));
+    } else {
+      int rc = build_csr_internal(a.block_idx, a.B, a.Hkv, a.T, a.S, kKeys, pl.n_ktiles,
+                                  (int32_t*)(base + pl.off_qob), (int32_t*)(base + pl.off_off),
+                                  (int32_t*)(base + pl.off_pbh), pair_of_slot, base + pl.off_csr_ws,
+                                  pl.off_qob - pl.off_csr_ws, st);
+      if (rc != NSA_OK) return rc;
+      rc = sel_build_worklist(p.offsets, pl.n_ktiles, (size_t)a.B * a.Hkv, pl.cap_pairs, pl.nq, base + pl.off_work, st);
+      if (rc != NSA_OK) return rc;
+    }
     p.work = (const SelWorkHeader*)(base + pl.off_work);
     KernelScope ks("sel_split_blocks_kernel", st);
     sel_split_blocks_kernel<<<dim3(pl.n_ktiles, a.B * a.Hkv), 256, 0, st>>>(p.offsets, p.dk_acc, p.dv_acc, p.dk, p.dv,

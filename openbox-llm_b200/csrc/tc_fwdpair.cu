@@ -176,6 +176,23 @@ int sel_build_worklist(const int32_t* offsets, int n_ktiles, size_t units, size_
   return NSA_OK;
 }
 
+// The index structures of a block list that the block-outer selection kernels walk: CSR
+// (queries of each block), the pair's unit, the block offsets, the (query, slot) -> pair map and
+// the work list.  Forward and backward lay them out the same way inside their workspaces, so a
+// copy built once ("plan") can be dropped into either instead of building them again.
+struct SelRegion { size_t qob, pbh, off, pos, work, total; };
+SelRegion sel_region(size_t units, int n_ktiles, size_t cap_pairs, int nq) {
+  SelRegion r;
+  size_t off = 0;
+  r.qob = off; off += align_up(cap_pairs * 4, 256);
+  r.pbh = off; off += align_up(cap_pairs * 4, 256);
+  r.off = off; off += align_up(units * (n_ktiles + 1) * 4, 256);
+  r.pos = off; off += align_up(cap_pairs * 4, 256);
+  r.work = off; off += align_up(sel_work_bytes(units, n_ktiles, cap_pairs, nq), 256);
+  r.total = off;
+  return r;
+}
+
 struct PairPlan {
   int n_ktiles, nq;
   size_t cap_pairs;
@@ -194,12 +211,10 @@ static PairPlan plan_pairs(const AttnArgs& a) {
   pl.off_part = off; off += align_up(pl.cap_pairs * G * a.D * 2, 256);
   pl.off_ml = off; off += align_up(pl.cap_pairs * G * 2 * 4, 256);
   pl.off_csr_ws = off; off += align_up(nsa_csr_workspace_bytes(a.B, a.Hkv, pl.n_ktiles * kKeys, a.S, kKeys), 256);
-  pl.off_qob = off; off += align_up(pl.cap_pairs * 4, 256);
-  pl.off_pbh = off; off += align_up(pl.cap_pairs * 4, 256);
-  pl.off_off = off; off += align_up(units * (pl.n_ktiles + 1) * 4, 256);
-  pl.off_pos = off; off += align_up(pl.cap_pairs * 4, 256);
-  pl.off_work = off; off += align_up(sel_work_bytes(units, pl.n_ktiles, pl.cap_pairs, pl.nq), 256);
-  pl.total = off;
+  const SelRegion r = sel_region(units, pl.n_ktiles, pl.cap_pairs, pl.nq);
+  pl.off_qob = off + r.qob; pl.off_pbh = off + r.pbh; pl.off_off = off + r.off;
+  pl.off_pos = off + r.pos; pl.off_work = off + r.work;
+  pl.total = off + r.total;
   return pl;
 }
 
@@ -216,6 +231,31 @@ int tc_fwdpair_launch(const AttnArgs& a, const int32_t* q_of_block, const int32_
                        int n_ktiles, int nq_union, size_t cap_pairs, unsigned grid, cudaStream_t st);
 
 size_t tc_sel_fwd_workspace(const AttnArgs& a) { return tc::plan_pairs(a).total; }
+
+// plan buffer: the region, then the scratch of the CSR build
+size_t tc_sel_plan_bytes(const AttnArgs& a) {
+  using namespace tc;
+  const PairPlan pl = plan_pairs(a);
+  const SelRegion r = sel_region((size_t)a.B * a.Hkv, pl.n_ktiles, pl.cap_pairs, pl.nq);
+  return r.total + align_up(nsa_csr_workspace_bytes(a.B, a.Hkv, pl.n_ktiles * kKeys, a.S, kKeys), 256);
+}
+
+int tc_sel_plan_build(const AttnArgs& a, void* plan, size_t plan_bytes, cudaStream_t st) {
+  using namespace tc;
+  const PairPlan pl = plan_pairs(a);
+  const size_t units = (size_t)a.B * a.Hkv;
+  const SelRegion r = sel_region(units, pl.n_ktiles, pl.cap_pairs, pl.nq);
+  if (!plan || plan_bytes < tc_sel_plan_bytes(a)) {
+    set_error("selection plan buffer too small: need %zu bytes", tc_sel_plan_bytes(a));
+    return NSA_ERR_WORKSPACE;
+  }
+  char* base = (char*)plan;
+  int rc = build_csr_internal(a.block_idx, a.B, a.Hkv, a.T, a.S, kKeys, pl.n_ktiles, (int32_t*)(base + r.qob),
+                              (int32_t*)(base + r.off), (int32_t*)(base + r.pbh), (int32_t*)(base + r.pos),
+                              base + r.total, plan_bytes - r.total, st);
+  if (rc != NSA_OK) return rc;
+  return sel_build_worklist((const int32_t*)(base + r.off), pl.n_ktiles, units, pl.cap_pairs, pl.nq, base + r.work, st);
+}
 
 // Selection forward: statistics, CSR, then both variants are launched; the device-side rule
 // lets exactly one of them do the work.
@@ -242,12 +282,17 @@ int tc_sel_fwd(const AttnArgs& a, void* ws, size_t ws_bytes, cudaStream_t st) {
   NSA_LAUNCH_OK("sel_stats_kernel");
   int32_t* offsets = (int32_t*)(base + pl.off_off);
   int32_t* pair_of_slot = (int32_t*)(base + pl.off_pos);
-  int rc = build_csr_internal(a.block_idx, a.B, a.Hkv, a.T, a.S, kKeys, pl.n_ktiles,
-                              (int32_t*)(base + pl.off_qob), offsets, (int32_t*)(base + pl.off_pbh),
-                              pair_of_slot, base + pl.off_csr_ws, pl.off_qob - pl.off_csr_ws, st);
-  if (rc != NSA_OK) return rc;
-  rc = sel_build_worklist(offsets, pl.n_ktiles, (size_t)a.B * a.Hkv, pl.cap_pairs, pl.nq, base + pl.off_work, st);
-  if (rc != NSA_OK) return rc;
+  int rc = NSA_OK;
+  if (a.sel_plan) {      // built earlier for this block list: one copy instead of the build
+    NSA_CUDA_OK(cudaMemcpyAsync(base + pl.off_qob, a.sel_plan, pl.total - pl.off_qob, cudaMemcpyDeviceToDevice, st));
+  } else {
+    rc = build_csr_internal(a.block_idx, a.B, a.Hkv, a.T, a.S, kKeys, pl.n_ktiles,
+                            (int32_t*)(base + pl.off_qob), offsets, (int32_t*)(base + pl.off_pbh),
+                            pair_of_slot, base + pl.off_csr_ws, pl.off_qob - pl.off_csr_ws, st);
+    if (rc != NSA_OK) return rc;
+    rc = sel_build_worklist(offsets, pl.n_ktiles, (size_t)a.B * a.Hkv, pl.cap_pairs, pl.nq, base + pl.off_work, st);
+    if (rc != NSA_OK) return rc;
+  }
   const int force = get_option_sel_fwd();
   rc = tc_fwd_union_launch(a, stats, offsets, force, st);
   if (rc != NSA_OK) return rc;

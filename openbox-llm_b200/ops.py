@@ -128,9 +128,29 @@ def range_attn_backward_acc(q, k, v, o, lse, do, mode, window, block_size, row_s
 
 
 @L.on_device
-def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False, out=None):
+def selection_plan(q, k, block_idx, block_size):
+    """The index structures the tcgen05 selection kernels walk (CSR, pair map, work list), built
+    once for a block list so that forward and backward need not each build them; None when the
+    shape is not served by those kernels.  Opaque uint8 tensor."""
+    B, Hq, T, D = q.shape
+    S = block_idx.shape[-1]
+    if _impl == "simt" or S == 0:
+        return None
+    d = L.dims(B, Hq, k.shape[1], T, D, L.dtype_code(q))
+    n = L.lib().nsa_selection_plan_bytes(d, S, int(block_size))
+    if n == 0:
+        return None
+    idx = block_idx.to(torch.int32).contiguous()
+    plan = torch.empty(n, dtype=torch.uint8, device=q.device)
+    L.check(L.lib().nsa_selection_plan_build(L.ptr(idx), d, S, int(block_size), L.ptr(plan), n, L.stream()))
+    return plan
+
+
+@L.on_device
+def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False, out=None, plan=None):
     """nsa_selection_kernel.py:175-213.  q [B,Hq,T,D], k/v [B,Hkv,T,D], block_idx [B,Hkv,T,S].
-    `out` = (o, lse): write into existing contiguous tensors (not in the reference's signature)."""
+    `out` = (o, lse): write into existing contiguous tensors; `plan`: see selection_plan (neither
+    is in the reference's signature)."""
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     S = block_idx.shape[-1]
     assert block_idx.shape[:3] == (B, Hkv, T)
@@ -142,15 +162,20 @@ def selection_forward_triton(q, k, v, block_idx, block_size, return_lse=False, o
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
     nws = L.lib().nsa_selection_fwd_workspace_bytes(d, S, block_size, L.IMPL[_impl])
     ws = L.workspace(nws, q.device)
-    L.check(L.lib().nsa_selection_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
-                                      L.ptr(lse), d, S, int(block_size), L.ptr(ws), nws,
-                                      L.IMPL[_impl], L.stream()))
+    if plan is not None:
+        L.check(L.lib().nsa_selection_fwd_planned(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
+                                                  L.ptr(lse), d, S, int(block_size), L.ptr(ws), nws,
+                                                  L.ptr(plan), L.stream()))
+    else:
+        L.check(L.lib().nsa_selection_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
+                                          L.ptr(lse), d, S, int(block_size), L.ptr(ws), nws,
+                                          L.IMPL[_impl], L.stream()))
     return (o, lse) if return_lse else o
 
 
 @L.on_device
 def _selection_backward(q, k, v, block_idx, block_size, do, o, lse, row_scale=None, row_dot=None,
-                        defer_dq=False):
+                        defer_dq=False, plan=None):
     B, Hq, Hkv, T, D = _check_qkv(q, k, v)
     S = block_idx.shape[-1]
     assert block_size >= 16
@@ -161,10 +186,16 @@ def _selection_backward(q, k, v, block_idx, block_size, do, o, lse, row_scale=No
     d = L.dims(B, Hq, Hkv, T, D, L.dtype_code(q))
     nws = L.lib().nsa_selection_bwd_workspace_bytes(d, S, block_size, L.IMPL[_impl])
     ws = L.workspace(nws, q.device)
-    L.check(L.lib().nsa_selection_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
-                                      L.ptr(lse), L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, S,
-                                      int(block_size), L.ptr(row_scale), L.ptr(row_dot), L.ptr(ws),
-                                      nws, L.IMPL[_impl], L.stream()))
+    if plan is not None:
+        L.check(L.lib().nsa_selection_bwd_planned(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
+                                                  L.ptr(lse), L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, S,
+                                                  int(block_size), L.ptr(row_scale), L.ptr(row_dot), L.ptr(ws),
+                                                  nws, L.ptr(plan), L.stream()))
+    else:
+        L.check(L.lib().nsa_selection_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(idx), L.ptr(o),
+                                          L.ptr(lse), L.ptr(do), L.ptr(dq), L.ptr(dk), L.ptr(dv), d, S,
+                                          int(block_size), L.ptr(row_scale), L.ptr(row_dot), L.ptr(ws),
+                                          nws, L.IMPL[_impl], L.stream()))
     return (ws if defer_dq else dq), dk, dv
 
 
@@ -342,15 +373,20 @@ class SelectionAttnTriton(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, block_idx, block_size):
-        o, lse = selection_forward_triton(q, k, v, block_idx, block_size, return_lse=True)
+        # the index structures of the block list are built once for forward and backward (the
+        # reference builds its CSR in each: nsa_selection_kernel.py:199-201, nsa_selection_backward.py:356-358)
+        plan = None
+        if q.is_cuda and q.dtype == torch.bfloat16 and any(ctx.needs_input_grad[:3]):
+            plan = selection_plan(q, k, block_idx, block_size)
+        o, lse = selection_forward_triton(q, k, v, block_idx, block_size, return_lse=True, plan=plan)
         ctx.save_for_backward(q, k, v, block_idx, o, lse)
-        ctx.block_size = block_size
+        ctx.block_size, ctx.sel_plan = block_size, plan
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, block_idx, o, lse = ctx.saved_tensors
-        dq, dk, dv = _selection_backward(q, k, v, block_idx, ctx.block_size, do, o, lse)
+        dq, dk, dv = _selection_backward(q, k, v, block_idx, ctx.block_size, do, o, lse, plan=ctx.sel_plan)
         return dq, dk, dv, None, None
 
 
@@ -538,12 +574,15 @@ class _NSAAttention(torch.autograd.Function):
                                     n_local_blocks=n_local, cmp_len=cl, cmp_stride=cs)
         else:
             block_idx = block_idx.to(torch.int32).contiguous()
+        # CSR, pair map and work list of the block list: built once, used by forward and backward
+        plan = selection_plan(q, ks, block_idx, block_size) if q.dtype == torch.bfloat16 else None
         o_slc, _ = selection_forward_triton(q, ks, vs, block_idx, block_size, return_lse=True,
-                                            out=(o3[1], lse3[1]))
+                                            out=(o3[1], lse3[1]), plan=plan)
         o_win, _ = range_attn_forward(q, kw, vw, MODE_WINDOW, window, 0, out=(o3[2], lse3[2]))
         gate = gate_logits.to(q.dtype).contiguous()
         out = _gate_fwd(o_cmp, o_slc, o_win, gate)
         ctx.save_for_backward(q, kc, vc, ks, vs, kw, vw, gate, k_cmp, v_cmp, o3, lse3, block_idx, *cp)
+        ctx.sel_plan = plan          # (an opaque byte buffer: kept on the context, not a differentiable input)
         ctx.cfg = (block_size, window, learned, gate_logits.dtype,
                    tuple(t.dtype for t in (k_intra, k_logits, k_proj, v_intra, v_logits, v_proj))
                    if learned else None, cl, cs)
@@ -589,7 +628,7 @@ class _NSAAttention(torch.autograd.Function):
             dkw, dvw = range_attn_backward_acc(q, kw, vw, o_win, lse_win, d_out, MODE_WINDOW, window, 0,
                                                rs[2], rd[2], dq_acc)
             ws2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
-                                                rs[1], rd[1], defer_dq=True)
+                                                rs[1], rd[1], defer_dq=True, plan=ctx.sel_plan)
             L.check(L.lib().nsa_dq_finish(dm, S, int(block_size), L.ptr(dq_acc), L.ptr(ws2), L.ptr(dq_sum),
                                           L.stream()))
             del ws2, dq_acc
@@ -598,7 +637,7 @@ class _NSAAttention(torch.autograd.Function):
                                                      MODE_COMPRESS_STRIDED, cs, cl, rs[0], rd[0],
                                                      defer_dq=fused)
             dq2, dks, dvs = _selection_backward(q, ks, vs, block_idx, block_size, d_out, o_slc, lse_slc,
-                                                rs[1], rd[1], defer_dq=fused)
+                                                rs[1], rd[1], defer_dq=fused, plan=ctx.sel_plan)
             dq3, dkw, dvw = range_attn_backward(q, kw, vw, o_win, lse_win, d_out, MODE_WINDOW, window, 0,
                                                 rs[2], rd[2], defer_dq=fused)
             if fused:

@@ -230,3 +230,30 @@ def test_wait_that_runs_out_gives_up_and_leaves_the_context_usable():
     torch.cuda.synchronize()
     assert lib.nsa_device_status(None) == 0
     assert torch.equal(o, o_ok) and torch.equal(lse, lse_ok)
+
+
+def test_selection_plan_gives_the_same_results():
+    """The index structures of a block list built once (nsa_selection_plan_build) and handed to
+    nsa_selection_fwd_planned / nsa_selection_bwd_planned, against the calls that build them inside
+    their workspace: o, lse and dq bit for bit (integer structures, same kernels), dk / dv within
+    the accumulation-order bound."""
+    nsa = pkg()
+    dtype = torch.bfloat16
+    for c in (TC_CONFIGS[1], TC_CONFIGS[3]):
+        if not nsa.tc_supported(c["B"], c["Hq"], c["Hkv"], c["T"], c["D"], dtype, c["block_size"]):
+            continue
+        t = make_inputs(c, dtype, seed=13, scale_qkv=True)
+        q, k, v, do = (dev(t[n], dtype) for n in ("q", "ks", "vs", "do"))
+        idx = t["block_idx"].cuda() if "block_idx" in t else O.make_block_idx(
+            c["B"], c["Hkv"], c["T"], c["block_size"], c["S"], seed=3).cuda()
+        plan = nsa.ops.selection_plan(q, k, idx, c["block_size"])
+        assert plan is not None
+        o0, l0 = nsa.selection_forward_triton(q, k, v, idx, c["block_size"], return_lse=True)
+        o1, l1 = nsa.selection_forward_triton(q, k, v, idx, c["block_size"], return_lse=True, plan=plan)
+        assert torch.equal(o0, o1) and torch.equal(l0, l1), cfg_id(c)
+        g0 = nsa.ops._selection_backward(q, k, v, idx, c["block_size"], do, o0, l0)
+        g1 = nsa.ops._selection_backward(q, k, v, idx, c["block_size"], do, o0, l0, plan=plan)
+        assert torch.equal(g0[0], g1[0]), cfg_id(c)
+        for a, b in zip(g0[1:], g1[1:]):
+            assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -7 * max(b.float().abs().max().item(), 1e-6)
+    assert nsa.lib().nsa_device_status(None) == 0
