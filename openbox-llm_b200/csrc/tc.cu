@@ -7,13 +7,15 @@
 //   compression the tiles covering summaries [0, (t_last + 1) / Bsz - 1]
 //   selection   the union of the 64-token blocks listed for the tile's nq queries, built in
 //               shared memory, with a per-(query, block) membership bit
-// Per tile: TMA brings K and V (128B-swizzled boxes) into a 2-stage ring; one thread issues
-// S = Q K^T (tcgen05.mma, accumulator in TMEM); each of the 128 threads owns one row of S
-// (tcgen05.ld, lane = row), masks it, runs the online softmax in the log2 domain without any
-// cross-thread traffic, writes P as packed bf16 back to TMEM (tcgen05.st) and the same
-// thread issues O += P V with P as the TMEM A operand and V as an MN-major shared-memory B
-// operand.  The running maximum is only raised when it grows by more than 8 (log2 units), so
-// the O accumulator in TMEM is rescaled rarely.
+// Per tile: a TMA warp brings K and V (128B-swizzled boxes) into a 2-stage ring; an MMA warp
+// issues S = Q K^T (tcgen05.mma, Q held in TMEM as the A operand, accumulator in TMEM); each of
+// the 128 softmax threads owns one row of S (tcgen05.ld, lane = row), masks it, runs the online
+// softmax in the log2 domain without any cross-thread traffic and writes P as packed bf16 over S
+// in TMEM (tcgen05.st); the MMA warp then issues O += P V with P as the TMEM A operand and V as
+// an MN-major shared-memory B operand.  The running maximum is only raised when it grows by more
+// than 8 (log2 units), so the O accumulator in TMEM is rescaled rarely.
+// tc_fwd_kernel takes one row tile per CTA (query-outer selection); tc_fwd_range_kernel is the
+// persistent form for window and compression.
 #include "tc_common.cuh"
 #include "tc_host.cuh"
 
