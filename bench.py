@@ -831,17 +831,16 @@ def main():
                     "selection_kernels": {k: {"launch_ms": v, "tflops": (4 if "fwd" in k else 10) * fl / (v * 1e-3) / 1e12,
                                               "frac_of_tensor_peak": (4 if "fwd" in k else 10) * fl / (v * 1e-3) / 1e12 / pk["tflops"]}
                                           for k, v in per.items() if v > 0.5}}
-            # (3) the published geometry (summaries 32 / 16, forced blocks): parity unpinned
-            # (its 2047 summaries would need 32 dQ slots per query: the compression and window
-            # branches add their dQ into the fp32 accumulator instead)
+            # (3) the published geometry (summaries 32 / 16, forced blocks): parity unpinned.  Its 2047
+            # summaries take 32 dQ slots per query in the compression backward (34 GB of partials on
+            # one GPU); --dq-accumulator trades them for the slower fp32 accumulator
             w2 = WORKLOADS["c4_t32k_l32d16"]
-            nsa.set_dq_accumulator(True)
             ms, peak, _, _ = short_leg(args, "c4_t32k_l32d16", w2, rank, world, dev, dist, nsa, L, mine, steps=3)
-            nsa.set_dq_accumulator(args.dq_accumulator)
             also["c4_t32k_l32d16"] = {"config": config_of("c4_t32k_l32d16", w2), "value": w2["B"] * w2["T"] / (ms * 1e-3),
                                       "unit": "tokens/s", "ms_per_step": ms, "steps": 3, "warmup": 3,
                                       "peak_hbm_gb": peak, "parity": "unpinned",
-                                      "backward": "dq of window + compression through the fp32 accumulator"}
+                                      "backward": ("dq of window + compression through the fp32 accumulator"
+                                                   if args.dq_accumulator else "bf16 dq partial slots")}
             # (4) forward only at long context: 4 kv-head units over min(world, 4) ranks
             sweep = {}
             for nm in ("c3_t16k_fwd", "c3_t32k_fwd", "c3_t64k_fwd", "c3_t128k_fwd"):
