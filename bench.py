@@ -755,6 +755,45 @@ def short_leg(args, name, w, rank, world, dev, dist, nsa, L, units, steps=5, blo
     return ms, peak, per, counts
 
 
+def head_split_leg(w, rank, used, parts, dev, dist, nsa, L, steps=5):
+    """Forward of a workload whose (batch, kv-head) units are fewer than the ranks: rank r takes
+    unit r // parts and the part r % parts of its query heads.  The block lists come from the
+    whole group (select_blocks, the same on every rank of a unit), everything else is the rank's
+    own heads against the unit's K / V.  Returns (ms per step as the max over ranks, peak GB)."""
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    step = lambda: None
+    if rank < used:
+        u, part = rank // parts, rank % parts
+        t, comp = unit_inputs(w, [u], seed=4321, device=dev)
+        G = t["q"].shape[1]
+        hs = slice(part * (G // parts), (part + 1) * (G // parts))
+        kw = dict(n_init_blocks=w.get("n_init", 0), n_local_blocks=w.get("n_local", 0),
+                  cmp_len=w.get("cmp_len"), cmp_stride=w.get("cmp_stride"))
+
+        q_part, gate_part = t["q"][:, hs].contiguous(), t["gate"][:, hs].contiguous()
+
+        def step():
+            with torch.no_grad():
+                idx = nsa.select_blocks(t["q"], t["kc"], t["vc"], w["block_size"], w["n_sel"], compressor=comp, **kw)
+                return nsa.nsa_attention(q_part, *(t[n] for n in NAMES[1:7]), gate_part, w["block_size"],
+                                         w["n_sel"], w["window"], compressor=comp, block_idx=idx, **kw)
+    for _ in range(3):
+        step()
+    ms = timed(step, steps, barrier) / steps
+    L.check_device_status()
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    if dist is not None:
+        tt = torch.tensor([ms, peak], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, peak = tt.tolist()
+    return ms, peak
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -841,14 +880,24 @@ def main():
                                       "peak_hbm_gb": peak, "parity": "unpinned",
                                       "backward": ("dq of window + compression through the fp32 accumulator"
                                                    if args.dq_accumulator else "bf16 dq partial slots")}
-            # (4) forward only at long context: 4 kv-head units over min(world, 4) ranks
+            # (4) forward only at long context: the 4 kv-head units over up to 4 ranks; with 8 ranks
+            # every unit's 16 query heads are dealt out over two ranks (K / V of the unit on both, the
+            # block lists computed from the whole group on both, no communication)
             sweep = {}
             for nm in ("c3_t16k_fwd", "c3_t32k_fwd", "c3_t64k_fwd", "c3_t128k_fwd"):
                 w3 = WORKLOADS[nm]
-                u3 = list(range(*shard.unit_range(w3["B"] * w3["Hkv"], min(world, 4), rank))) if rank < 4 else []
-                ms, peak, _, _ = short_leg(args, nm, w3, rank, world, dev, dist, nsa, L, u3, steps=5)
+                n3 = w3["B"] * w3["Hkv"]
+                parts = 2 if world >= 2 * n3 else 1
+                used = min(world, n3) * parts
+                if parts == 1:
+                    u3 = list(range(*shard.unit_range(n3, min(world, n3), rank))) if rank < n3 else []
+                    ms, peak, _, _ = short_leg(args, nm, w3, rank, world, dev, dist, nsa, L, u3, steps=5)
+                else:
+                    ms, peak = head_split_leg(w3, rank, used, parts, dev, dist, nsa, L, steps=5)
                 sweep[nm] = {"T": w3["T"], "value": w3["B"] * w3["T"] / (ms * 1e-3), "unit": "forward tokens/s",
-                             "ms_per_step": ms, "peak_hbm_gb": peak, "ranks_used": min(world, 4), "steps": 5, "warmup": 3}
+                             "ms_per_step": ms, "peak_hbm_gb": peak, "ranks_used": used,
+                             "split": "units" if parts == 1 else "units x halves of each unit's query heads",
+                             "steps": 5, "warmup": 3}
             also["c3_forward_sweep"] = {"shape": "B=1, 64 query / 4 kv heads, D=128", "points": sweep}
             # (5) the 12-layer model step
             m = model_workload(args, rank, world, dev, dist, steps=8)

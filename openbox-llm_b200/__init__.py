@@ -4,5 +4,5 @@ from .ops import (MODE_COMPRESS, MODE_COMPRESS_STRIDED, MODE_WINDOW, SelectionAt
                   block_compress, block_mean_pool, build_block_to_query_csr,
                   compression_attn_triton, gate_combine, get_dq_accumulator, get_impl, nsa_attention,
                   nsa_fused_forward, range_attn_backward, range_attn_forward,
-                  selection_attn_triton, selection_backward_triton, selection_forward_triton,
+                  select_blocks, selection_attn_triton, selection_backward_triton, selection_forward_triton,
                   set_dq_accumulator, set_impl, set_option, tc_supported, topn_blocks, window_attn_triton)

@@ -663,6 +663,29 @@ class _NSAAttention(torch.autograd.Function):
                 *pgrads)
 
 
+@torch.no_grad()
+def select_blocks(q, kc, vc, block_size, n_sel, compressor=None, n_init_blocks=0, n_local_blocks=0,
+                  cmp_len=None, cmp_stride=None):
+    """The block lists [B,Hkv,T,n_sel] the whole op picks for q (pooling, compression attention,
+    block scoring + top-n; nsa_model.py:336-355), without the rest of the op.  The scores sum over
+    all query heads of a kv head, so a caller that deals the query heads of one group out over
+    several devices computes the lists from the whole group on each and passes them to
+    nsa_attention(..., block_idx=...) with its share of the heads."""
+    cl = int(block_size if cmp_len is None else cmp_len)
+    cs = int(cl if cmp_stride is None else cmp_stride)
+    if compressor is not None:
+        cp = [compressor[n].detach().float().contiguous()
+              for n in ("k_intra", "k_logits", "k_proj", "v_intra", "v_logits", "v_proj")]
+        k_cmp = _compress_fwd(kc, cp[0], cp[1], cp[2], cl, cs)
+        v_cmp = _compress_fwd(vc, cp[3], cp[4], cp[5], cl, cs)
+    else:
+        assert cl == cs == block_size, "mean pooling is defined on the aligned grid only"
+        k_cmp, v_cmp = _mean_pool_fwd(kc, block_size), _mean_pool_fwd(vc, block_size)
+    _, lse_cmp = range_attn_forward(q, k_cmp, v_cmp, MODE_COMPRESS_STRIDED, cs, cl)
+    return topn_blocks(q, k_cmp, lse_cmp, block_size, n_sel, n_init_blocks=n_init_blocks,
+                       n_local_blocks=n_local_blocks, cmp_len=cl, cmp_stride=cs)
+
+
 def nsa_attention(q, kc, vc, ks, vs, kw, vw, gate_logits, block_size, n_sel, window,
                   block_idx=None, compressor=None, return_block_idx=False, n_init_blocks=0,
                   n_local_blocks=0, cmp_len=None, cmp_stride=None):

@@ -128,3 +128,38 @@ def test_unit_shards_on_the_gpu_reproduce_the_unsharded_call_bit_for_bit():
         ref = full_p[k]
         assert (s - ref).abs().max().item() <= 1e-3 * max(1.0, ref.abs().max().item()), k
     assert nsa.lib().nsa_device_status(None) == 0
+
+
+@pytest.mark.gpu
+def test_query_heads_of_a_group_dealt_out_over_two_parts():
+    """Forward with fewer (batch, kv-head) units than devices, as bench.py runs the long-context
+    sweep on eight ranks: each part takes half of a group's query heads, the block lists come from
+    the whole group (select_blocks), K / V are the unit's.  The lists equal the unsplit op's bit
+    for bit; the outputs agree within bf16 rounding (a part has other row tiles than the whole
+    group, so its key tiles, hence the order of its sums, differ)."""
+    nsa = importlib.import_module("openbox-llm_b200")
+    dtype = torch.bfloat16
+    B, Hq, Hkv, T, D, bs, n_sel, W = 1, 16, 1, 2048, 128, 64, 8, 512
+    g = torch.Generator().manual_seed(31)
+    mk = lambda h: (torch.randn(B, h, T, D, generator=g) * D ** -0.5).to(dtype).cuda()
+    q = mk(Hq)
+    kv = [mk(Hkv) for _ in range(6)]
+    gate = torch.randn(B, Hq, T, 3, generator=g).to(dtype).cuda()
+    comp = {}
+    for p in ("k", "v"):
+        comp[p + "_intra"] = (0.02 * torch.randn(bs, D, generator=g)).cuda()
+        comp[p + "_logits"] = (0.3 * torch.randn(bs, generator=g)).cuda()
+        comp[p + "_proj"] = (torch.randn(D, D, generator=g) * D ** -0.5).cuda()
+    with torch.no_grad():
+        full, full_idx = nsa.nsa_attention(q, *kv, gate, bs, n_sel, W, compressor=comp, return_block_idx=True)
+        idx = nsa.select_blocks(q, kv[0], kv[1], bs, n_sel, compressor=comp)
+        assert torch.equal(idx, full_idx)
+        outs = []
+        for part in range(2):
+            hs = slice(part * 8, part * 8 + 8)
+            outs.append(nsa.nsa_attention(q[:, hs].contiguous(), *kv, gate[:, hs].contiguous(), bs, n_sel, W,
+                                          compressor=comp, block_idx=idx))
+    merged = torch.cat(outs, 1)
+    d = (merged.float() - full.float()).abs().max().item()
+    assert d <= 2.0 ** -7 * max(full.float().abs().max().item(), 1e-3), d
+    assert nsa.lib().nsa_device_status(None) == 0
