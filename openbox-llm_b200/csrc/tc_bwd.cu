@@ -753,6 +753,7 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
       for (int r = 0; r < kRounds; ++r) tq[r] = tq_of(0, box_of(r));
     }
+    const uint64_t pol_keep = l2_policy_evict_normal();   // gathered q / dO rows: read again by other blocks
     int issued = 0;                                  // tiles whose loads this warp has sent off
     for (int k = 0; k < n_tiles; ++k) {
       const int sb = k & 1;
@@ -779,8 +780,8 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         for (int r = 0; r < kRounds; ++r) {
           const int o = box_of(r);
           if (o < n_ops && p.merged) {
-            tma_load_5d(((o & 1) ? sDO : sQ) + (o >> 1) * (p.G / 8) * 2048, (o & 1) ? &tm_do : &tm_q, g_full + sb,
-                        0, 0, 0, tq[r], (b * p.Hq + hkv * p.G) >> 3);
+            tma_load_5d_hint(((o & 1) ? sDO : sQ) + (o >> 1) * (p.G / 8) * 2048, (o & 1) ? &tm_do : &tm_q, g_full + sb,
+                             0, 0, 0, tq[r], (b * p.Hq + hkv * p.G) >> 3, pol_keep);
           } else if (o < n_ops) {
             const int qq = o / (kSlabs * 2), kx = o % (kSlabs * 2);
             const int s = kx >> 1;
@@ -1028,7 +1029,7 @@ tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
           const int outer = p.kind == 2 ? 0 : bh;
 #pragma unroll
           for (int sl = 0; sl < kSlabs; ++sl)
-            tma_store_5d(&tm_dq, sP + sl * (kRows * 128), sl * 64, 0, slot, mid, outer);
+            tma_store_5d_hint(&tm_dq, sP + sl * (kRows * 128), sl * 64, 0, slot, mid, outer, l2_policy_evict_first());
           bulk_commit();
         }
       } else {   // the ragged last tile: 16 lanes write the 256 (D = 128) or 128 bytes of one row

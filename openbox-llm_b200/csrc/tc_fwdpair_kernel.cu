@@ -180,7 +180,8 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         const int o = r ? o1 : o0, tq = r ? tq1 : tq0;
         if (o < n_ops) {
           if (p.merged) {
-            tma_load_5d(dst + o * (p.G / 8) * 2048, &tm_q, q_full + st, 0, 0, 0, tq, (b * p.Hq + hkv * p.G) >> 3);
+            tma_load_5d_hint(dst + o * (p.G / 8) * 2048, &tm_q, q_full + st, 0, 0, 0, tq, (b * p.Hq + hkv * p.G) >> 3,
+                             l2_policy_evict_normal());
           } else {
             const int qq = o / kSlabs, sl = o % kSlabs;
             tma_load_3d(dst + sl * (kRows * 128) + qq * p.G * 128, &tm_q, q_full + st, sl * 64,
@@ -345,7 +346,8 @@ tc_fwdpair_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         if (et == 0) {
 #pragma unroll
           for (int sl = 0; sl < kSlabs; ++sl)
-            tma_store_5d(&tm_o, stage + sl * (kRows * 128), sl * 64, 0, 0, pair_base + i * p.nq, 0);
+            tma_store_5d_hint(&tm_o, stage + sl * (kRows * 128), sl * 64, 0, 0, pair_base + i * p.nq, 0,
+                              l2_policy_evict_first());
           bulk_commit();
         }
       } else {   // the ragged last tile: whole rows out by hand
